@@ -1,0 +1,96 @@
+/*
+ * fluxbin_b200 -- C ABI of the B200 (sm_100a) batch-1 packed-Linear decode kernels.
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no framework types.  Every
+ * entry point launches on the given CUDA stream, never synchronises and never throws;
+ * unless its comment says otherwise it also never allocates.  Return value: 0 on
+ * success, a negative FB_E* code on rejection (nothing was launched);
+ * fb_last_error() then holds a message for the calling thread.
+ * Device pointers must belong to the device that is current when the call is made.
+ *
+ * Citations name the reference project's interface each entry point replaces
+ * (paths relative to the reference project's root).
+ */
+#ifndef FLUXBIN_B200_H_
+#define FLUXBIN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* 16-bit floating formats of activations, outputs and scales. */
+#define FB_F16 0
+#define FB_BF16 1
+
+/* Error codes. */
+#define FB_OK 0
+#define FB_EINVAL (-1)  /* bad argument: null pointer, shape, dtype tag, alignment */
+#define FB_ELIMIT (-2)  /* dimension outside the supported bounds */
+#define FB_ESCRATCH (-3) /* scratch buffer missing or too small */
+#define FB_ECUDA (-4)   /* a CUDA runtime call failed (message holds its text) */
+#define FB_EALIAS (-5)  /* an output overlaps an input */
+
+/* fb_w3_gemv flags. */
+#define FB_W3_DECODED_BF16 1u /* add the +/-3 weight-rounding correction: the result then
+                                 follows the dequantised 16-bit weight rather than
+                                 scale * integer-dot (reference: "decoded_bf16" arithmetic,
+                                 csrc/w3_lut.cu:105-122).  Needs zero point 4 (zeros == NULL). */
+
+#define FB_W3_NO_PDL 2u /* launch without programmatic dependent launch (by default the
+                          kernel's prologue may overlap the previous kernel in the stream;
+                          it still waits for that kernel before reading x or writing) */
+#define FB_W3_GROUP_PARTIALS 4u /* M = 1 only: `out` is an fp32 [G,O] workspace that receives
+                                   each group's scaled sum instead of the reduced result
+                                   (reference: inline_main, csrc/w3_lut.cu:251-273); follow
+                                   with fb_w3_finish */
+
+typedef void* fb_stream_t; /* a cudaStream_t */
+
+/* Message describing the last rejected call made by this thread ("" if none). */
+const char* fb_last_error(void);
+
+/* Library / device facts: key "version", "sm_count", "max_smem", "w3_max_m".
+ *  Returns the value, or FB_EINVAL for an unknown key. */
+int64_t fb_query(const char* key);
+
+/* Bytes of scratch fb_w3_gemv needs for a problem of this size (partials of the K
+ * split plus one ticket word per 32 output rows).  The scratch must be zero-filled
+ * once after allocation; every call leaves it ready for the next.  One scratch may be
+ * shared by all calls that are ordered on one stream; calls that can overlap on the
+ * GPU need separate scratch. */
+size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_features);
+
+/*
+ * y[M,O] = x[M,K] . W^T with W the GPTQ W3 group-128 planar layout:
+ *   planes  uint8 [G,3,O,16]  bit planes of the codes, plane 2 stored inverted,
+ *                             8 input positions per byte, LSB first (G = K/128)
+ *   scales  f16|bf16 [G,O]
+ *   zeros   uint8 [G,O] zero points, or NULL for the constant zero point 4
+ *   perm    int16 [K] sorted position -> input column (desc_act), or NULL for identity
+ * W[o, perm[k]] = scale[k/128, o] * (code - zero); accumulation in fp32; the split over
+ * K is reduced inside the kernel in a fixed order, so results are repeat-exact.
+ * M = 1..4.  O % 32 == 0, G <= 255 (K <= 32640), O <= 65536; x, planes 16-byte aligned.
+ *
+ * Replaces the reference's pybind entry points inline_main + finish and m1_out
+ * (csrc/w3_lut.cu:251-332) and their launchers (:153-189).
+ */
+int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales,
+               int scale_dtype, const uint8_t* zeros, const int16_t* perm, void* out,
+               int out_features, int in_features, void* scratch, size_t scratch_bytes,
+               unsigned flags, fb_stream_t stream);
+
+/*
+ * out[o] = T( sum_s partials[s, o] ), rows summed in ascending order.
+ * partials fp32 [splits, O]; out f16|bf16 [O].
+ * Replaces the reference's finish (csrc/w3_lut.cu:275-296, kernel :142-150).
+ */
+int fb_w3_finish(const float* partials, int splits, int out_features, void* out, int out_dtype,
+                 fb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLUXBIN_B200_H_ */

@@ -1,0 +1,128 @@
+"""ctypes binding of ``libfluxbin_b200.so`` (the C ABI declared in ``include/fluxbin_b200.h``).
+
+There is no CPU substitute: if the library is missing or cannot be loaded, every call
+raises.  Tensors are passed as raw device pointers; the current torch CUDA stream is
+used for the launch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os as _os
+from pathlib import Path
+
+import torch
+
+LIBRARY = Path(__import__("os").environ.get("FB_LIBRARY", str(Path(__file__).resolve().parent / "libfluxbin_b200.so")))
+
+FB_F16, FB_BF16 = 0, 1
+FB_W3_DECODED_BF16 = 1
+FB_W3_NO_PDL = 2
+FB_W3_GROUP_PARTIALS = 4
+
+_lib = None
+
+
+class NativeError(RuntimeError):
+    """A call into the CUDA library was rejected (message from ``fb_last_error``)."""
+
+
+def library() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIBRARY.exists():
+            raise RuntimeError(
+                f"{LIBRARY.name} is not built; run `python -m marlin_style_fluxbin_b200.build` "
+                "(needs nvcc). There is no CPU or other fallback for the packed kernels."
+            )
+        lib = ctypes.CDLL(str(LIBRARY))
+        lib.fb_last_error.restype = ctypes.c_char_p
+        lib.fb_query.restype = ctypes.c_int64
+        lib.fb_query.argtypes = [ctypes.c_char_p]
+        lib.fb_w3_gemv_scratch_bytes.restype = ctypes.c_size_t
+        lib.fb_w3_gemv_scratch_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        lib.fb_w3_gemv.restype = ctypes.c_int
+        lib.fb_w3_gemv.argtypes = [
+            ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+            ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p,
+        ]
+        lib.fb_w3_finish.restype = ctypes.c_int
+        lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        _lib = lib
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise NativeError(library().fb_last_error().decode() or f"native call failed with code {code}")
+
+
+def dtype_tag(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return FB_F16
+    if dtype == torch.bfloat16:
+        return FB_BF16
+    raise ValueError("FP16/BF16 required")
+
+
+def ptr(tensor):
+    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+
+
+def stream_handle(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def query(key: str) -> int:
+    return int(library().fb_query(key.encode()))
+
+
+def w3_scratch_bytes(m: int, out_features: int, in_features: int) -> int:
+    return int(library().fb_w3_gemv_scratch_bytes(m, out_features, in_features))
+
+
+# One zero-initialised scratch per (device, stream): calls ordered on one stream may share
+# it; the kernels leave it ready for the next call.  Grown on demand, which allocates, so
+# the first call of a given size must happen before CUDA-graph capture (warm-up).
+_scratch: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("packed GEMV scratch must be sized by a warm-up call before graph capture")
+        buf = torch.zeros(max(nbytes, 1 << 21), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def w3_gemv(x, planes, scales, zeros, perm, out, *, decoded_bf16=False, group_partials=False,
+            pdl=True, scratch=None) -> None:
+    """Raw launch: x [M,K], planes [G,3,O,16], scales [G,O], out [M,O]; see the header.
+
+    With ``group_partials`` ``out`` is the fp32 ``[G,O]`` workspace of the two-call form."""
+    m, k = x.shape
+    o = planes.shape[2]
+    need = w3_scratch_bytes(m, o, k)
+    if scratch is None:
+        scratch = scratch_for(x.device, need)
+    if _os.environ.get("FB_NO_PDL"):
+        pdl = False
+    flags = (FB_W3_DECODED_BF16 if decoded_bf16 else 0) | (0 if pdl else FB_W3_NO_PDL) | (
+        FB_W3_GROUP_PARTIALS if group_partials else 0)
+    with torch.cuda.device(x.device):
+        check(library().fb_w3_gemv(
+            ptr(x), dtype_tag(x.dtype), m, ptr(planes), ptr(scales), dtype_tag(scales.dtype),
+            ptr(zeros), ptr(perm), ptr(out), o, k, ptr(scratch), scratch.numel() * scratch.element_size(),
+            flags, stream_handle(x.device)))
+
+
+def w3_finish(partials, out) -> None:
+    """out[0, o] = sum over rows of partials[:, o] (ascending), cast to out's dtype."""
+    splits, o = partials.shape
+    with torch.cuda.device(out.device):
+        check(library().fb_w3_finish(ptr(partials), splits, o, ptr(out), dtype_tag(out.dtype),
+                                     stream_handle(out.device)))

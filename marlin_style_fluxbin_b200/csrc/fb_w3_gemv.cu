@@ -1,0 +1,574 @@
+// GPTQ W3 group-128 planar GEMV for M = 1..4 rows of activations (batch-1 decode).
+//
+// HBM-bound byte work: every packed weight byte is read exactly once.  The design:
+//
+//  * K is cut into blocks of two groups (256 inputs = 32 chunks of 8).  For a K block a
+//    CTA holds 32 activation lookup tables (one per chunk, 256 subset sums each) in
+//    shared memory, laid out entry-major: entry p of table t lives at byte p*128 + t*4
+//    (M = 1), so the BANK of a lookup is the table number, never the weight byte.
+//  * A warp processes a unit of 32 output rows x one K block; lane = row, so no
+//    cross-lane reduction is needed.  Lanes walk the 32 chunks in a rotated order
+//    (half / word / byte rotation from the lane number) such that at every step the 32
+//    lanes address 32 different tables: all table lookups are bank-conflict free by
+//    construction, whatever the weights are.  The same rotation makes the reads of the
+//    staged weight words conflict free.
+//  * The three bit planes of a warp's units (contiguous rows, so 6 copies of n x 512
+//    bytes) are staged into shared memory with bulk asynchronous copies (cp.async.bulk
+//    + mbarrier) issued by one elected lane; a lookup address is a rotate and one
+//    logic op on the staged weight word.
+//  * One CTA per SM at most: each K block is served by floor(SMs / K blocks) CTAs that
+//    split its rows, so a CTA builds the tables of exactly one K block.
+//  * Launched with programmatic dependent launch: a kernel's prologue and first weight
+//    copies overlap the tail of the previous kernel in the stream; everything that
+//    reads activations or touches scratch comes after griddepcontrol.wait.  A CTA stays
+//    near 104 KB of shared memory (M = 1) so that two can be resident on an SM.
+//  * Split-K is reduced inside the kernel: fp32 partials go to a small L2-resident
+//    scratch, a ticket per 32-row unit elects the last contributor, which sums the
+//    partials in ascending K order (deterministic, repeat-exact) and writes the output.
+//
+// Arithmetic follows the reference kernel (csrc/w3_lut.cu:38-139): per group
+// dot = a0 + 2*a1 - 4*a2 over the stored planes (plane 2 inverted), times the group
+// scale, fp32 accumulation; tables hold ascending-order subset sums as in
+// csrc/lut8_unsigned.cuh:12-27.  Extension over the reference: fp16 or bf16 scales and
+// an optional per-(group,row) zero point, y += scale*(4-zero)*sum(x_group).
+#include <mutex>
+
+#ifndef FB_W3_TRACE
+#define FB_W3_TRACE 0
+#endif
+#if FB_W3_TRACE
+#define FB_MARK(i)                                                                                   \
+  do {                                                                                               \
+    if (threadIdx.x == 0 && blockIdx.x == 0) reinterpret_cast<long long*>(p.status)[8 + (i)] = clock64(); \
+    if (threadIdx.x == 0 && ((i) == 0 || (i) == 8))                                                  \
+      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.status) + (3 << 20))[blockIdx.x * 2 + ((i) == 8)] = fb::global_timer_ns(); \
+  } while (0)
+#else
+#define FB_MARK(i) \
+  do {             \
+  } while (0)
+#endif
+
+#include "fb_common.cuh"
+
+namespace {
+
+using namespace fb;
+
+constexpr int kUnitRows = 32;
+constexpr int kPlaneTile = kUnitRows * 16;  // 512 B: one plane of one group for a unit
+constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
+constexpr int kWarps = 16;
+constexpr int kMaxSlots = 4;
+constexpr int kMaxM = 4;
+
+struct W3Params {
+  const void* x;
+  const uint8_t* planes;
+  const unsigned short* scales;
+  const uint8_t* zeros;
+  const int16_t* perm;
+  void* out;        // [M,O] 16-bit, or fp32 [G,O] group partials when group_partials != 0
+  float* partials;  // [nKB, M, O]
+  unsigned* tickets;
+  unsigned* status;
+  int O, K, G, nKB, nRU;
+  int act_dtype, scale_dtype;
+  int slots;           // staged units per warp
+  int ctas_per_kb;     // row slices per K block
+  int group_partials;  // write scale-multiplied per-group sums instead of reducing
+};
+
+// log2 of the number of activation rows a table entry is padded to (1, 2 or 4 floats).
+template <int M>
+struct LutGeom {
+  static constexpr int kLog = M == 1 ? 0 : (M == 2 ? 1 : 2);
+  static constexpr int kStrideLog = 7 + kLog;           // bytes between consecutive entries
+  static constexpr int kBytes = 256 << kStrideLog;      // 32 KB per padded activation row
+};
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <int M, bool CORRECT>
+__global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const W3Params p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  using Geom = LutGeom<M>;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int S = p.slots;
+  unsigned char* const lut = smem;
+  // per warp: [group half][plane][slot][32 rows x 16 B]
+  unsigned char* const stage_base = smem + Geom::kBytes + (size_t)warp * S * kUnitBytes;
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + Geom::kBytes + (size_t)kWarps * S * kUnitBytes) + warp * (kMaxSlots + 1);
+  const uint32_t stage_u32 = smem_u32(stage_base);
+
+  FB_MARK(0);
+  // The next kernel in the stream may start its own prologue (weight prefetch) now; it
+  // orders itself after this grid with its own wait before touching activations or scratch.
+  pdl_launch_dependents();
+
+  const int nV = p.nKB * p.ctas_per_kb;
+  if ((int)blockIdx.x >= nV) return;
+
+  if (lane == 0)
+    for (int s = 0; s <= kMaxSlots; ++s) mbar_init(smem_u32(&bars[s]), 1);
+  mbar_init_fence();
+  __syncwarp();
+
+  // Work of virtual CTA v: K block v / c, rows of slice v % c; this warp's contiguous share.
+  auto share = [&](int v, int& kb, int& first, int& count) {
+    kb = v / p.ctas_per_kb;
+    const int slice = v - kb * p.ctas_per_kb;
+    const int ua = (int)((long long)slice * p.nRU / p.ctas_per_kb);
+    const int ub = (int)((long long)(slice + 1) * p.nRU / p.ctas_per_kb);
+    const int n = ub - ua, q = n / kWarps, r = n - q * kWarps;
+    first = ua + warp * q + min(warp, r);
+    count = q + (warp < r ? 1 : 0);
+  };
+  // Bulk copies of `n` consecutive units starting at unit `first` into slots [slot, slot+n).
+  auto stage_units = [&](int kb, int first, int n, int slot, int bar_index) {
+    if (lane == 0) {
+      const int ngroups = min(2, p.G - 2 * kb);
+      const uint32_t bar = smem_u32(&bars[bar_index]);
+      mbar_expect_tx(bar, (uint32_t)(ngroups * 3 * n * kPlaneTile));
+      for (int i = 0; i < ngroups * 3; ++i) {
+        const uint8_t* src = p.planes + (((size_t)(2 * kb) * 3 + i) * p.O + (size_t)first * kUnitRows) * 16;
+        bulk_g2s(stage_u32 + (uint32_t)((i * S + slot) * kPlaneTile), src, (uint32_t)(n * kPlaneTile), bar);
+      }
+    }
+  };
+
+  // Lane rotation (byte, half, word): at every step the 32 lanes hit 32 different tables.
+  const int rb = lane & 3, rh = (lane >> 2) & 1, rw = (lane >> 3) & 3;
+  uint32_t rot[4];
+#pragma unroll
+  for (int b = 0; b < 4; ++b) rot[b] = (uint32_t)((8 * ((b + rb) & 3) - Geom::kStrideLog) & 31);
+  constexpr uint32_t kEntryMask = 0xffu << Geom::kStrideLog;
+
+  uint32_t chunk_parity = 0, slot_parity = 0;
+  bool dead = false;
+  bool first_pass = true;
+
+  int kb, my_first, my_count;
+  share((int)blockIdx.x, kb, my_first, my_count);
+  stage_units(kb, my_first, min(S, my_count), 0, kMaxSlots);  // weights never change: no need to wait
+  FB_MARK(1);
+
+  // Everything below reads activations and writes scratch / outputs of this stream.
+  pdl_wait_prior_grid();
+  FB_MARK(9);
+
+  for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
+    if (!first_pass) {
+      __syncthreads();  // everyone has finished reading the previous tables
+      share(v, kb, my_first, my_count);
+      if (!dead) stage_units(kb, my_first, min(S, my_count), 0, kMaxSlots);
+    }
+    first_pass = false;
+
+    // ---- build the 32 tables of this K block: lane = table, warp = 16 consecutive entries ----
+    float sx_m[M];  // lanes 0..15: sum of group A's activations, lanes 16..31: group B's
+    {
+      const int g = 2 * kb + (lane >> 4);
+      const int kbase = g * 128 + (lane & 15) * 8;
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float v8[8];
+        if (g < p.G) {
+          if (p.perm) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v8[j] = load_act(p.x, p.act_dtype, m * p.K + p.perm[kbase + j]);
+          } else {
+            const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + (size_t)m * p.K + kbase);
+            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v8[j] = 0.f;
+        }
+        // ascending-order subset sums of the low four values ...
+        float lo[16];
+        lo[0] = 0.f;
+#pragma unroll
+        for (int q = 1; q < 16; ++q) {
+          const int top = q >= 8 ? 3 : (q >= 4 ? 2 : (q >= 2 ? 1 : 0));
+          lo[q] = lo[q & ~(1 << top)] + v8[top];
+        }
+        // ... then the high four, still in ascending order; this warp owns the sixteen
+        // entries whose high nibble is the warp number.
+        unsigned char* const column = lut + m * 128 + lane * 4;
+        {
+          const int hi = warp;
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            float s = lo[q];
+            if (hi & 1) s += v8[4];
+            if (hi & 2) s += v8[5];
+            if (hi & 4) s += v8[6];
+            if (hi & 8) s += v8[7];
+            *reinterpret_cast<float*>(column + ((size_t)(hi * 16 + q) << Geom::kStrideLog)) = s;
+          }
+        }
+        float total = 0.f;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) total += v8[b];
+#pragma unroll
+        for (int d = 8; d >= 1; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+        sx_m[m] = total;
+      }
+    }
+    FB_MARK(2);
+    __syncthreads();
+    FB_MARK(3);
+
+    // ---- this warp's units ----
+    const int gA = 2 * kb, gB = 2 * kb + 1;
+    const bool hasB = gB < p.G;
+    const int chunk = min(S, my_count);
+    for (int i = 0; i < my_count; ++i) {
+      const int slot = i % S;
+      const int ru = my_first + i;
+      const int row = ru * kUnitRows + lane;
+      // scale / zero loads first: their latency overlaps the wait below
+      const unsigned short sbitsA = p.scales[(size_t)gA * p.O + row];
+      const unsigned short sbitsB = hasB ? p.scales[(size_t)gB * p.O + row] : (unsigned short)0;
+      float zcA = 0.f, zcB = 0.f;
+      if (p.zeros) {
+        zcA = 4.f - (float)p.zeros[(size_t)gA * p.O + row];
+        if (hasB) zcB = 4.f - (float)p.zeros[(size_t)gB * p.O + row];
+      }
+
+      bool ok = false;
+      if (!dead) {
+        if (i < chunk)
+          ok = mbar_wait_bounded(smem_u32(&bars[kMaxSlots]), chunk_parity);
+        else
+          ok = mbar_wait_bounded(smem_u32(&bars[slot]), (slot_parity >> slot) & 1u);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && !dead) {
+        dead = true;
+        if (lane == 0) atomicExch(p.status, 1u);
+      }
+      if (i >= chunk) slot_parity ^= 1u << slot;
+      FB_MARK(4);
+
+      float acc[M][2][3];
+      float corr[M][2];
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh) {
+          corr[m][jh] = 0.f;
+#pragma unroll
+          for (int pl = 0; pl < 3; ++pl) acc[m][jh][pl] = 0.f;
+        }
+
+      if (!dead) {
+        const unsigned char* const buf = stage_base + slot * kPlaneTile + lane * 16;
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh) {
+          const int h = jh ^ rh;
+#pragma unroll
+          for (int jw = 0; jw < 4; ++jw) {
+            const int ws = (jw + rw) & 3;
+            const unsigned char* wp = buf + (h * 3) * S * kPlaneTile + ws * 4;
+            uint32_t w[3];
+#pragma unroll
+            for (int pl = 0; pl < 3; ++pl) w[pl] = *reinterpret_cast<const uint32_t*>(wp + pl * S * kPlaneTile);
+            uint32_t plus3 = 0, minus3 = 0;
+            if (CORRECT) {
+              plus3 = w[0] & w[1] & ~w[2];   // code 7 (stored high plane is inverted)
+              minus3 = w[0] & ~w[1] & w[2];  // code 1
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const uint32_t xoff = (uint32_t)(64 * h + 16 * ws + 4 * ((b + rb) & 3));
+#pragma unroll
+              for (int pl = 0; pl < 3; ++pl) {
+                const uint32_t a = (__funnelshift_r(w[pl], w[pl], rot[b]) & kEntryMask) | xoff;
+#pragma unroll
+                for (int m = 0; m < M; ++m) acc[m][jh][pl] += *reinterpret_cast<const float*>(lut + m * 128 + a);
+              }
+              if (CORRECT) {
+                const uint32_t ap = (__funnelshift_r(plus3, plus3, rot[b]) & kEntryMask) | xoff;
+                const uint32_t am = (__funnelshift_r(minus3, minus3, rot[b]) & kEntryMask) | xoff;
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+                  corr[m][jh] += *reinterpret_cast<const float*>(lut + m * 128 + ap) - *reinterpret_cast<const float*>(lut + m * 128 + am);
+              }
+            }
+          }
+        }
+      }
+      FB_MARK(5);
+
+      // all lanes are done with the staged bytes: refill the slot with a later unit
+      __syncwarp();
+      if (!dead && i + S < my_count) stage_units(kb, my_first + i + S, 1, slot, slot);
+
+      if (!dead) {
+        const float sA = bits_to_float(sbitsA, p.scale_dtype);
+        const float sB = bits_to_float(sbitsB, p.scale_dtype);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float first = acc[m][0][0] + 2.f * acc[m][0][1] - 4.f * acc[m][0][2];
+          const float second = acc[m][1][0] + 2.f * acc[m][1][1] - 4.f * acc[m][1][2];
+          float dA = rh ? second : first, dB = rh ? first : second;
+          if (p.zeros) {
+            dA += zcA * __shfl_sync(0xffffffffu, sx_m[m], 0);
+            dB += zcB * __shfl_sync(0xffffffffu, sx_m[m], 16);
+          }
+          float vA = dA * sA, vB = dB * sB;
+          if (CORRECT) {
+            // rounding of scale*(+/-3) in the scale's dtype: the only inexact products
+            const float cA = rh ? corr[m][1] : corr[m][0], cB = rh ? corr[m][0] : corr[m][1];
+            const float r3A = p.scale_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(3.f * sA))
+                                                       : __half2float(__float2half_rn(3.f * sA));
+            const float r3B = p.scale_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(3.f * sB))
+                                                       : __half2float(__float2half_rn(3.f * sB));
+            vA += cA * (r3A - 3.f * sA);
+            vB += cB * (r3B - 3.f * sB);
+          }
+          if (p.group_partials) {
+            float* ws_out = reinterpret_cast<float*>(p.out);
+            ws_out[(size_t)gA * p.O + row] = vA;
+            if (hasB) ws_out[(size_t)gB * p.O + row] = vB;
+          } else if (p.nKB == 1) {
+            store_act(p.out, p.act_dtype, m * p.O + row, vA + vB);
+          } else {
+            p.partials[((size_t)kb * M + m) * p.O + row] = vA + vB;
+          }
+        }
+      }
+    }
+    chunk_parity ^= 1u;
+  }
+
+  // ---- split-K hand-over, once per warp so that its global round trips are not paid per
+  // unit: lane i announces the warp's i-th unit with one release/acquire ticket increment;
+  // whoever draws the last ticket of a row unit sums the partials in ascending K order.
+  FB_MARK(6);
+  if (p.nKB > 1 && !p.group_partials && !dead) {
+    __syncwarp();  // orders every lane's partial stores before the releases below
+    for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
+      share(v, kb, my_first, my_count);
+      for (int base = 0; base < my_count; base += 32) {
+        const int count = min(32, my_count - base);
+        const int my_ru = lane < count ? my_first + base + lane : -1;
+        unsigned prior = 0;
+        if (my_ru >= 0)
+          asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
+        __syncwarp();
+        FB_MARK(7);
+        // Units whose last ticket this warp drew are reduced four at a time so that their
+        // L2 round trips overlap; each row's partials are still summed in ascending K order.
+        const unsigned mine = __ballot_sync(0xffffffffu, my_ru >= 0 && prior == (unsigned)p.nKB - 1u);
+        unsigned todo = mine;
+        while (todo) {
+          int rows[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            if (todo) {
+              const int j = __ffs(todo) - 1;
+              todo &= todo - 1;
+              rows[t] = (my_first + base + j) * kUnitRows + lane;
+            } else {
+              rows[t] = -1;
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            float total[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+            for (int k2 = 0; k2 < p.nKB; ++k2) {
+              float part[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t)
+                part[t] = rows[t] >= 0 ? __ldcg(&p.partials[((size_t)k2 * M + m) * p.O + rows[t]]) : 0.f;
+#pragma unroll
+              for (int t = 0; t < 4; ++t) total[t] += part[t];
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              if (rows[t] >= 0) store_act(p.out, p.act_dtype, m * p.O + rows[t], total[t]);
+          }
+        }
+        if (my_ru >= 0 && prior == (unsigned)p.nKB - 1u) p.tickets[my_ru] = 0u;
+      }
+    }
+  }
+  FB_MARK(8);
+}
+
+struct Plan {
+  int grid, slots, ctas_per_kb;
+  size_t smem;
+};
+
+size_t lut_bytes(int m) { return (size_t)32768 << (m == 1 ? 0 : (m == 2 ? 1 : 2)); }
+
+Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
+  Plan plan;
+  int c = info.sm_count / nKB;
+  if (c < 1) c = 1;
+  if (c > nRU) c = nRU;
+  plan.ctas_per_kb = c;
+  const int nV = nKB * c;
+  plan.grid = nV < info.sm_count ? nV : info.sm_count;
+  const int per_cta = (nRU + c - 1) / c;
+  const int per_warp = (per_cta + kWarps - 1) / kWarps;
+  // Up to three staged units per warp keeps a CTA near 104 KB for M = 1, so that a CTA of
+  // the next kernel in the stream can become resident (and prefetch) beside it.
+  int slots = per_warp < 3 ? per_warp : 3;
+  if (slots < 1) slots = 1;
+  plan.slots = slots;
+  plan.smem = lut_bytes(m) + (size_t)kWarps * slots * kUnitBytes + (size_t)kWarps * (kMaxSlots + 1) * 8;
+  return plan;
+}
+
+template <int M, bool CORRECT>
+int launch(const W3Params& p, const Plan& plan, int max_smem, bool pdl, cudaStream_t stream) {
+  // Raising the dynamic shared memory limit is a per-device, per-kernel setting; do it once.
+  static std::mutex lock;
+  static bool ready[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    if (!ready[device]) {
+      cudaError_t err = cudaFuncSetAttribute(w3_gemv_kernel<M, CORRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+      if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(w3_gemv_kernel)");
+      ready[device] = true;
+    }
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(plan.grid);
+  config.blockDim = dim3(kWarps * 32);
+  config.dynamicSmemBytes = plan.smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl ? 1 : 0;
+  cudaError_t err = cudaLaunchKernelEx(&config, w3_gemv_kernel<M, CORRECT>, p);
+  if (err != cudaSuccess) return cuda_fail(err, "w3_gemv_kernel launch");
+  return FB_OK;
+}
+
+// Scratch layout, identical for every problem size so that one scratch can serve calls of
+// different shapes: [0,256) status word; [256,16384) one ticket per 32-row unit (at most
+// 2048); partials from byte 16384.  Tickets are zero between calls.
+constexpr size_t kTicketsOffset = 256;
+constexpr size_t kPartialsOffset = 16384;
+
+size_t partial_bytes(int m, int O, int K) {
+  const int nKB = (K / 128 + 1) / 2;
+  return nKB > 1 ? (size_t)nKB * m * O * sizeof(float) : 0;
+}
+
+}  // namespace
+
+extern "C" size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_features) {
+  if (m < 1 || m > kMaxM || out_features < 1 || in_features < 128) return 0;
+  return kPartialsOffset + partial_bytes(m, out_features, in_features);
+}
+
+extern "C" int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales,
+                          int scale_dtype, const uint8_t* zeros, const int16_t* perm, void* out,
+                          int out_features, int in_features, void* scratch, size_t scratch_bytes,
+                          unsigned flags, fb_stream_t stream) {
+  const int O = out_features, K = in_features;
+  const bool group_partials = (flags & FB_W3_GROUP_PARTIALS) != 0;
+  if (!x || !planes || !scales || !out) return fail(FB_EINVAL, "fb_w3_gemv: x, planes, scales and out must be non-null");
+  if ((act_dtype != FB_F16 && act_dtype != FB_BF16) || (scale_dtype != FB_F16 && scale_dtype != FB_BF16))
+    return fail(FB_EINVAL, "fb_w3_gemv: dtype tags must be FB_F16 or FB_BF16");
+  if (m < 1 || m > kMaxM) return fail(FB_ELIMIT, "fb_w3_gemv: M=%d outside 1..%d", m, kMaxM);
+  if (K < 128 || K % 128 || K / 128 > 255) return fail(FB_ELIMIT, "fb_w3_gemv: K=%d must be a multiple of 128 with at most 255 groups", K);
+  if (O < 32 || O > 65536 || O % 32) return fail(FB_ELIMIT, "fb_w3_gemv: O=%d must be a multiple of 32 in 32..65536", O);
+  if (!aligned(planes, 16)) return fail(FB_EINVAL, "fb_w3_gemv: planes must be 16-byte aligned");
+  if (!aligned(x, 16) && !perm) return fail(FB_EINVAL, "fb_w3_gemv: x must be 16-byte aligned");
+  if (!aligned(scales, 2) || !aligned(out, group_partials ? 4 : 2) || !aligned(x, 2) || (perm && !aligned(perm, 2)))
+    return fail(FB_EINVAL, "fb_w3_gemv: 16-bit tensors must be 2-byte aligned");
+  if ((flags & FB_W3_DECODED_BF16) && zeros) return fail(FB_EINVAL, "fb_w3_gemv: the rounding correction needs the constant zero point (zeros == NULL)");
+  if (flags & ~(FB_W3_DECODED_BF16 | FB_W3_NO_PDL | FB_W3_GROUP_PARTIALS)) return fail(FB_EINVAL, "fb_w3_gemv: unknown flag bits 0x%x", flags);
+  if (group_partials && m != 1) return fail(FB_EINVAL, "fb_w3_gemv: group partials need M = 1");
+  const int G = K / 128;
+  const size_t out_bytes = group_partials ? (size_t)(K / 128) * O * 4 : (size_t)m * O * 2, x_bytes = (size_t)m * K * 2;
+  if (overlaps(out, out_bytes, x, x_bytes) || overlaps(out, out_bytes, planes, (size_t)G * 3 * O * 16) ||
+      overlaps(out, out_bytes, scales, (size_t)G * O * 2))
+    return fail(FB_EALIAS, "fb_w3_gemv: out overlaps an input");
+  const size_t need = fb_w3_gemv_scratch_bytes(m, O, K);
+  if (!scratch || scratch_bytes < need) return fail(FB_ESCRATCH, "fb_w3_gemv: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+  if (!aligned(scratch, 256)) return fail(FB_EINVAL, "fb_w3_gemv: scratch must be 256-byte aligned");
+  if (overlaps(scratch, need, out, out_bytes) || overlaps(scratch, need, x, x_bytes))
+    return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps x or out");
+
+  const DeviceInfo* info = device_info();
+  if (!info) return FB_ECUDA;
+
+  W3Params p;
+  p.x = x;
+  p.planes = planes;
+  p.scales = static_cast<const unsigned short*>(scales);
+  p.zeros = zeros;
+  p.perm = perm;
+  p.out = out;
+  p.O = O;
+  p.K = K;
+  p.G = G;
+  p.nKB = (G + 1) / 2;
+  p.nRU = O / kUnitRows;
+  p.act_dtype = act_dtype;
+  p.scale_dtype = scale_dtype;
+  unsigned char* base = static_cast<unsigned char*>(scratch);
+  p.status = reinterpret_cast<unsigned*>(base);
+  p.tickets = reinterpret_cast<unsigned*>(base + kTicketsOffset);
+  p.partials = reinterpret_cast<float*>(base + kPartialsOffset);
+  const Plan plan = make_plan(m, p.nKB, p.nRU, *info);
+  p.slots = plan.slots;
+  p.ctas_per_kb = plan.ctas_per_kb;
+  p.group_partials = group_partials ? 1 : 0;
+  if (plan.smem > (size_t)info->max_smem_optin) return fail(FB_ELIMIT, "fb_w3_gemv: plan needs %zu bytes of shared memory", plan.smem);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool correct = (flags & FB_W3_DECODED_BF16) != 0;
+  const bool pdl = (flags & FB_W3_NO_PDL) == 0;
+#define FB_DISPATCH(MM)                                                                    \
+  case MM:                                                                                 \
+    return correct ? launch<MM, true>(p, plan, info->max_smem_optin, pdl, s) : launch<MM, false>(p, plan, info->max_smem_optin, pdl, s);
+  switch (m) {
+    FB_DISPATCH(1)
+    FB_DISPATCH(2)
+    FB_DISPATCH(3)
+    FB_DISPATCH(4)
+  }
+#undef FB_DISPATCH
+  return fail(FB_ELIMIT, "fb_w3_gemv: unsupported M");
+}
+
+namespace {
+__global__ void w3_finish_kernel(const float* __restrict__ partials, int splits, int O, void* out, int dtype) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= O) return;
+  float total = 0.f;
+  for (int s = 0; s < splits; ++s) total += partials[(size_t)s * O + o];
+  fb::store_act(out, dtype, o, total);
+}
+}  // namespace
+
+extern "C" int fb_w3_finish(const float* partials, int splits, int out_features, void* out, int out_dtype,
+                            fb_stream_t stream) {
+  using namespace fb;
+  if (!partials || !out) return fail(FB_EINVAL, "fb_w3_finish: null pointer");
+  if (out_dtype != FB_F16 && out_dtype != FB_BF16) return fail(FB_EINVAL, "fb_w3_finish: out dtype must be FB_F16 or FB_BF16");
+  if (splits < 1 || splits > 255 || out_features < 1 || out_features > 65536) return fail(FB_ELIMIT, "fb_w3_finish: dimensions outside bounds");
+  if (overlaps(out, (size_t)out_features * 2, partials, (size_t)splits * out_features * 4)) return fail(FB_EALIAS, "fb_w3_finish: out overlaps partials");
+  w3_finish_kernel<<<(out_features + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(partials, splits, out_features, out, out_dtype);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return cuda_fail(err, "w3_finish_kernel launch");
+  return FB_OK;
+}
