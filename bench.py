@@ -1,0 +1,336 @@
+"""Benchmark of the batch-1 packed-Linear decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): all seven Qwen3-8B Linear shapes as W3 group-128
+GEMVs at M=1, for 36 layers of DISTINCT synthetic weights (2.8 GB, far larger than L2, so
+every weight byte comes from HBM), value distributions as configs[0] states (uniform codes,
+fp16 scales U(0.005,0.02), zero points in {3,4}, x ~ N(0,1) bf16).  One step = one pass over
+all 252 GEMVs = the Linear work of one decoded token, replayed from a CUDA graph.
+
+Metric: HBM GB/s on the algorithmic bytes (stored planes + scales + zero points + x + y).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = (  # name, out_features, in_features (Qwen3-8B)
+    ("q_proj", 4096, 4096), ("k_proj", 1024, 4096), ("v_proj", 1024, 4096), ("o_proj", 4096, 4096),
+    ("gate_proj", 12288, 4096), ("up_proj", 12288, 4096), ("down_proj", 4096, 12288),
+)
+LAYERS = 36
+NOMINAL_HBM_GBS = 8000.0
+METRIC = "W3 GEMV HBM GB/s (% of 8 TB/s) per Qwen3-8B shape; batch-1 decode tokens/s"
+
+
+def gemv_bytes(o: int, k: int, zeros: bool = True) -> int:
+    """Algorithmic bytes of one M=1 GEMV: planes, fp16 scales, uint8 zero points, x and y."""
+    g = k // 128
+    return 3 * o * k // 8 + 2 * g * o + (g * o if zeros else 0) + 2 * k + 2 * o
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+
+    def summary(self):
+        good = [r for r in self.rows if len(r) == 6 and r[0].isdigit()]
+        if not good:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        mhz = sorted(int(r[0]) for r in good)
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in good)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(good[0][1]), "reasons": reasons, "samples": len(good)}
+
+
+def synthetic_layout(torch, o, k, device, gen):
+    g = k // 128
+    return {
+        "planes": torch.randint(0, 256, (g, 3, o, 16), dtype=torch.uint8, device=device, generator=gen),
+        "scales": (torch.rand(g, o, device=device, generator=gen) * 0.015 + 0.005).half(),
+        "zeros": torch.randint(3, 5, (g, o), dtype=torch.uint8, device=device, generator=gen),
+        "perm": torch.arange(k, dtype=torch.int16, device=device),
+    }
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+
+    from marlin_style_fluxbin_b200.w3_lut_deployment import PackedW3Linear
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    gen = torch.Generator(device=device).manual_seed(20260916 + rank)
+    with torch.inference_mode():
+        modules = []  # LAYERS x 7 bound modules, distinct weights
+        for _ in range(LAYERS):
+            for name, o, k in SHAPES:
+                module = PackedW3Linear(synthetic_layout(torch, o, k, device, gen), row_tile=1024 if max(o, k) > 4096 else 256)
+                module.bind_prepared_decode(torch.bfloat16)
+                modules.append((name, module))
+        x_dev = {k: torch.randn(1, 1, k, device=device, generator=gen).bfloat16() for k in (4096, 12288)}
+        x_host = {k: v.cpu().pin_memory() for k, v in x_dev.items()}
+        last = [m for _, m in modules[-len(SHAPES):]]
+        out_host = [torch.empty(1, 1, m.out_features, dtype=torch.bfloat16).pin_memory() for m in last]
+
+        def one_pass():
+            for _, module in modules:
+                module(x_dev[module.in_features])
+
+        stream = torch.cuda.Stream(device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                one_pass()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                one_pass()
+
+            def e2e_step():
+                for k in x_dev:
+                    x_dev[k].copy_(x_host[k], non_blocking=True)
+                graph.replay()
+                for host, module in zip(out_host, last):
+                    host.copy_(module._decode_output.view(1, 1, -1), non_blocking=True)
+                stream.synchronize()
+
+            def barrier():
+                stream.synchronize()
+                if world > 1:
+                    torch.distributed.barrier()
+                stream.synchronize()
+
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            barrier()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(local_rank) as clocks:
+                begin.record(stream)
+                for _ in range(args.steps):
+                    graph.replay()
+                end.record(stream)
+                barrier()
+            step_ms = begin.elapsed_time(end) / args.steps
+
+            # per-shape: the same protocol on 36 distinct weights of one shape
+            per_shape = {}
+            for name, o, k in SHAPES:
+                if name in ("v_proj", "up_proj", "o_proj"):
+                    continue
+                mods = [m for n, m in modules if n == name]
+                shape_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(shape_graph, stream=stream):
+                    for m in mods:
+                        m(x_dev[k])
+                for _ in range(3):
+                    shape_graph.replay()
+                stream.synchronize()
+                begin.record(stream)
+                for _ in range(20):
+                    shape_graph.replay()
+                end.record(stream)
+                stream.synchronize()
+                us = begin.elapsed_time(end) * 1000 / (20 * len(mods))
+                gbs = gemv_bytes(o, k) / us / 1e3
+                per_shape[f"{o}x{k}"] = {"us": round(us, 3), "gbs": round(gbs, 1), "bytes": gemv_bytes(o, k)}
+
+            for _ in range(3):
+                e2e_step()
+            barrier()
+            t0 = time.perf_counter()
+            begin.record(stream)
+            for _ in range(args.steps):
+                e2e_step()
+            end.record(stream)
+            barrier()
+            e2e_ms = max(begin.elapsed_time(end), (time.perf_counter() - t0) * 1e3) / args.steps
+
+    if world > 1:
+        t = torch.tensor([step_ms, e2e_ms], device=device, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        step_ms, e2e_ms = float(t[0]), float(t[1])
+    step_bytes = LAYERS * sum(gemv_bytes(o, k) for _, o, k in SHAPES)
+    return {
+        "step_ms": step_ms, "e2e_ms": e2e_ms, "step_bytes": step_bytes, "per_shape": per_shape,
+        "clocks": clocks.summary(), "launches": len(modules) * args.steps,
+        "h2d": sum(v.numel() * 2 for v in x_host.values()), "d2h": sum(v.numel() * 2 for v in out_host),
+    }
+
+
+def cpu_reference(steps: int, warmup: int):
+    """The reference's CPU path (dequantise, then fp32 matmul) restated in the oracle, timed
+    on the host cores over ONE layer's seven Linears per step (a bounded sample)."""
+    import numpy as np
+
+    from oracle import oracle as orc
+
+    rng = np.random.default_rng(20260916)
+    layer = []
+    t_dequant = 0.0
+    for _, o, k in SHAPES:
+        g = k // 128
+        planes = rng.integers(0, 256, (g, 3, o, 16), dtype=np.uint8)
+        scales = (rng.random((g, o), dtype=np.float32) * 0.015 + 0.005).astype(np.float16).view(np.uint16)
+        zeros = rng.integers(3, 5, (g, o), dtype=np.uint8)
+        t0 = time.perf_counter()
+        dense = orc.w3_dequant(planes, scales, orc.F16, zeros, None, orc.F32)
+        t_dequant += time.perf_counter() - t0
+        layer.append((dense, rng.standard_normal((1, k), dtype=np.float32)))
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        for dense, x in layer:
+            orc.dense_gemv_f32(dense, x)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    step_s = sum(times) / len(times)
+    nbytes = sum(gemv_bytes(o, k) for _, o, k in SHAPES)
+    return {"value": nbytes / step_s / 1e9, "cores": orc.num_threads(), "step_ms": step_s * 1e3,
+            "dequant_s_per_layer": t_dequant,
+            "sample": (f"one layer (7 Linears, {nbytes} packed bytes) per step: fp32 matmul on weights dequantised once "
+                       f"outside the timer ({t_dequant:.2f} s per layer when redone every call)")}
+
+
+def small_case(args):
+    """A few launches of one shape on distinct weights (larger than L2 together): the
+    small, self-ending program that profiler captures are taken on."""
+    import torch
+
+    from marlin_style_fluxbin_b200.w3_lut_deployment import w3_lut_m1_out, workspace_shape
+
+    o, k = (int(v) for v in args.case.lower().split("x"))
+    device = torch.device("cuda", 0)
+    gen = torch.Generator(device=device).manual_seed(1)
+    layouts = [synthetic_layout(torch, o, k, device, gen) for _ in range(args.copies)]
+    x = torch.randn(1, k, device=device, generator=gen).bfloat16()
+    out = torch.empty(1, o, device=device, dtype=torch.bfloat16)
+    workspace = torch.empty(workspace_shape(o, k), device=device)
+    for _ in range(2):
+        for layout in layouts:
+            w3_lut_m1_out(x, layout, out, workspace, row_tile=256)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "copies": args.copies, "launches": 2 * args.copies,
+                      "bytes_per_launch": gemv_bytes(o, k), "checksum": float(out.float().abs().sum())}))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--case", default=None, metavar="OxK",
+                        help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
+    parser.add_argument("--copies", type=int, default=8)
+    args = parser.parse_args()
+    if args.case:
+        return small_case(args)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {
+        "workload": "qwen3-8b all seven Linear shapes, W3 g128 GEMV, M=1, 36 layers of distinct weights (configs[1])",
+        "shapes": [f"{o}x{k}" for _, o, k in SHAPES], "layers": LAYERS, "gemvs_per_step": LAYERS * len(SHAPES),
+        "cache": "inputs larger than L2 (2.8 GB of weights per pass), no flush needed",
+        "zero_points": "uint8 per (group,row), counted at their stored size", "parallelism": f"replicas x{world}",
+    }
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        ref = cpu_reference(args.steps, min(args.warmup, 1))
+        line = {
+            "impl": "reference", "metric": METRIC, "value": round(ref["value"], 3), "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ref["step_ms"], 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": round(ref["value"], 3), "unit": "GB/s", "cores": ref["cores"], "kind": "port", "sample": ref["sample"]},
+            "e2e": {"value": round(ref["value"], 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line))
+        return
+
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the packed kernels have no CPU path")
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    result = run_ours(args, rank, world, local_rank)
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        total_bytes = result["step_bytes"] * world
+        value = total_bytes / (result["step_ms"] * 1e-3) / 1e9
+        per_gpu = value / world
+        e2e = total_bytes / (result["e2e_ms"] * 1e-3) / 1e9
+        for entry in result["per_shape"].values():
+            entry["pct_of_8TBps"] = round(100 * entry["gbs"] / NOMINAL_HBM_GBS, 1)
+            entry["pct_of_measured"] = round(100 * entry["gbs"] / peak, 1)
+        cpu = cpu_reference(3, 1) if world == 1 else None
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(result["step_ms"], 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "pct_of_8TBps": round(100 * per_gpu / NOMINAL_HBM_GBS, 1),
+            "linear_tokens_per_s": round(world * 1e3 / result["step_ms"], 1),
+            "per_shape": result["per_shape"], "clocks": result["clocks"],
+            "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": result["h2d"], "d2h_bytes_per_step": result["d2h"]},
+            "gpu_launches": result["launches"],
+            "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(per_gpu / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "w3_gemv_kernel<1,false>", "bytes_per_launch_avg": result["step_bytes"] // (LAYERS * len(SHAPES))},
+        }
+        traffic = ROOT / "profiles" / "w3_gemv_traffic.json"
+        if traffic.exists():
+            line["roofline"]["traffic"] = json.loads(traffic.read_text()).get("dram_bytes_per_launch_avg")
+        if cpu is not None:
+            line["cpu_baseline"] = {"value": round(cpu["value"], 3), "unit": "GB/s", "cores": cpu["cores"], "kind": "port", "sample": cpu["sample"]}
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -58,7 +58,8 @@ using namespace fb;
 constexpr int kUnitRows = 32;
 constexpr int kPlaneTile = kUnitRows * 16;  // 512 B: one plane of one group for a unit
 constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
-constexpr int kWarps = 16;
+constexpr int kWarps = 8;
+constexpr int kCtasPerSm = 2;
 constexpr int kMaxSlots = 4;
 constexpr int kMaxM = 4;
 
@@ -91,7 +92,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <int M, bool CORRECT>
-__global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const W3Params p) {
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const W3Params p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   using Geom = LutGeom<M>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const W3Params 
     }
     first_pass = false;
 
-    // ---- build the 32 tables of this K block: lane = table, warp = 16 consecutive entries ----
+    // ---- build the 32 tables of this K block: lane = table, warp = 32 consecutive entries ----
     float sx_m[M];  // lanes 0..15: sum of group A's activations, lanes 16..31: group B's
     {
       const int g = 2 * kb + (lane >> 4);
@@ -197,11 +198,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const W3Params 
           const int top = q >= 8 ? 3 : (q >= 4 ? 2 : (q >= 2 ? 1 : 0));
           lo[q] = lo[q & ~(1 << top)] + v8[top];
         }
-        // ... then the high four, still in ascending order; this warp owns the sixteen
-        // entries whose high nibble is the warp number.
+        // ... then the high four, still in ascending order; this warp owns the entries
+        // whose high nibble is 2*warp or 2*warp+1.
         unsigned char* const column = lut + m * 128 + lane * 4;
-        {
-          const int hi = warp;
+#pragma unroll
+        for (int hh = 0; hh < 16 / kWarps; ++hh) {
+          const int hi = warp * (16 / kWarps) + hh;
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
             float s = lo[q];
@@ -413,12 +415,12 @@ size_t lut_bytes(int m) { return (size_t)32768 << (m == 1 ? 0 : (m == 2 ? 1 : 2)
 
 Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   Plan plan;
-  int c = info.sm_count / nKB;
+  int c = kCtasPerSm * info.sm_count / nKB;
   if (c < 1) c = 1;
   if (c > nRU) c = nRU;
   plan.ctas_per_kb = c;
   const int nV = nKB * c;
-  plan.grid = nV < info.sm_count ? nV : info.sm_count;
+  plan.grid = nV < kCtasPerSm * info.sm_count ? nV : kCtasPerSm * info.sm_count;
   const int per_cta = (nRU + c - 1) / c;
   const int per_warp = (per_cta + kWarps - 1) / kWarps;
   // Up to three staged units per warp keeps a CTA near 104 KB for M = 1, so that a CTA of
