@@ -90,6 +90,23 @@ int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const
 int fb_w3_finish(const float* partials, int splits, int out_features, void* out, int out_dtype,
                  fb_stream_t stream);
 
+/*
+ * fb_w3_gemv without a scratch argument, for callers that cannot allocate device memory where
+ * they call this library (all memory already handed to a pool, a framework allocator that must
+ * not be bypassed, a CUDA graph capture in progress).  The split-K scratch is a fixed array of
+ * FB_W3_STATIC_SCRATCH_BYTES inside the library, resident on every GPU that loads it.
+ * Same arguments and results as fb_w3_gemv; problems whose scratch need
+ * (fb_w3_gemv_scratch_bytes) exceeds that size are rejected with FB_ELIMIT.  This call itself
+ * allocates nothing.  The first call on a device looks up the array's device address; make that
+ * first call before any stream capture.  All calls on a device share the one array: the control
+ * block is cleared on the stream at every call, and two calls that can overlap on the GPU race.
+ * It has no counterpart in the reference, whose callers always pass a workspace.
+ */
+#define FB_W3_STATIC_SCRATCH_BYTES (4u << 20)
+int fb_w3_gemv_static(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales,
+                      int scale_dtype, const uint8_t* zeros, const int16_t* perm, void* out,
+                      int out_features, int in_features, unsigned flags, fb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

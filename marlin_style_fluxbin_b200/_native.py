@@ -48,6 +48,8 @@ def library() -> ctypes.CDLL:
         ]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_w3_gemv_static.restype = ctypes.c_int
+        lib.fb_w3_gemv_static.argtypes = lib.fb_w3_gemv.argtypes[:11] + [ctypes.c_uint, ctypes.c_void_p]
         _lib = lib
     return _lib
 
@@ -126,3 +128,22 @@ def w3_finish(partials, out) -> None:
     with torch.cuda.device(out.device):
         check(library().fb_w3_finish(ptr(partials), splits, o, ptr(out), dtype_tag(out.dtype),
                                      stream_handle(out.device)))
+
+
+FB_W3_STATIC_SCRATCH_BYTES = 4 << 20
+
+
+def w3_gemv_static(x, planes, scales, zeros, perm, out, *, decoded_bf16=False, pdl=True) -> None:
+    """``w3_gemv`` through the entry point that uses the library's built-in scratch.
+
+    For callers that cannot allocate device memory at the call site; nothing is allocated
+    here either.  Rejects problems needing more than ``FB_W3_STATIC_SCRATCH_BYTES`` of
+    scratch.  Calls on one device share that scratch, so they must not overlap on the GPU.
+    """
+    m, k = x.shape
+    o = planes.shape[2]
+    flags = (FB_W3_DECODED_BF16 if decoded_bf16 else 0) | (0 if pdl else FB_W3_NO_PDL)
+    with torch.cuda.device(x.device):
+        check(library().fb_w3_gemv_static(
+            ptr(x), dtype_tag(x.dtype), m, ptr(planes), ptr(scales), dtype_tag(scales.dtype),
+            ptr(zeros), ptr(perm), ptr(out), o, k, flags, stream_handle(x.device)))
