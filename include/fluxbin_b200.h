@@ -91,6 +91,24 @@ int fb_w3_finish(const float* partials, int splits, int out_features, void* out,
                  fb_stream_t stream);
 
 /*
+ * RMSNorm over `rows` vectors of `dim` 16-bit values:
+ *   out = weight * T( x_f32 * rsqrt(mean(x_f32^2) + eps) )   (cast to T before the weight multiply)
+ * x, out [rows, dim] contiguous; weight [dim]; out may alias x.
+ * Replaces the reference's compiled RMSNorm forward (fused_modules.py:30-63).
+ */
+int fb_rmsnorm(const void* x, const void* weight, void* out, int rows, int dim, float eps, int dtype,
+               fb_stream_t stream);
+
+/*
+ * Rotary embedding of one token's q heads [q_heads, head_dim] and k heads [k_heads, head_dim]
+ * with one cos/sin row [head_dim]:  out = T( T(v*cos) + rotate_half(v)*sin ).
+ * q_out / k_out may alias q / k.
+ * Replaces the reference's fused_apply_rotary_pos_emb for a single position (fused_modules.py:66-85).
+ */
+int fb_rope_qk(const void* q, const void* k, const void* cosv, const void* sinv, void* q_out, void* k_out,
+               int q_heads, int k_heads, int head_dim, int dtype, fb_stream_t stream);
+
+/*
  * fb_w3_gemv without a scratch argument, for callers that cannot allocate device memory where
  * they call this library (all memory already handed to a pool, a framework allocator that must
  * not be bypassed, a CUDA graph capture in progress).  The split-K scratch is a fixed array of

@@ -48,6 +48,10 @@ def library() -> ctypes.CDLL:
         ]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_rmsnorm.restype = ctypes.c_int
+        lib.fb_rmsnorm.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_rope_qk.restype = ctypes.c_int
+        lib.fb_rope_qk.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 4 + [ctypes.c_void_p]
         lib.fb_w3_gemv_static.restype = ctypes.c_int
         lib.fb_w3_gemv_static.argtypes = lib.fb_w3_gemv.argtypes[:11] + [ctypes.c_uint, ctypes.c_void_p]
         _lib = lib
@@ -147,3 +151,19 @@ def w3_gemv_static(x, planes, scales, zeros, perm, out, *, decoded_bf16=False, p
         check(library().fb_w3_gemv_static(
             ptr(x), dtype_tag(x.dtype), m, ptr(planes), ptr(scales), dtype_tag(scales.dtype),
             ptr(zeros), ptr(perm), ptr(out), o, k, flags, stream_handle(x.device)))
+
+
+def rmsnorm(x, weight, out, eps: float) -> None:
+    """``out = weight * dtype(x * rsqrt(mean(x^2) + eps))`` over the last dimension of ``x``."""
+    dim = x.shape[-1]
+    with torch.cuda.device(x.device):
+        check(library().fb_rmsnorm(ptr(x), ptr(weight), ptr(out), x.numel() // dim, dim, float(eps),
+                                   dtype_tag(x.dtype), stream_handle(x.device)))
+
+
+def rope_qk(q, k, cos, sin, q_out, k_out) -> None:
+    """Rotary embedding of one position: ``q [Hq,D]``, ``k [Hk,D]`` (any leading unit dims), ``cos/sin [D]``."""
+    dim = q.shape[-1]
+    with torch.cuda.device(q.device):
+        check(library().fb_rope_qk(ptr(q), ptr(k), ptr(cos), ptr(sin), ptr(q_out), ptr(k_out),
+                                   q.numel() // dim, k.numel() // dim, dim, dtype_tag(q.dtype), stream_handle(q.device)))
