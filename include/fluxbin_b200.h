@@ -91,6 +91,36 @@ int fb_w3_finish(const float* partials, int splits, int out_features, void* out,
                  fb_stream_t stream);
 
 /*
+ * Two-base binary-basis GEMV, M = 1, reference hybrid g128-s8 kernel layout (G = K/128):
+ *   codes        uint8 [G,O,2,16] (planar != 0) or [G,O,32] (interleaved, planar == 0)
+ *   rows         f32 [G,O,2]      cols         f32 [G,128,2]
+ *   sparse_codes uint8 [G,O,2,1] (planar) or [G,O,2] (interleaved)
+ *   sparse_rows  f32 [G,O,2]      sparse_cols  f32 [G,8,2]      indices int16 [G,8]
+ * y[o] = sum_g ( r0*d0 + r1*d1 + sr0*s0 + sr1*s1 ), d_b = sum_k sign_b*col_b*x over the group,
+ * s_b the same over the group's 8 refined columns; fp32, groups summed in ascending order.
+ * Any O in 1..65536; scratch as for fb_w3_gemv, sized by fb_bb_gemv_scratch_bytes(O, K, 0).
+ * Replaces the reference's m1_out of the v5 kernels (csrc/m1_v5.cu:132-195); all the
+ * reference's kernel names map to this one entry point.
+ */
+size_t fb_bb_gemv_scratch_bytes(int out_features, int in_features, int global_scales);
+int fb_bb_gemv(const void* x, int act_dtype, const uint8_t* codes, int planar, const float* rows,
+               const float* cols, const uint8_t* sparse_codes, const float* sparse_rows,
+               const float* sparse_cols, const int16_t* indices, void* out, int out_features,
+               int in_features, void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream);
+
+/*
+ * Two-base GEMV with matrix-wide scales:  W = sum_b diag(r_b) B_b diag(c_b) + dense residual
+ * columns.  codes uint8 [G,O,2,16] planar sign bits; row_scales f16 [2,O]; col_scales f16 [2,K];
+ * salient_idx int32 [n] input columns; salient bf16 [O,n] added weights on those columns.
+ * Scratch sized by fb_bb_gemv_scratch_bytes(O, K, 1).  The two-base part follows the
+ * reference's global materialiser (evaluation.py:59-95) with one scale per row and per column.
+ */
+int fb_bb_global_gemv(const void* x, int act_dtype, const uint8_t* codes, const void* row_scales,
+                      const void* col_scales, const int32_t* salient_idx, const void* salient,
+                      int n_salient, void* out, int out_features, int in_features, void* scratch,
+                      size_t scratch_bytes, unsigned flags, fb_stream_t stream);
+
+/*
  * RMSNorm over `rows` vectors of `dim` 16-bit values:
  *   out = weight * T( x_f32 * rsqrt(mean(x_f32^2) + eps) )   (cast to T before the weight multiply)
  * x, out [rows, dim] contiguous; weight [dim]; out may alias x.

@@ -48,6 +48,14 @@ def library() -> ctypes.CDLL:
         ]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_bb_gemv_scratch_bytes.restype = ctypes.c_size_t
+        lib.fb_bb_gemv_scratch_bytes.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        lib.fb_bb_gemv.restype = ctypes.c_int
+        lib.fb_bb_gemv.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 7 + [
+            ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p]
+        lib.fb_bb_global_gemv.restype = ctypes.c_int
+        lib.fb_bb_global_gemv.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_void_p,
+            ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p]
         lib.fb_rmsnorm.restype = ctypes.c_int
         lib.fb_rmsnorm.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
         lib.fb_rope_qk.restype = ctypes.c_int
@@ -167,3 +175,36 @@ def rope_qk(q, k, cos, sin, q_out, k_out) -> None:
     with torch.cuda.device(q.device):
         check(library().fb_rope_qk(ptr(q), ptr(k), ptr(cos), ptr(sin), ptr(q_out), ptr(k_out),
                                    q.numel() // dim, k.numel() // dim, dim, dtype_tag(q.dtype), stream_handle(q.device)))
+
+
+def bb_scratch_bytes(out_features: int, in_features: int, global_scales: bool) -> int:
+    return int(library().fb_bb_gemv_scratch_bytes(out_features, in_features, int(global_scales)))
+
+
+def bb_gemv(x, layout, out, *, pdl=True, scratch=None) -> None:
+    """Two-base GEMV on the reference's kernel layout (dict with the eight layout fields)."""
+    codes = layout["codes"]
+    groups, o = codes.shape[0], codes.shape[1]
+    k = groups * 128
+    if scratch is None:
+        scratch = scratch_for(x.device, bb_scratch_bytes(o, k, False))
+    with torch.cuda.device(x.device):
+        check(library().fb_bb_gemv(
+            ptr(x), dtype_tag(x.dtype), ptr(codes), int(codes.ndim == 4), ptr(layout["rows"]), ptr(layout["columns"]),
+            ptr(layout["sparse_codes"]), ptr(layout["sparse_rows"]), ptr(layout["sparse_columns"]), ptr(layout["indices"]),
+            ptr(out), o, k, ptr(scratch), scratch.numel() * scratch.element_size(), 0 if pdl else FB_W3_NO_PDL,
+            stream_handle(x.device)))
+
+
+def bb_global_gemv(x, codes, row_scales, col_scales, salient_idx, salient, out, *, pdl=True, scratch=None) -> None:
+    """Two-base GEMV with matrix-wide fp16 scales and dense bf16 residual columns."""
+    groups, o = codes.shape[0], codes.shape[1]
+    k = groups * 128
+    if scratch is None:
+        scratch = scratch_for(x.device, bb_scratch_bytes(o, k, True))
+    n_sal = 0 if salient_idx is None else salient_idx.numel()
+    with torch.cuda.device(x.device):
+        check(library().fb_bb_global_gemv(
+            ptr(x), dtype_tag(x.dtype), ptr(codes), ptr(row_scales), ptr(col_scales), ptr(salient_idx), ptr(salient),
+            n_sal, ptr(out), o, k, ptr(scratch), scratch.numel() * scratch.element_size(), 0 if pdl else FB_W3_NO_PDL,
+            stream_handle(x.device)))

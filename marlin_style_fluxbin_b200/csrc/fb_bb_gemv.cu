@@ -1,0 +1,417 @@
+// Two-base binary-basis GEMV, M = 1:  W ~ sum_b diag(row_b) * B_b * diag(col_b), B_b in {-1,+1},
+// packed one bit per weight per base, in groups of 128 inputs.
+//
+// Same skeleton as the W3 GEMV (HBM-bound byte work, see fb_w3_gemv.cu): a K block is ONE group;
+// a CTA holds 32 signed activation tables for it (2 bases x 16 chunks of 8 inputs, entries are
+// sums of +/- x*col in ascending order) laid out entry-major so that the bank of a lookup is the
+// table number; lane = output row; lanes walk the 32 (base, chunk) pairs in a lane-rotated order
+// so that lookups and staged-word reads are bank-conflict free; a warp's rows are one contiguous
+// run of 32-byte code rows, staged by a single bulk copy; split-K over groups is reduced in the
+// kernel through tickets, in ascending group order.
+//
+// Two scale conventions:
+//  * group mode (the reference's hybrid g128-s8 payload, deployment.py:23-27, kernel
+//    csrc/m1_v5.cu:27-104): fp32 row scales per (group,row,base), fp32 column scales per
+//    (group,input,base), plus a two-base refinement on 8 selected columns per group (two more
+//    tables).  Codes may be planar [G,O,2,16] or interleaved [G,O,32].
+//  * global mode (matrix-wide fp16 scales r_b[O], c_b[K], planar codes, and `n_sal` dense bf16
+//    residual columns): the per-base sums are kept separate through the K split and the row
+//    scales and the residual are applied once, by whoever reduces a row.
+#include <mutex>
+
+#include "fb_common.cuh"
+
+namespace {
+
+using namespace fb;
+
+constexpr int kUnitRows = 32;
+constexpr int kUnitBytes = kUnitRows * 32;  // 1 KB of codes per unit
+constexpr int kWarps = 8;
+constexpr int kCtasPerSm = 2;
+constexpr int kMaxSlots = 4;
+constexpr int kLutBytes = 32768;            // 256 entries x 32 tables x 4 B
+constexpr int kSparseLutBytes = 2048;       // 2 tables x 256 entries
+
+struct BBParams {
+  const void* x;
+  const uint8_t* codes;
+  const float* rows;
+  const float* cols;
+  const uint8_t* sparse;
+  const float* srows;
+  const float* scols;
+  const int16_t* indices;
+  const __half* grow;
+  const __half* gcol;
+  const int32_t* sal_idx;
+  const __nv_bfloat16* sal;
+  void* out;
+  float* partials;
+  unsigned* tickets;
+  unsigned* status;
+  int O, K, G, nRU;
+  int act_dtype, interleaved, global_mode, n_sal;
+  int slots, ctas_per_kb;
+};
+
+// one base's eight sign bits out of sixteen interleaved bits (reference csrc/lut8.cuh:10-15)
+__device__ __forceinline__ uint32_t compact_even(uint32_t word) {
+  word &= 0x5555u;
+  word = (word | (word >> 1)) & 0x3333u;
+  word = (word | (word >> 2)) & 0x0f0fu;
+  return (word | (word >> 4)) & 0xffu;
+}
+
+template <bool INTERLEAVED, bool GLOBAL>
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const BBParams p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int S = p.slots;
+  unsigned char* const lut = smem;
+  float* const sparse_lut = reinterpret_cast<float*>(smem + kLutBytes);
+  unsigned char* const stage_base = smem + kLutBytes + kSparseLutBytes + (size_t)warp * S * kUnitBytes;
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + kLutBytes + kSparseLutBytes + (size_t)kWarps * S * kUnitBytes) + warp * (kMaxSlots + 1);
+  const uint32_t stage_u32 = smem_u32(stage_base);
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int nV = p.G * p.ctas_per_kb;
+  if ((int)blockIdx.x >= nV) return;
+
+  if (lane == 0)
+    for (int s = 0; s <= kMaxSlots; ++s) mbar_init(smem_u32(&bars[s]), 1);
+  mbar_init_fence();
+  __syncwarp();
+
+  auto share = [&](int v, int& g, int& first, int& count) {
+    g = v / p.ctas_per_kb;
+    const int slice = v - g * p.ctas_per_kb;
+    const int ua = (int)((long long)slice * p.nRU / p.ctas_per_kb);
+    const int ub = (int)((long long)(slice + 1) * p.nRU / p.ctas_per_kb);
+    const int n = ub - ua, q = n / kWarps, r = n - q * kWarps;
+    first = ua + warp * q + min(warp, r);
+    count = q + (warp < r ? 1 : 0);
+  };
+  // rows past O in the last unit are never copied (the copy is clipped) and never stored
+  auto stage_units = [&](int g, int first, int n, int slot, int bar_index) {
+    if (lane == 0) {
+      const int rows = min(n * kUnitRows, p.O - first * kUnitRows);
+      const uint32_t bar = smem_u32(&bars[bar_index]);
+      mbar_expect_tx(bar, (uint32_t)(rows * 32));
+      bulk_g2s(stage_u32 + (uint32_t)(slot * kUnitBytes), p.codes + ((size_t)g * p.O + (size_t)first * kUnitRows) * 32,
+               (uint32_t)(rows * 32), bar);
+    }
+  };
+
+  const int rb = lane & 3, rw = (lane >> 2) & 3, rh = (lane >> 4) & 1;
+  uint32_t chunk_parity = 0, slot_parity = 0;
+  bool dead = false, first_pass = true;
+  int g, my_first, my_count;
+  share((int)blockIdx.x, g, my_first, my_count);
+  if (my_count > 0) stage_units(g, my_first, min(S, my_count), 0, kMaxSlots);
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
+    if (!first_pass) {
+      __syncthreads();  // everyone has finished reading the previous tables
+      share(v, g, my_first, my_count);
+      if (!dead && my_count > 0) stage_units(g, my_first, min(S, my_count), 0, kMaxSlots);
+    }
+    first_pass = false;
+
+    // ---- 32 signed tables: lane = table (base = lane/16, chunk = lane%16), warp = 32 entries ----
+    {
+      const int base = lane >> 4, chunk = lane & 15;
+      float v8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int kk = g * 128 + chunk * 8 + j;
+        const float xv = load_act(p.x, p.act_dtype, kk);
+        const float cv = GLOBAL ? __half2float(p.gcol[(size_t)base * p.K + kk]) : p.cols[(size_t)kk * 2 + base];
+        v8[j] = __fmul_rn(xv, cv);
+      }
+      unsigned char* const column = lut + lane * 4;
+#pragma unroll 4
+      for (int e = 0; e < 256 / kWarps; ++e) {
+        const int pp = warp * (256 / kWarps) + e;
+        float s = 0.f;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) s += ((pp >> b) & 1) ? v8[b] : -v8[b];
+        *reinterpret_cast<float*>(column + (size_t)pp * 128) = s;
+      }
+      if (!GLOBAL) {
+        // two refinement tables over the group's 8 selected columns; warp w fills entries 32w..32w+31
+        const int pp = warp * 32 + lane;
+#pragma unroll
+        for (int base2 = 0; base2 < 2; ++base2) {
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int idx = p.indices[g * 8 + j];
+            const float sv = __fmul_rn(load_act(p.x, p.act_dtype, g * 128 + idx), p.scols[(size_t)(g * 8 + j) * 2 + base2]);
+            s += ((pp >> j) & 1) ? sv : -sv;
+          }
+          sparse_lut[base2 * 256 + pp] = s;
+        }
+      }
+    }
+    __syncthreads();
+
+    const int chunk_units = min(S, my_count);
+    for (int i = 0; i < my_count; ++i) {
+      const int slot = i % S;
+      const int ru = my_first + i;
+      const int row = ru * kUnitRows + lane;
+      const bool live = row < p.O;
+      float2 rs = make_float2(0.f, 0.f), srs = make_float2(0.f, 0.f);
+      unsigned sp = 0;
+      if (!GLOBAL && live) {
+        rs = *reinterpret_cast<const float2*>(p.rows + ((size_t)g * p.O + row) * 2);
+        srs = *reinterpret_cast<const float2*>(p.srows + ((size_t)g * p.O + row) * 2);
+        sp = *reinterpret_cast<const unsigned short*>(p.sparse + ((size_t)g * p.O + row) * 2);
+      }
+
+      bool ok = false;
+      if (!dead) {
+        if (i < chunk_units)
+          ok = mbar_wait_bounded(smem_u32(&bars[kMaxSlots]), chunk_parity);
+        else
+          ok = mbar_wait_bounded(smem_u32(&bars[slot]), (slot_parity >> slot) & 1u);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && !dead) {
+        dead = true;
+        if (lane == 0) atomicExch(p.status, 1u);
+      }
+      if (i >= chunk_units) slot_parity ^= 1u << slot;
+
+      float d0 = 0.f, d1 = 0.f;
+      if (!dead) {
+        const unsigned char* const buf = stage_base + slot * kUnitBytes + lane * 32;
+        if (!INTERLEAVED) {
+          // row = [base 0: 16 bytes][base 1: 16 bytes]; steps with jh = 0 serve base rh
+          float acc[2] = {0.f, 0.f};
+#pragma unroll
+          for (int jh = 0; jh < 2; ++jh) {
+            const int h = jh ^ rh;
+#pragma unroll
+            for (int jw = 0; jw < 4; ++jw) {
+              const int ws = (jw + rw) & 3;
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(buf + h * 16 + ws * 4);
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const int byte = (b + rb) & 3;
+                const uint32_t entry = (w >> (8 * byte)) & 0xffu;
+                acc[jh] += *reinterpret_cast<const float*>(lut + entry * 128 + (64 * h + 16 * ws + 4 * byte));
+              }
+            }
+          }
+          d0 = rh ? acc[1] : acc[0];
+          d1 = rh ? acc[0] : acc[1];
+        } else {
+          // row = 16 little-endian 16-bit words, word c holds chunk c of both bases, bits
+          // interleaved.  A 32-bit read gives chunks 2w and 2w+1; sub-step b picks
+          // (chunk half, base) = ((b+rb)&1, (b+rb)>>1 & 1).
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int jh = 0; jh < 2; ++jh) {
+#pragma unroll
+            for (int jw = 0; jw < 4; ++jw) {
+              const int w8 = 4 * (jh ^ rh) + ((jw + rw) & 3);
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(buf + w8 * 4);
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const int combo = (b + rb) & 3, half = combo & 1, base = combo >> 1;
+                const uint32_t entry = compact_even((w >> (16 * half)) >> base);
+                acc[b] += *reinterpret_cast<const float*>(lut + entry * 128 + 4 * (16 * base + 2 * w8 + half));
+              }
+            }
+          }
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            if ((((b + rb) & 3) >> 1) == 0) d0 += acc[b]; else d1 += acc[b];
+          }
+        }
+      }
+
+      __syncwarp();
+      if (!dead && i + S < my_count) stage_units(g, my_first + i + S, 1, slot, slot);
+
+      if (!dead && live) {
+        if (GLOBAL) {
+          float* dst = p.partials + ((size_t)g * 2) * p.O + row;
+          dst[0] = d0;
+          dst[p.O] = d1;
+        } else {
+          const uint32_t p0 = INTERLEAVED ? compact_even(sp) : (sp & 0xffu);
+          const uint32_t p1 = INTERLEAVED ? compact_even(sp >> 1) : (sp >> 8);
+          float value = __fmaf_rn(rs.x, d0, 0.f);
+          value = __fmaf_rn(rs.y, d1, value);
+          value = __fmaf_rn(srs.x, sparse_lut[p0], value);
+          value = __fmaf_rn(srs.y, sparse_lut[256 + p1], value);
+          if (p.G == 1)
+            store_act(p.out, p.act_dtype, row, value);
+          else
+            p.partials[(size_t)g * p.O + row] = value;
+        }
+      }
+    }
+    if (my_count > 0) chunk_parity ^= 1u;
+  }
+
+  // ---- split-K hand-over (see fb_w3_gemv.cu): one ticket per 32-row unit, taken once per warp ----
+  if ((GLOBAL || p.G > 1) && !dead) {
+    __syncwarp();
+    for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
+      share(v, g, my_first, my_count);
+      for (int base = 0; base < my_count; base += 32) {
+        const int count = min(32, my_count - base);
+        const int my_ru = lane < count ? my_first + base + lane : -1;
+        unsigned prior = 0;
+        if (my_ru >= 0)
+          asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
+        __syncwarp();
+        unsigned todo = __ballot_sync(0xffffffffu, my_ru >= 0 && prior == (unsigned)p.G - 1u);
+        while (todo) {
+          const int j = __ffs(todo) - 1;
+          todo &= todo - 1;
+          const int row = (my_first + base + j) * kUnitRows + lane;
+          if (row < p.O) {
+            if (GLOBAL) {
+              float t0 = 0.f, t1 = 0.f;
+#pragma unroll 4
+              for (int g2 = 0; g2 < p.G; ++g2) {
+                t0 += __ldcg(p.partials + ((size_t)g2 * 2) * p.O + row);
+                t1 += __ldcg(p.partials + ((size_t)g2 * 2 + 1) * p.O + row);
+              }
+              float value = __fmaf_rn(__half2float(p.grow[row]), t0, 0.f);
+              value = __fmaf_rn(__half2float(p.grow[(size_t)p.O + row]), t1, value);
+              for (int s = 0; s < p.n_sal; ++s)
+                value = __fmaf_rn(__bfloat162float(p.sal[(size_t)row * p.n_sal + s]), load_act(p.x, p.act_dtype, p.sal_idx[s]), value);
+              store_act(p.out, p.act_dtype, row, value);
+            } else {
+              float total = 0.f;
+#pragma unroll 8
+              for (int g2 = 0; g2 < p.G; ++g2) total += __ldcg(p.partials + (size_t)g2 * p.O + row);
+              store_act(p.out, p.act_dtype, row, total);
+            }
+          }
+        }
+        if (my_ru >= 0 && prior == (unsigned)p.G - 1u) p.tickets[my_ru] = 0u;
+      }
+    }
+  }
+}
+
+constexpr size_t kTicketsOffset = 256;
+constexpr size_t kPartialsOffset = 16384;
+
+template <bool INTERLEAVED, bool GLOBAL>
+int launch(const BBParams& p, int grid, size_t smem, int max_smem, bool pdl, cudaStream_t stream) {
+  static std::mutex lock;
+  static bool ready[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    if (!ready[device]) {
+      cudaError_t err = cudaFuncSetAttribute(bb_gemv_kernel<INTERLEAVED, GLOBAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+      if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(bb_gemv_kernel)");
+      ready[device] = true;
+    }
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kWarps * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl ? 1 : 0;
+  cudaError_t err = cudaLaunchKernelEx(&config, bb_gemv_kernel<INTERLEAVED, GLOBAL>, p);
+  if (err != cudaSuccess) return cuda_fail(err, "bb_gemv_kernel launch");
+  return FB_OK;
+}
+
+int run(BBParams& p, void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream, const char* who) {
+  const size_t need = kPartialsOffset + (size_t)p.G * (p.global_mode ? 2 : 1) * p.O * sizeof(float);
+  if (!scratch || scratch_bytes < need) return fail(FB_ESCRATCH, "%s: scratch of %zu bytes needed, %zu given", who, need, scratch_bytes);
+  if (!aligned(scratch, 256)) return fail(FB_EINVAL, "%s: scratch must be 256-byte aligned", who);
+  const DeviceInfo* info = device_info();
+  if (!info) return FB_ECUDA;
+  unsigned char* base = static_cast<unsigned char*>(scratch);
+  p.status = reinterpret_cast<unsigned*>(base);
+  p.tickets = reinterpret_cast<unsigned*>(base + kTicketsOffset);
+  p.partials = reinterpret_cast<float*>(base + kPartialsOffset);
+  p.nRU = (p.O + kUnitRows - 1) / kUnitRows;
+  int c = kCtasPerSm * info->sm_count / p.G;
+  if (c < 1) c = 1;
+  if (c > p.nRU) c = p.nRU;
+  p.ctas_per_kb = c;
+  const int nV = p.G * c;
+  const int grid = nV < kCtasPerSm * info->sm_count ? nV : kCtasPerSm * info->sm_count;
+  const int per_warp = ((p.nRU + c - 1) / c + kWarps - 1) / kWarps;
+  p.slots = per_warp < kMaxSlots ? (per_warp < 1 ? 1 : per_warp) : kMaxSlots;
+  const size_t smem = kLutBytes + kSparseLutBytes + (size_t)kWarps * p.slots * kUnitBytes + (size_t)kWarps * (kMaxSlots + 1) * 8;
+  const bool pdl = (flags & FB_W3_NO_PDL) == 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p.global_mode) return launch<false, true>(p, grid, smem, info->max_smem_optin, pdl, s);
+  if (p.interleaved) return launch<true, false>(p, grid, smem, info->max_smem_optin, pdl, s);
+  return launch<false, false>(p, grid, smem, info->max_smem_optin, pdl, s);
+}
+
+int check_common(const char* who, const void* x, int act_dtype, const uint8_t* codes, void* out, int O, int K) {
+  if (!x || !codes || !out) return fail(FB_EINVAL, "%s: x, codes and out must be non-null", who);
+  if (act_dtype != FB_F16 && act_dtype != FB_BF16) return fail(FB_EINVAL, "%s: activation dtype must be FB_F16 or FB_BF16", who);
+  if (K < 128 || K % 128 || K / 128 > 1024) return fail(FB_ELIMIT, "%s: K=%d must be a multiple of 128 with at most 1024 groups", who, K);
+  if (O < 1 || O > 65536) return fail(FB_ELIMIT, "%s: O=%d outside 1..65536", who, O);
+  if (!aligned(codes, 16)) return fail(FB_EINVAL, "%s: codes must be 16-byte aligned", who);
+  if (overlaps(out, (size_t)O * 2, x, (size_t)K * 2) || overlaps(out, (size_t)O * 2, codes, (size_t)(K / 128) * O * 32))
+    return fail(FB_EALIAS, "%s: out overlaps an input", who);
+  return FB_OK;
+}
+
+}  // namespace
+
+extern "C" size_t fb_bb_gemv_scratch_bytes(int out_features, int in_features, int global_scales) {
+  if (out_features < 1 || in_features < 128) return 0;
+  return kPartialsOffset + (size_t)(in_features / 128) * (global_scales ? 2 : 1) * out_features * sizeof(float);
+}
+
+extern "C" int fb_bb_gemv(const void* x, int act_dtype, const uint8_t* codes, int planar, const float* rows,
+                          const float* cols, const uint8_t* sparse_codes, const float* sparse_rows,
+                          const float* sparse_cols, const int16_t* indices, void* out, int out_features,
+                          int in_features, void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
+  int rc = check_common("fb_bb_gemv", x, act_dtype, codes, out, out_features, in_features);
+  if (rc) return rc;
+  if (!rows || !cols || !sparse_codes || !sparse_rows || !sparse_cols || !indices)
+    return fail(FB_EINVAL, "fb_bb_gemv: every payload tensor must be non-null");
+  if (!aligned(rows, 8) || !aligned(sparse_rows, 8) || !aligned(sparse_codes, 2) || !aligned(cols, 4) || !aligned(sparse_cols, 4))
+    return fail(FB_EINVAL, "fb_bb_gemv: scale tensors are misaligned");
+  if (flags & ~FB_W3_NO_PDL) return fail(FB_EINVAL, "fb_bb_gemv: unknown flag bits 0x%x", flags);
+  BBParams p = {};
+  p.x = x; p.codes = codes; p.rows = rows; p.cols = cols; p.sparse = sparse_codes; p.srows = sparse_rows;
+  p.scols = sparse_cols; p.indices = indices; p.out = out; p.O = out_features; p.K = in_features;
+  p.G = in_features / 128; p.act_dtype = act_dtype; p.interleaved = planar ? 0 : 1; p.global_mode = 0;
+  return run(p, scratch, scratch_bytes, flags, stream, "fb_bb_gemv");
+}
+
+extern "C" int fb_bb_global_gemv(const void* x, int act_dtype, const uint8_t* codes, const void* row_scales,
+                                 const void* col_scales, const int32_t* salient_idx, const void* salient,
+                                 int n_salient, void* out, int out_features, int in_features, void* scratch,
+                                 size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
+  int rc = check_common("fb_bb_global_gemv", x, act_dtype, codes, out, out_features, in_features);
+  if (rc) return rc;
+  if (!row_scales || !col_scales) return fail(FB_EINVAL, "fb_bb_global_gemv: scales must be non-null");
+  if (n_salient < 0 || n_salient > 256 || (n_salient > 0 && (!salient_idx || !salient)))
+    return fail(FB_EINVAL, "fb_bb_global_gemv: salient columns: 0..256 with index and value tensors");
+  if (flags & ~FB_W3_NO_PDL) return fail(FB_EINVAL, "fb_bb_global_gemv: unknown flag bits 0x%x", flags);
+  BBParams p = {};
+  p.x = x; p.codes = codes; p.grow = static_cast<const __half*>(row_scales); p.gcol = static_cast<const __half*>(col_scales);
+  p.sal_idx = salient_idx; p.sal = static_cast<const __nv_bfloat16*>(salient); p.n_sal = n_salient; p.out = out;
+  p.O = out_features; p.K = in_features; p.G = in_features / 128; p.act_dtype = act_dtype; p.global_mode = 1;
+  return run(p, scratch, scratch_bytes, flags, stream, "fb_bb_global_gemv");
+}
