@@ -83,6 +83,27 @@ int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const
                unsigned flags, fb_stream_t stream);
 
 /*
+ * Several W3 matrices that share the activations x and K (q/k/v, or gate/up) in ONE launch:
+ * the activation tables are built once per K block and the fixed cost of a launch is paid once.
+ * Each matrix has its own planes / scales / zeros / out and out_features (a multiple of 32);
+ * `residual` (optional, [M,O] in the activation dtype) is added to the rounded result, and the
+ * sum is rounded again: out = T(T(y) + residual), what a Linear followed by an add produces.
+ * Up to 4 matrices, at most 65536 rows in total; scratch sized for the total row count.
+ * No counterpart in the reference, which launches every Linear on its own.
+ */
+typedef struct fb_w3_matrix {
+  const uint8_t* planes;
+  const void* scales;
+  const uint8_t* zeros;   /* or NULL */
+  void* out;
+  const void* residual;   /* or NULL */
+  int out_features;
+} fb_w3_matrix_t;
+int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices,
+                     int scale_dtype, const int16_t* perm, int in_features, void* scratch,
+                     size_t scratch_bytes, unsigned flags, fb_stream_t stream);
+
+/*
  * out[o] = T( sum_s partials[s, o] ), rows summed in ascending order.
  * partials fp32 [splits, O]; out f16|bf16 [O].
  * Replaces the reference's finish (csrc/w3_lut.cu:275-296, kernel :142-150).

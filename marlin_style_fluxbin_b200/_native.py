@@ -22,6 +22,13 @@ FB_W3_GROUP_PARTIALS = 4
 _lib = None
 
 
+class W3Matrix(ctypes.Structure):
+    """``fb_w3_matrix_t`` of the C header."""
+
+    _fields_ = [("planes", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("zeros", ctypes.c_void_p),
+                ("out", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("out_features", ctypes.c_int)]
+
+
 class NativeError(RuntimeError):
     """A call into the CUDA library was rejected (message from ``fb_last_error``)."""
 
@@ -46,6 +53,10 @@ def library() -> ctypes.CDLL:
             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
             ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p,
         ]
+        lib.fb_w3_gemv_multi.restype = ctypes.c_int
+        lib.fb_w3_gemv_multi.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(W3Matrix), ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                                         ctypes.c_uint, ctypes.c_void_p]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.fb_bb_gemv_scratch_bytes.restype = ctypes.c_size_t
@@ -208,3 +219,30 @@ def bb_global_gemv(x, codes, row_scales, col_scales, salient_idx, salient, out, 
             ptr(x), dtype_tag(x.dtype), ptr(codes), ptr(row_scales), ptr(col_scales), ptr(salient_idx), ptr(salient),
             n_sal, ptr(out), o, k, ptr(scratch), scratch.numel() * scratch.element_size(), 0 if pdl else FB_W3_NO_PDL,
             stream_handle(x.device)))
+
+
+def _addr(tensor):
+    return None if tensor is None else tensor.data_ptr()
+
+
+def w3_matrix_list(entries):
+    """Build the C array for ``w3_gemv_multi`` from ``(planes, scales, zeros, out, residual)`` tuples.
+
+    Keep the returned array (and the tensors) alive for as long as launches use it."""
+    array = (W3Matrix * len(entries))()
+    for slot, (planes, scales, zeros, out, residual) in zip(array, entries):
+        slot.planes, slot.scales, slot.zeros = _addr(planes), _addr(scales), _addr(zeros)
+        slot.out, slot.residual, slot.out_features = _addr(out), _addr(residual), planes.shape[2]
+    return array
+
+
+def w3_gemv_multi(x, matrices, n_matrices, total_out, scale_dtype, perm, *, decoded_bf16=False, pdl=True, scratch=None) -> None:
+    """One launch for several matrices sharing ``x`` ``[M,K]``; ``matrices`` from ``w3_matrix_list``."""
+    m, k = x.shape
+    if scratch is None:
+        scratch = scratch_for(x.device, w3_scratch_bytes(m, total_out, k))
+    flags = (FB_W3_DECODED_BF16 if decoded_bf16 else 0) | (0 if pdl else FB_W3_NO_PDL)
+    with torch.cuda.device(x.device):
+        check(library().fb_w3_gemv_multi(ptr(x), dtype_tag(x.dtype), m, matrices, n_matrices, dtype_tag(scale_dtype),
+                                         ptr(perm), k, ptr(scratch), scratch.numel() * scratch.element_size(), flags,
+                                         stream_handle(x.device)))

@@ -63,13 +63,25 @@ constexpr int kCtasPerSm = 2;
 constexpr int kMaxSlots = 4;
 constexpr int kMaxM = 4;
 
-struct W3Params {
-  const void* x;
+constexpr int kMaxMatrices = 4;
+
+// One weight matrix of a launch.  Several matrices that share x and K (q/k/v, gate/up) are
+// served by one launch: their rows are concatenated, 32-row unit by unit.
+struct W3Matrix {
   const uint8_t* planes;
   const unsigned short* scales;
   const uint8_t* zeros;
+  void* out;             // [M,O] 16-bit, or fp32 [G,O] group partials when group_partials != 0
+  const void* residual;  // optional [M,O] 16-bit, added to the rounded result
+  int O;
+  int ru_begin;          // first 32-row unit of this matrix in the concatenated row space
+};
+
+struct W3Params {
+  const void* x;
+  W3Matrix mats[kMaxMatrices];
+  int n_mats;
   const int16_t* perm;
-  void* out;        // [M,O] 16-bit, or fp32 [G,O] group partials when group_partials != 0
   float* partials;  // [nKB, M, O]
   unsigned* tickets;
   unsigned* status;
@@ -126,17 +138,42 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     first = ua + warp * q + min(warp, r);
     count = q + (warp < r ? 1 : 0);
   };
-  // Bulk copies of `n` consecutive units starting at unit `first` into slots [slot, slot+n).
+  // Matrix that owns 32-row unit `ru` of the concatenated row space.
+  auto locate = [&](int ru) {
+    int j = 0;
+    while (j + 1 < p.n_mats && ru >= p.mats[j + 1].ru_begin) ++j;
+    return j;
+  };
+  // Bulk copies of `n` consecutive units starting at unit `first` into slots [slot, slot+n);
+  // one run of copies per matrix the range touches.
   auto stage_units = [&](int kb, int first, int n, int slot, int bar_index) {
     if (lane == 0) {
       const int ngroups = min(2, p.G - 2 * kb);
       const uint32_t bar = smem_u32(&bars[bar_index]);
       mbar_expect_tx(bar, (uint32_t)(ngroups * 3 * n * kPlaneTile));
-      for (int i = 0; i < ngroups * 3; ++i) {
-        const uint8_t* src = p.planes + (((size_t)(2 * kb) * 3 + i) * p.O + (size_t)first * kUnitRows) * 16;
-        bulk_g2s(stage_u32 + (uint32_t)((i * S + slot) * kPlaneTile), src, (uint32_t)(n * kPlaneTile), bar);
+      while (n > 0) {
+        const int j = locate(first);
+        const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
+        const int run = min(n, end - first);
+        for (int i = 0; i < ngroups * 3; ++i) {
+          const uint8_t* src = p.mats[j].planes +
+                               (((size_t)(2 * kb) * 3 + i) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * 16;
+          bulk_g2s(stage_u32 + (uint32_t)((i * S + slot) * kPlaneTile), src, (uint32_t)(run * kPlaneTile), bar);
+        }
+        first += run;
+        slot += run;
+        n -= run;
       }
     }
+  };
+  // Final value of one output element: rounded to the 16-bit dtype, then the optional residual
+  // is added and the sum rounded again (what separate Linear and add kernels produce).
+  auto emit = [&](const W3Matrix& mat, int m, int lrow, float value) {
+    if (mat.residual) {
+      const float y = p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(value)) : __half2float(__float2half_rn(value));
+      value = y + load_act(mat.residual, p.act_dtype, m * mat.O + lrow);
+    }
+    store_act(mat.out, p.act_dtype, m * mat.O + lrow, value);
   };
 
   // Lane rotation (byte, half, word): at every step the 32 lanes hit 32 different tables.
@@ -233,14 +270,16 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     for (int i = 0; i < my_count; ++i) {
       const int slot = i % S;
       const int ru = my_first + i;
-      const int row = ru * kUnitRows + lane;
+      const int row = ru * kUnitRows + lane;  // in the concatenated row space
+      const W3Matrix& mat = p.mats[locate(ru)];
+      const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
       // scale / zero loads first: their latency overlaps the wait below
-      const unsigned short sbitsA = p.scales[(size_t)gA * p.O + row];
-      const unsigned short sbitsB = hasB ? p.scales[(size_t)gB * p.O + row] : (unsigned short)0;
+      const unsigned short sbitsA = mat.scales[(size_t)gA * mat.O + lrow];
+      const unsigned short sbitsB = hasB ? mat.scales[(size_t)gB * mat.O + lrow] : (unsigned short)0;
       float zcA = 0.f, zcB = 0.f;
-      if (p.zeros) {
-        zcA = 4.f - (float)p.zeros[(size_t)gA * p.O + row];
-        if (hasB) zcB = 4.f - (float)p.zeros[(size_t)gB * p.O + row];
+      if (mat.zeros) {
+        zcA = 4.f - (float)mat.zeros[(size_t)gA * mat.O + lrow];
+        if (hasB) zcB = 4.f - (float)mat.zeros[(size_t)gB * mat.O + lrow];
       }
 
       bool ok = false;
@@ -320,7 +359,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           const float first = acc[m][0][0] + 2.f * acc[m][0][1] - 4.f * acc[m][0][2];
           const float second = acc[m][1][0] + 2.f * acc[m][1][1] - 4.f * acc[m][1][2];
           float dA = rh ? second : first, dB = rh ? first : second;
-          if (p.zeros) {
+          if (mat.zeros) {
             dA += zcA * __shfl_sync(0xffffffffu, sx_m[m], 0);
             dB += zcB * __shfl_sync(0xffffffffu, sx_m[m], 16);
           }
@@ -336,11 +375,11 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
             vB += cB * (r3B - 3.f * sB);
           }
           if (p.group_partials) {
-            float* ws_out = reinterpret_cast<float*>(p.out);
-            ws_out[(size_t)gA * p.O + row] = vA;
-            if (hasB) ws_out[(size_t)gB * p.O + row] = vB;
+            float* ws_out = reinterpret_cast<float*>(mat.out);
+            ws_out[(size_t)gA * mat.O + lrow] = vA;
+            if (hasB) ws_out[(size_t)gB * mat.O + lrow] = vB;
           } else if (p.nKB == 1) {
-            store_act(p.out, p.act_dtype, m * p.O + row, vA + vB);
+            emit(mat, m, lrow, vA + vB);
           } else {
             p.partials[((size_t)kb * M + m) * p.O + row] = vA + vB;
           }
@@ -371,15 +410,17 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         const unsigned mine = __ballot_sync(0xffffffffu, my_ru >= 0 && prior == (unsigned)p.nKB - 1u);
         unsigned todo = mine;
         while (todo) {
-          int rows[4];
+          int rows[4], owner[4];
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             if (todo) {
               const int j = __ffs(todo) - 1;
               todo &= todo - 1;
               rows[t] = (my_first + base + j) * kUnitRows + lane;
+              owner[t] = locate(my_first + base + j);
             } else {
               rows[t] = -1;
+              owner[t] = 0;
             }
           }
 #pragma unroll
@@ -396,7 +437,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
             }
 #pragma unroll
             for (int t = 0; t < 4; ++t)
-              if (rows[t] >= 0) store_act(p.out, p.act_dtype, m * p.O + rows[t], total[t]);
+              if (rows[t] >= 0) emit(p.mats[owner[t]], m, rows[t] - p.mats[owner[t]].ru_begin * kUnitRows, total[t]);
           }
         }
         if (my_ru >= 0 && prior == (unsigned)p.nKB - 1u) p.tickets[my_ru] = 0u;
@@ -480,51 +521,71 @@ extern "C" size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_featu
   return kPartialsOffset + partial_bytes(m, out_features, in_features);
 }
 
-extern "C" int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales,
-                          int scale_dtype, const uint8_t* zeros, const int16_t* perm, void* out,
-                          int out_features, int in_features, void* scratch, size_t scratch_bytes,
-                          unsigned flags, fb_stream_t stream) {
-  const int O = out_features, K = in_features;
+extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices,
+                                int scale_dtype, const int16_t* perm, int in_features, void* scratch,
+                                size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
+  const int K = in_features;
   const bool group_partials = (flags & FB_W3_GROUP_PARTIALS) != 0;
-  if (!x || !planes || !scales || !out) return fail(FB_EINVAL, "fb_w3_gemv: x, planes, scales and out must be non-null");
+  if (!x || !matrices) return fail(FB_EINVAL, "fb_w3_gemv: x and the matrix list must be non-null");
+  if (n_matrices < 1 || n_matrices > kMaxMatrices) return fail(FB_ELIMIT, "fb_w3_gemv: %d matrices given, 1..%d supported", n_matrices, kMaxMatrices);
   if ((act_dtype != FB_F16 && act_dtype != FB_BF16) || (scale_dtype != FB_F16 && scale_dtype != FB_BF16))
     return fail(FB_EINVAL, "fb_w3_gemv: dtype tags must be FB_F16 or FB_BF16");
   if (m < 1 || m > kMaxM) return fail(FB_ELIMIT, "fb_w3_gemv: M=%d outside 1..%d", m, kMaxM);
   if (K < 128 || K % 128 || K / 128 > 255) return fail(FB_ELIMIT, "fb_w3_gemv: K=%d must be a multiple of 128 with at most 255 groups", K);
-  if (O < 32 || O > 65536 || O % 32) return fail(FB_ELIMIT, "fb_w3_gemv: O=%d must be a multiple of 32 in 32..65536", O);
-  if (!aligned(planes, 16)) return fail(FB_EINVAL, "fb_w3_gemv: planes must be 16-byte aligned");
   if (!aligned(x, 16) && !perm) return fail(FB_EINVAL, "fb_w3_gemv: x must be 16-byte aligned");
-  if (!aligned(scales, 2) || !aligned(out, group_partials ? 4 : 2) || !aligned(x, 2) || (perm && !aligned(perm, 2)))
-    return fail(FB_EINVAL, "fb_w3_gemv: 16-bit tensors must be 2-byte aligned");
-  if ((flags & FB_W3_DECODED_BF16) && zeros) return fail(FB_EINVAL, "fb_w3_gemv: the rounding correction needs the constant zero point (zeros == NULL)");
+  if (!aligned(x, 2) || (perm && !aligned(perm, 2))) return fail(FB_EINVAL, "fb_w3_gemv: 16-bit tensors must be 2-byte aligned");
   if (flags & ~(FB_W3_DECODED_BF16 | FB_W3_NO_PDL | FB_W3_GROUP_PARTIALS)) return fail(FB_EINVAL, "fb_w3_gemv: unknown flag bits 0x%x", flags);
-  if (group_partials && m != 1) return fail(FB_EINVAL, "fb_w3_gemv: group partials need M = 1");
+  if (group_partials && (m != 1 || n_matrices != 1)) return fail(FB_EINVAL, "fb_w3_gemv: group partials need M = 1 and a single matrix");
   const int G = K / 128;
-  const size_t out_bytes = group_partials ? (size_t)(K / 128) * O * 4 : (size_t)m * O * 2, x_bytes = (size_t)m * K * 2;
-  if (overlaps(out, out_bytes, x, x_bytes) || overlaps(out, out_bytes, planes, (size_t)G * 3 * O * 16) ||
-      overlaps(out, out_bytes, scales, (size_t)G * O * 2))
-    return fail(FB_EALIAS, "fb_w3_gemv: out overlaps an input");
-  const size_t need = fb_w3_gemv_scratch_bytes(m, O, K);
-  if (!scratch || scratch_bytes < need) return fail(FB_ESCRATCH, "fb_w3_gemv: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
-  if (!aligned(scratch, 256)) return fail(FB_EINVAL, "fb_w3_gemv: scratch must be 256-byte aligned");
-  if (overlaps(scratch, need, out, out_bytes) || overlaps(scratch, need, x, x_bytes))
-    return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps x or out");
-
-  const DeviceInfo* info = device_info();
-  if (!info) return FB_ECUDA;
+  const size_t x_bytes = (size_t)m * K * 2;
 
   W3Params p;
   p.x = x;
-  p.planes = planes;
-  p.scales = static_cast<const unsigned short*>(scales);
-  p.zeros = zeros;
   p.perm = perm;
-  p.out = out;
-  p.O = O;
+  p.n_mats = n_matrices;
+  long long total = 0;
+  for (int j = 0; j < kMaxMatrices; ++j) {
+    W3Matrix& mat = p.mats[j];
+    if (j >= n_matrices) {
+      mat = W3Matrix{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
+      continue;
+    }
+    const fb_w3_matrix_t& in = matrices[j];
+    const int O = in.out_features;
+    if (!in.planes || !in.scales || !in.out) return fail(FB_EINVAL, "fb_w3_gemv: planes, scales and out must be non-null");
+    if (O < 32 || O > 65536 || O % 32) return fail(FB_ELIMIT, "fb_w3_gemv: O=%d must be a multiple of 32 in 32..65536", O);
+    if (!aligned(in.planes, 16)) return fail(FB_EINVAL, "fb_w3_gemv: planes must be 16-byte aligned");
+    if (!aligned(in.scales, 2) || !aligned(in.out, group_partials ? 4 : 2) || !aligned(in.residual, 2))
+      return fail(FB_EINVAL, "fb_w3_gemv: 16-bit tensors must be 2-byte aligned");
+    if ((flags & FB_W3_DECODED_BF16) && in.zeros)
+      return fail(FB_EINVAL, "fb_w3_gemv: the rounding correction needs the constant zero point (zeros == NULL)");
+    const size_t out_bytes = group_partials ? (size_t)G * O * 4 : (size_t)m * O * 2;
+    if (overlaps(in.out, out_bytes, x, x_bytes) || overlaps(in.out, out_bytes, in.planes, (size_t)G * 3 * O * 16) ||
+        overlaps(in.out, out_bytes, in.scales, (size_t)G * O * 2))
+      return fail(FB_EALIAS, "fb_w3_gemv: out overlaps an input");
+    if (scratch && overlaps(scratch, scratch_bytes, in.out, out_bytes)) return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps out");
+    mat.planes = in.planes;
+    mat.scales = static_cast<const unsigned short*>(in.scales);
+    mat.zeros = in.zeros;
+    mat.out = in.out;
+    mat.residual = in.residual;
+    mat.O = O;
+    mat.ru_begin = (int)(total / kUnitRows);
+    total += O;
+  }
+  if (total > 65536) return fail(FB_ELIMIT, "fb_w3_gemv: %lld output rows in one launch, at most 65536", total);
+  const size_t need = fb_w3_gemv_scratch_bytes(m, (int)total, K);
+  if (!scratch || scratch_bytes < need) return fail(FB_ESCRATCH, "fb_w3_gemv: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+  if (!aligned(scratch, 256)) return fail(FB_EINVAL, "fb_w3_gemv: scratch must be 256-byte aligned");
+  if (overlaps(scratch, need, x, x_bytes)) return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps x");
+
+  const DeviceInfo* info = device_info();
+  if (!info) return FB_ECUDA;
+  p.O = (int)total;
   p.K = K;
   p.G = G;
   p.nKB = (G + 1) / 2;
-  p.nRU = O / kUnitRows;
+  p.nRU = (int)(total / kUnitRows);
   p.act_dtype = act_dtype;
   p.scale_dtype = scale_dtype;
   unsigned char* base = static_cast<unsigned char*>(scratch);
@@ -550,6 +611,14 @@ extern "C" int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* pl
   }
 #undef FB_DISPATCH
   return fail(FB_ELIMIT, "fb_w3_gemv: unsupported M");
+}
+
+extern "C" int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales,
+                          int scale_dtype, const uint8_t* zeros, const int16_t* perm, void* out,
+                          int out_features, int in_features, void* scratch, size_t scratch_bytes,
+                          unsigned flags, fb_stream_t stream) {
+  fb_w3_matrix_t one = {planes, scales, zeros, out, nullptr, out_features};
+  return fb_w3_gemv_multi(x, act_dtype, m, &one, 1, scale_dtype, perm, in_features, scratch, scratch_bytes, flags, stream);
 }
 
 namespace {

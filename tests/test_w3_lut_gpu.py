@@ -245,3 +245,30 @@ def test_prepared_linear_binding_and_graph():
         finally:
             module.clear_prepared_decode()
         assert module._decode_output is None
+
+
+def test_fused_matrices_share_one_launch_and_residual_epilogue():
+    """q/k/v-style fusion: three matrices on the same x in one launch give bit-identical rows to
+    three single launches; the residual epilogue equals a separate add in the output dtype."""
+    from marlin_style_fluxbin_b200 import _native
+
+    k = 1024
+    cases = [make_case(o, k, seed=30 + i, zeros=(i == 1)) for i, o in enumerate((256, 64, 96))]
+    x = cases[0][1].cuda()
+    singles, entries, keep = [], [], []
+    residual = torch.randn(1, 256, generator=torch.Generator().manual_seed(2)).bfloat16().cuda()
+    for i, (layout, _) in enumerate(cases):
+        lg = to_cuda(layout)
+        out = torch.empty(1, layout["planes"].shape[2], device="cuda", dtype=torch.bfloat16)
+        _native.w3_gemv(x, lg["planes"], lg["scales"], lg.get("zeros"), None, out)
+        singles.append(out)
+        fused_out = torch.full_like(out, float("nan"))
+        entries.append((lg["planes"], lg["scales"], lg.get("zeros"), fused_out, residual if i == 0 else None))
+        keep.append(lg)
+        reference, _ = oracle_outputs(layout, cases[0][1])
+        assert_parity(out, reference)
+    array = _native.w3_matrix_list(entries)
+    _native.w3_gemv_multi(x, array, 3, 256 + 64 + 96, torch.float16, None)
+    torch.cuda.synchronize()
+    assert torch.equal(entries[0][3], (singles[0].float() + residual.float()).bfloat16())
+    assert torch.equal(entries[1][3], singles[1]) and torch.equal(entries[2][3], singles[2])
