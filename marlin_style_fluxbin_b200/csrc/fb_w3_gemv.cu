@@ -14,8 +14,8 @@
 //    staged weight words conflict free.
 //  * The three bit planes of a warp's units (contiguous rows, so 6 copies of n x 512
 //    bytes) are staged into shared memory with bulk asynchronous copies (cp.async.bulk
-//    + mbarrier) issued by one elected lane; a lookup address is a rotate and one
-//    logic op on the staged weight word.
+//    + mbarrier), a wave of one unit per warp at a time, one (group, plane) copy per
+//    issuing lane; a lookup address is a rotate and one logic op on the staged weight word.
 //  * One CTA per SM at most: each K block is served by floor(SMs / K blocks) CTAs that
 //    split its rows, so a CTA builds the tables of exactly one K block.
 //  * Launched with programmatic dependent launch: a kernel's prologue and first weight
@@ -60,7 +60,8 @@ constexpr int kPlaneTile = kUnitRows * 16;  // 512 B: one plane of one group for
 constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
 constexpr int kWarps = 8;
 constexpr int kCtasPerSm = 2;
-constexpr int kMaxSlots = 4;
+constexpr int kRing = 3;                           // waves staged per CTA
+constexpr int kWaveBytes = kWarps * kUnitBytes;    // 24 KB: one unit per warp
 constexpr int kMaxM = 4;
 
 constexpr int kMaxMatrices = 4;
@@ -87,18 +88,33 @@ struct W3Params {
   unsigned* status;
   int O, K, G, nKB, nRU;
   int act_dtype, scale_dtype;
-  int slots;           // staged units per warp
   int ctas_per_kb;     // row slices per K block
   int group_partials;  // write scale-multiplied per-group sums instead of reducing
 };
 
-// log2 of the number of activation rows a table entry is padded to (1, 2 or 4 floats).
+// Table geometry: entry p of table t for activation row m lives at byte
+//   p * kStride + m * 128 + t * 4,   kStride = 128 * (M rounded up to a power of two),
+// so with M = 1 the 32 tables of a K block take 32 KB and the bank of a lookup is the table
+// number.  A lookup address is a rotate of the staged weight word (which brings the weight
+// byte to the entry field) and one logic op that masks it and merges the lane's table offset.
 template <int M>
 struct LutGeom {
-  static constexpr int kLog = M == 1 ? 0 : (M == 2 ? 1 : 2);
-  static constexpr int kStrideLog = 7 + kLog;           // bytes between consecutive entries
-  static constexpr int kBytes = 256 << kStrideLog;      // 32 KB per padded activation row
+  static constexpr int kStrideLog = 7 + (M == 1 ? 0 : (M == 2 ? 1 : 2));
+  static constexpr int kStride = 1 << kStrideLog;
+  static constexpr int kBytes = 256 << kStrideLog;
 };
+
+// acc.{lo,hi} += {a, b} with one packed fp32x2 add
+__device__ __forceinline__ void add_pair(unsigned long long& acc, float a, float b) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(a), "f"(b));
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc) : "l"(v));
+}
+__device__ __forceinline__ float pair_sum(unsigned long long acc) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc));
+  return lo + hi;
+}
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -108,12 +124,12 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   extern __shared__ __align__(1024) unsigned char smem[];
   using Geom = LutGeom<M>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int S = p.slots;
   unsigned char* const lut = smem;
-  // per warp: [group half][plane][slot][32 rows x 16 B]
-  unsigned char* const stage_base = smem + Geom::kBytes + (size_t)warp * S * kUnitBytes;
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + Geom::kBytes + (size_t)kWarps * S * kUnitBytes) + warp * (kMaxSlots + 1);
-  const uint32_t stage_u32 = smem_u32(stage_base);
+  // Ring of kRing staged waves; a wave is one 32-row unit per warp (contiguous rows), laid out
+  // [group half * 3 + plane][warp][32 rows x 16 B], so each (half, plane) is ONE copy of up to 4 KB.
+  unsigned char* const ring = smem + Geom::kBytes;
+  uint64_t* const full_bars = reinterpret_cast<uint64_t*>(smem + Geom::kBytes + (size_t)kRing * kWaveBytes);
+  uint64_t* const empty_bars = full_bars + kRing;
 
   FB_MARK(0);
   // The next kernel in the stream may start its own prologue (weight prefetch) now; it
@@ -123,20 +139,21 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   const int nV = p.nKB * p.ctas_per_kb;
   if ((int)blockIdx.x >= nV) return;
 
-  if (lane == 0)
-    for (int s = 0; s <= kMaxSlots; ++s) mbar_init(smem_u32(&bars[s]), 1);
-  mbar_init_fence();
-  __syncwarp();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRing; ++s) {
+      mbar_init(smem_u32(&full_bars[s]), 6);        // six issuing lanes, one per (half, plane)
+      mbar_init(smem_u32(&empty_bars[s]), kWarps);  // every warp releases a wave after reading it
+    }
+    mbar_init_fence();
+  }
+  __syncthreads();
 
-  // Work of virtual CTA v: K block v / c, rows of slice v % c; this warp's contiguous share.
+  // Work of virtual CTA v: K block v / c, the row units [first, first + count) of slice v % c.
   auto share = [&](int v, int& kb, int& first, int& count) {
     kb = v / p.ctas_per_kb;
     const int slice = v - kb * p.ctas_per_kb;
-    const int ua = (int)((long long)slice * p.nRU / p.ctas_per_kb);
-    const int ub = (int)((long long)(slice + 1) * p.nRU / p.ctas_per_kb);
-    const int n = ub - ua, q = n / kWarps, r = n - q * kWarps;
-    first = ua + warp * q + min(warp, r);
-    count = q + (warp < r ? 1 : 0);
+    first = (int)((long long)slice * p.nRU / p.ctas_per_kb);
+    count = (int)((long long)(slice + 1) * p.nRU / p.ctas_per_kb) - first;
   };
   // Matrix that owns 32-row unit `ru` of the concatenated row space.
   auto locate = [&](int ru) {
@@ -144,24 +161,28 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     while (j + 1 < p.n_mats && ru >= p.mats[j + 1].ru_begin) ++j;
     return j;
   };
-  // Bulk copies of `n` consecutive units starting at unit `first` into slots [slot, slot+n);
-  // one run of copies per matrix the range touches.
-  auto stage_units = [&](int kb, int first, int n, int slot, int bar_index) {
-    if (lane == 0) {
-      const int ngroups = min(2, p.G - 2 * kb);
-      const uint32_t bar = smem_u32(&bars[bar_index]);
-      mbar_expect_tx(bar, (uint32_t)(ngroups * 3 * n * kPlaneTile));
-      while (n > 0) {
+  bool dead = false;
+  // Stage wave number `seq` (counted over the whole kernel): units [first, first + n) of K
+  // block kb.  Lane 0 of warps 0..5 each copy one (half, plane); a slot is reused only after
+  // all warps have released the wave that occupied it.
+  auto issue_wave = [&](int seq, int kb, int first, int n) {
+    if (warp < 6 && lane == 0) {
+      const int slot = seq % kRing;
+      if (seq >= kRing && !mbar_wait_bounded(smem_u32(&empty_bars[slot]), (uint32_t)((seq / kRing - 1) & 1)))
+        atomicExch(p.status, 2u);
+      const bool present = warp < 3 * min(2, p.G - 2 * kb);
+      const uint32_t bar = smem_u32(&full_bars[slot]);
+      mbar_expect_tx(bar, present ? (uint32_t)(n * kPlaneTile) : 0u);
+      uint32_t dst = smem_u32(ring + (size_t)slot * kWaveBytes + (size_t)warp * kWarps * kPlaneTile);
+      while (present && n > 0) {  // one copy per matrix the wave touches
         const int j = locate(first);
         const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
         const int run = min(n, end - first);
-        for (int i = 0; i < ngroups * 3; ++i) {
-          const uint8_t* src = p.mats[j].planes +
-                               (((size_t)(2 * kb) * 3 + i) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * 16;
-          bulk_g2s(stage_u32 + (uint32_t)((i * S + slot) * kPlaneTile), src, (uint32_t)(run * kPlaneTile), bar);
-        }
+        const uint8_t* src = p.mats[j].planes +
+                             (((size_t)(2 * kb) * 3 + warp) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * 16;
+        bulk_g2s(dst, src, (uint32_t)(run * kPlaneTile), bar);
+        dst += run * kPlaneTile;
         first += run;
-        slot += run;
         n -= run;
       }
     }
@@ -178,18 +199,27 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
 
   // Lane rotation (byte, half, word): at every step the 32 lanes hit 32 different tables.
   const int rb = lane & 3, rh = (lane >> 2) & 1, rw = (lane >> 3) & 3;
-  uint32_t rot[4];
+  // Rotation amounts and table offsets, fixed per lane.
+  uint32_t rot[4], xoff[2][4][4];
 #pragma unroll
   for (int b = 0; b < 4; ++b) rot[b] = (uint32_t)((8 * ((b + rb) & 3) - Geom::kStrideLog) & 31);
   constexpr uint32_t kEntryMask = 0xffu << Geom::kStrideLog;
+  auto entry_address = [&](uint32_t word, int b, uint32_t offset) { return (__funnelshift_r(word, word, rot[b]) & kEntryMask) | offset; };
+#pragma unroll
+  for (int jh = 0; jh < 2; ++jh)
+#pragma unroll
+    for (int jw = 0; jw < 4; ++jw)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) xoff[jh][jw][b] = (uint32_t)(64 * (jh ^ rh) + 16 * ((jw + rw) & 3) + 4 * ((b + rb) & 3));
+  auto table_of = [&](int m) { return lut + m * 128; };
 
-  uint32_t chunk_parity = 0, slot_parity = 0;
-  bool dead = false;
   bool first_pass = true;
+  int seq_base = 0;  // waves staged before the current virtual CTA
 
-  int kb, my_first, my_count;
-  share((int)blockIdx.x, kb, my_first, my_count);
-  stage_units(kb, my_first, min(S, my_count), 0, kMaxSlots);  // weights never change: no need to wait
+  int kb, cta_first, cta_count;
+  share((int)blockIdx.x, kb, cta_first, cta_count);
+  for (int w = 0; w < kRing && w * kWarps < cta_count; ++w)  // weights never change: no need to wait
+    issue_wave(w, kb, cta_first + w * kWarps, min(kWarps, cta_count - w * kWarps));
   FB_MARK(1);
 
   // Everything below reads activations and writes scratch / outputs of this stream.
@@ -199,8 +229,9 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
     if (!first_pass) {
       __syncthreads();  // everyone has finished reading the previous tables
-      share(v, kb, my_first, my_count);
-      if (!dead) stage_units(kb, my_first, min(S, my_count), 0, kMaxSlots);
+      share(v, kb, cta_first, cta_count);
+      for (int w = 0; w < kRing && w * kWarps < cta_count; ++w)
+        issue_wave(seq_base + w, kb, cta_first + w * kWarps, min(kWarps, cta_count - w * kWarps));
     }
     first_pass = false;
 
@@ -237,7 +268,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         }
         // ... then the high four, still in ascending order; this warp owns the entries
         // whose high nibble is 2*warp or 2*warp+1.
-        unsigned char* const column = lut + m * 128 + lane * 4;
+        unsigned char* const column = table_of(m) + lane * 4;
 #pragma unroll
         for (int hh = 0; hh < 16 / kWarps; ++hh) {
           const int hi = warp * (16 / kWarps) + hh;
@@ -248,7 +279,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
             if (hi & 2) s += v8[5];
             if (hi & 4) s += v8[6];
             if (hi & 8) s += v8[7];
-            *reinterpret_cast<float*>(column + ((size_t)(hi * 16 + q) << Geom::kStrideLog)) = s;
+            *reinterpret_cast<float*>(column + (size_t)(hi * 16 + q) * Geom::kStride) = s;
           }
         }
         float total = 0.f;
@@ -266,38 +297,36 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     // ---- this warp's units ----
     const int gA = 2 * kb, gB = 2 * kb + 1;
     const bool hasB = gB < p.G;
-    const int chunk = min(S, my_count);
-    for (int i = 0; i < my_count; ++i) {
-      const int slot = i % S;
-      const int ru = my_first + i;
+    const int waves = (cta_count + kWarps - 1) / kWarps;
+    for (int i = 0; i < waves; ++i) {
+      const int seq = seq_base + i, slot = seq % kRing;
+      const bool mine = i * kWarps + warp < cta_count;  // the last wave may be short
+      const int ru = cta_first + i * kWarps + (mine ? warp : 0);
       const int row = ru * kUnitRows + lane;  // in the concatenated row space
       const W3Matrix& mat = p.mats[locate(ru)];
       const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
       // scale / zero loads first: their latency overlaps the wait below
-      const unsigned short sbitsA = mat.scales[(size_t)gA * mat.O + lrow];
-      const unsigned short sbitsB = hasB ? mat.scales[(size_t)gB * mat.O + lrow] : (unsigned short)0;
+      unsigned short sbitsA = 0, sbitsB = 0;
       float zcA = 0.f, zcB = 0.f;
-      if (mat.zeros) {
-        zcA = 4.f - (float)mat.zeros[(size_t)gA * mat.O + lrow];
-        if (hasB) zcB = 4.f - (float)mat.zeros[(size_t)gB * mat.O + lrow];
+      if (mine) {
+        sbitsA = mat.scales[(size_t)gA * mat.O + lrow];
+        if (hasB) sbitsB = mat.scales[(size_t)gB * mat.O + lrow];
+        if (mat.zeros) {
+          zcA = 4.f - (float)mat.zeros[(size_t)gA * mat.O + lrow];
+          if (hasB) zcB = 4.f - (float)mat.zeros[(size_t)gB * mat.O + lrow];
+        }
       }
 
-      bool ok = false;
-      if (!dead) {
-        if (i < chunk)
-          ok = mbar_wait_bounded(smem_u32(&bars[kMaxSlots]), chunk_parity);
-        else
-          ok = mbar_wait_bounded(smem_u32(&bars[slot]), (slot_parity >> slot) & 1u);
-      }
+      bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[slot]), (uint32_t)((seq / kRing) & 1));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && !dead) {
         dead = true;
         if (lane == 0) atomicExch(p.status, 1u);
       }
-      if (i >= chunk) slot_parity ^= 1u << slot;
       FB_MARK(4);
 
-      float acc[M][2][3];
+      // per activation row, group half and plane: a pair of partial sums (even / odd byte steps)
+      unsigned long long acc2[M][2][3];
       float corr[M][2];
 #pragma unroll
       for (int m = 0; m < M; ++m)
@@ -305,41 +334,46 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         for (int jh = 0; jh < 2; ++jh) {
           corr[m][jh] = 0.f;
 #pragma unroll
-          for (int pl = 0; pl < 3; ++pl) acc[m][jh][pl] = 0.f;
+          for (int pl = 0; pl < 3; ++pl) acc2[m][jh][pl] = 0ull;
         }
 
-      if (!dead) {
-        const unsigned char* const buf = stage_base + slot * kPlaneTile + lane * 16;
+      if (!dead && mine) {
+        const unsigned char* const buf = ring + (size_t)slot * kWaveBytes + warp * kPlaneTile + lane * 16;
 #pragma unroll
         for (int jh = 0; jh < 2; ++jh) {
           const int h = jh ^ rh;
 #pragma unroll
           for (int jw = 0; jw < 4; ++jw) {
             const int ws = (jw + rw) & 3;
-            const unsigned char* wp = buf + (h * 3) * S * kPlaneTile + ws * 4;
+            const unsigned char* wp = buf + (h * 3) * kWarps * kPlaneTile + ws * 4;
             uint32_t w[3];
 #pragma unroll
-            for (int pl = 0; pl < 3; ++pl) w[pl] = *reinterpret_cast<const uint32_t*>(wp + pl * S * kPlaneTile);
+            for (int pl = 0; pl < 3; ++pl) w[pl] = *reinterpret_cast<const uint32_t*>(wp + pl * kWarps * kPlaneTile);
             uint32_t plus3 = 0, minus3 = 0;
             if (CORRECT) {
               plus3 = w[0] & w[1] & ~w[2];   // code 7 (stored high plane is inverted)
               minus3 = w[0] & ~w[1] & w[2];  // code 1
             }
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const uint32_t xoff = (uint32_t)(64 * h + 16 * ws + 4 * ((b + rb) & 3));
+            for (int b = 0; b < 4; b += 2) {
 #pragma unroll
               for (int pl = 0; pl < 3; ++pl) {
-                const uint32_t a = (__funnelshift_r(w[pl], w[pl], rot[b]) & kEntryMask) | xoff;
-#pragma unroll
-                for (int m = 0; m < M; ++m) acc[m][jh][pl] += *reinterpret_cast<const float*>(lut + m * 128 + a);
-              }
-              if (CORRECT) {
-                const uint32_t ap = (__funnelshift_r(plus3, plus3, rot[b]) & kEntryMask) | xoff;
-                const uint32_t am = (__funnelshift_r(minus3, minus3, rot[b]) & kEntryMask) | xoff;
+                const uint32_t a0 = entry_address(w[pl], b, xoff[jh][jw][b]);
+                const uint32_t a1 = entry_address(w[pl], b + 1, xoff[jh][jw][b + 1]);
 #pragma unroll
                 for (int m = 0; m < M; ++m)
-                  corr[m][jh] += *reinterpret_cast<const float*>(lut + m * 128 + ap) - *reinterpret_cast<const float*>(lut + m * 128 + am);
+                  add_pair(acc2[m][jh][pl], *reinterpret_cast<const float*>(table_of(m) + a0),
+                           *reinterpret_cast<const float*>(table_of(m) + a1));
+              }
+              if (CORRECT) {
+#pragma unroll
+                for (int bb = b; bb < b + 2; ++bb) {
+                  const uint32_t ap = entry_address(plus3, bb, xoff[jh][jw][bb]);
+                  const uint32_t am = entry_address(minus3, bb, xoff[jh][jw][bb]);
+#pragma unroll
+                  for (int m = 0; m < M; ++m)
+                    corr[m][jh] += *reinterpret_cast<const float*>(table_of(m) + ap) - *reinterpret_cast<const float*>(table_of(m) + am);
+                }
               }
             }
           }
@@ -347,17 +381,20 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       }
       FB_MARK(5);
 
-      // all lanes are done with the staged bytes: refill the slot with a later unit
+      // all lanes are done with the staged bytes: release the wave; when every warp has,
+      // the issuing lanes refill the slot with a later wave
       __syncwarp();
-      if (!dead && i + S < my_count) stage_units(kb, my_first + i + S, 1, slot, slot);
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bars[slot])) : "memory");
+      if (!dead && (i + kRing) * kWarps < cta_count)
+        issue_wave(seq + kRing, kb, cta_first + (i + kRing) * kWarps, min(kWarps, cta_count - (i + kRing) * kWarps));
 
-      if (!dead) {
+      if (!dead && mine) {
         const float sA = bits_to_float(sbitsA, p.scale_dtype);
         const float sB = bits_to_float(sbitsB, p.scale_dtype);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          const float first = acc[m][0][0] + 2.f * acc[m][0][1] - 4.f * acc[m][0][2];
-          const float second = acc[m][1][0] + 2.f * acc[m][1][1] - 4.f * acc[m][1][2];
+          const float first = pair_sum(acc2[m][0][0]) + 2.f * pair_sum(acc2[m][0][1]) - 4.f * pair_sum(acc2[m][0][2]);
+          const float second = pair_sum(acc2[m][1][0]) + 2.f * pair_sum(acc2[m][1][1]) - 4.f * pair_sum(acc2[m][1][2]);
           float dA = rh ? second : first, dB = rh ? first : second;
           if (mat.zeros) {
             dA += zcA * __shfl_sync(0xffffffffu, sx_m[m], 0);
@@ -386,7 +423,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         }
       }
     }
-    chunk_parity ^= 1u;
+    seq_base += waves;
   }
 
   // ---- split-K hand-over, once per warp so that its global round trips are not paid per
@@ -396,10 +433,12 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   if (p.nKB > 1 && !p.group_partials && !dead) {
     __syncwarp();  // orders every lane's partial stores before the releases below
     for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
-      share(v, kb, my_first, my_count);
+      share(v, kb, cta_first, cta_count);
+      // this warp's units are cta_first + warp, + kWarps, ...
+      const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
       for (int base = 0; base < my_count; base += 32) {
         const int count = min(32, my_count - base);
-        const int my_ru = lane < count ? my_first + base + lane : -1;
+        const int my_ru = lane < count ? cta_first + (base + lane) * kWarps + warp : -1;
         unsigned prior = 0;
         if (my_ru >= 0)
           asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
@@ -416,8 +455,9 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
             if (todo) {
               const int j = __ffs(todo) - 1;
               todo &= todo - 1;
-              rows[t] = (my_first + base + j) * kUnitRows + lane;
-              owner[t] = locate(my_first + base + j);
+              const int ru = cta_first + (base + j) * kWarps + warp;
+              rows[t] = ru * kUnitRows + lane;
+              owner[t] = locate(ru);
             } else {
               rows[t] = -1;
               owner[t] = 0;
@@ -448,12 +488,14 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
 }
 
 struct Plan {
-  int grid, slots, ctas_per_kb;
+  int grid, ctas_per_kb;
   size_t smem;
 };
 
 size_t lut_bytes(int m) { return (size_t)32768 << (m == 1 ? 0 : (m == 2 ? 1 : 2)); }
 
+// Two CTAs per SM: with M = 1 a CTA needs 32 KB of tables + 72 KB of staged waves, so a CTA
+// of the next kernel in the stream can be resident (and prefetching) beside one of this kernel.
 Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   Plan plan;
   int c = kCtasPerSm * info.sm_count / nKB;
@@ -462,14 +504,7 @@ Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   plan.ctas_per_kb = c;
   const int nV = nKB * c;
   plan.grid = nV < kCtasPerSm * info.sm_count ? nV : kCtasPerSm * info.sm_count;
-  const int per_cta = (nRU + c - 1) / c;
-  const int per_warp = (per_cta + kWarps - 1) / kWarps;
-  // Up to three staged units per warp keeps a CTA near 104 KB for M = 1, so that a CTA of
-  // the next kernel in the stream can become resident (and prefetch) beside it.
-  int slots = per_warp < 3 ? per_warp : 3;
-  if (slots < 1) slots = 1;
-  plan.slots = slots;
-  plan.smem = lut_bytes(m) + (size_t)kWarps * slots * kUnitBytes + (size_t)kWarps * (kMaxSlots + 1) * 8;
+  plan.smem = lut_bytes(m) + (size_t)kRing * kWaveBytes + 2 * kRing * sizeof(uint64_t);
   return plan;
 }
 
@@ -593,7 +628,6 @@ extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3
   p.tickets = reinterpret_cast<unsigned*>(base + kTicketsOffset);
   p.partials = reinterpret_cast<float*>(base + kPartialsOffset);
   const Plan plan = make_plan(m, p.nKB, p.nRU, *info);
-  p.slots = plan.slots;
   p.ctas_per_kb = plan.ctas_per_kb;
   p.group_partials = group_partials ? 1 : 0;
   if (plan.smem > (size_t)info->max_smem_optin) return fail(FB_ELIMIT, "fb_w3_gemv: plan needs %zu bytes of shared memory", plan.smem);
