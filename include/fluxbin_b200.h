@@ -160,6 +160,26 @@ int fb_rope_qk(const void* q, const void* k, const void* cosv, const void* sinv,
                int q_heads, int k_heads, int head_dim, int dtype, fb_stream_t stream);
 
 /*
+ * Glue kernels of one decode step.  The reference leaves these steps to stock HF modules
+ * (static_decode.py:43-76: Qwen3 attention with q/k RMSNorm, rotary embedding, StaticCache update,
+ * SDPA, and the SwiGLU MLP); they have no kernel of their own there.
+ *
+ * fb_qknorm_rope_cache: q [q_heads,D], k/v [kv_heads,D] of the new token -> per-head RMSNorm of q
+ *   and k (weights [D]), rotary embedding with cos/sin [D], rotated q to q_out, rotated k and v
+ *   into k_cache / v_cache [kv_heads, max_positions, D] at `position`.
+ * fb_attn_decode: softmax(q k^T * scale) v over cache positions 0..length-1, grouped-query heads,
+ *   D = 128; out [q_heads, D].
+ * fb_silu_mul: out[i] = T(silu(gate[i])) * up[i].
+ */
+int fb_qknorm_rope_cache(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
+                         const void* cosv, const void* sinv, void* q_out, void* k_cache, void* v_cache, int q_heads,
+                         int kv_heads, int head_dim, int position, int max_positions, float eps, int dtype,
+                         fb_stream_t stream);
+int fb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, int q_heads, int kv_heads,
+                   int head_dim, int length, int max_positions, float scale, int dtype, fb_stream_t stream);
+int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream);
+
+/*
  * fb_w3_gemv without a scratch argument, for callers that cannot allocate device memory where
  * they call this library (all memory already handed to a pool, a framework allocator that must
  * not be bypassed, a CUDA graph capture in progress).  The split-K scratch is a fixed array of

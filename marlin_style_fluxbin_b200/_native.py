@@ -71,6 +71,12 @@ def library() -> ctypes.CDLL:
         lib.fb_rmsnorm.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
         lib.fb_rope_qk.restype = ctypes.c_int
         lib.fb_rope_qk.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int] * 4 + [ctypes.c_void_p]
+        lib.fb_qknorm_rope_cache.restype = ctypes.c_int
+        lib.fb_qknorm_rope_cache.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_attn_decode.restype = ctypes.c_int
+        lib.fb_attn_decode.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_silu_mul.restype = ctypes.c_int
+        lib.fb_silu_mul.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         lib.fb_w3_gemv_static.restype = ctypes.c_int
         lib.fb_w3_gemv_static.argtypes = lib.fb_w3_gemv.argtypes[:11] + [ctypes.c_uint, ctypes.c_void_p]
         _lib = lib
@@ -246,3 +252,24 @@ def w3_gemv_multi(x, matrices, n_matrices, total_out, scale_dtype, perm, *, deco
         check(library().fb_w3_gemv_multi(ptr(x), dtype_tag(x.dtype), m, matrices, n_matrices, dtype_tag(scale_dtype),
                                          ptr(perm), k, ptr(scratch), scratch.numel() * scratch.element_size(), flags,
                                          stream_handle(x.device)))
+
+
+def qknorm_rope_cache(q, k, v, q_weight, k_weight, cos, sin, q_out, k_cache, v_cache, position: int, eps: float) -> None:
+    """Per-head RMSNorm of q/k, rotary embedding, and the KV-cache write of one token (see the header)."""
+    dim = q_weight.numel()
+    with torch.cuda.device(q.device):
+        check(library().fb_qknorm_rope_cache(ptr(q), ptr(k), ptr(v), ptr(q_weight), ptr(k_weight), ptr(cos), ptr(sin), ptr(q_out),
+                                             ptr(k_cache), ptr(v_cache), q.numel() // dim, k.numel() // dim, dim, int(position),
+                                             k_cache.shape[-2], float(eps), dtype_tag(q.dtype), stream_handle(q.device)))
+
+
+def attn_decode(q, k_cache, v_cache, out, length: int, scale: float) -> None:
+    dim = k_cache.shape[-1]
+    with torch.cuda.device(q.device):
+        check(library().fb_attn_decode(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), q.numel() // dim, k_cache.shape[-3], dim,
+                                       int(length), k_cache.shape[-2], float(scale), dtype_tag(q.dtype), stream_handle(q.device)))
+
+
+def silu_mul(gate, up, out) -> None:
+    with torch.cuda.device(gate.device):
+        check(library().fb_silu_mul(ptr(gate), ptr(up), ptr(out), gate.numel(), dtype_tag(gate.dtype), stream_handle(gate.device)))

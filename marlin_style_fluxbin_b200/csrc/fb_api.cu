@@ -1,6 +1,7 @@
 // Error reporting, device facts and fb_query for the C ABI.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -20,6 +21,11 @@ int fail(int code, const char* fmt, ...) {
 
 int cuda_fail(cudaError_t err, const char* what) {
   return fail(FB_ECUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+bool pdl_allowed() {
+  static const bool allowed = getenv("FB_NO_PDL") == nullptr;
+  return allowed;
 }
 
 const DeviceInfo* device_info() {

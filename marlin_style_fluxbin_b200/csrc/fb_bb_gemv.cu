@@ -330,7 +330,7 @@ int launch(const BBParams& p, int grid, size_t smem, int max_smem, bool pdl, cud
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
-  config.numAttrs = pdl ? 1 : 0;
+  config.numAttrs = pdl && pdl_allowed() ? 1 : 0;
   cudaError_t err = cudaLaunchKernelEx(&config, bb_gemv_kernel<INTERLEAVED, GLOBAL>, p);
   if (err != cudaSuccess) return cuda_fail(err, "bb_gemv_kernel launch");
   return FB_OK;

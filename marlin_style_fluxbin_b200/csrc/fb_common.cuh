@@ -23,6 +23,10 @@ struct DeviceInfo {
 // (after recording it).
 const DeviceInfo* device_info();
 
+// Programmatic dependent launch can be switched off for the whole library by setting the
+// environment variable FB_NO_PDL (read once); used to tell launch-overlap effects apart.
+bool pdl_allowed();
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline bool overlaps(const void* a, size_t na, const void* b, size_t nb) {
   auto pa = reinterpret_cast<uintptr_t>(a), pb = reinterpret_cast<uintptr_t>(b);

@@ -1,0 +1,197 @@
+// Small fused kernels of one decode step (one token), the glue between the packed GEMVs:
+//   fb_qknorm_rope_cache  per-head RMSNorm of q and k, rotary embedding, and the write of the new
+//                         k / v into the static KV cache, in one launch
+//   fb_attn_decode        single-query attention over the cached positions (grouped-query heads)
+//   fb_silu_mul           SwiGLU gate: out = silu(gate) * up
+// The reference leaves these steps to stock HF modules (static_decode.py:43-76); after the Linears
+// shrink by 5x they dominate the step, so each becomes one launch here.  All are launched with
+// programmatic dependent launch and let the next kernel start its prologue at once.
+#include "fb_common.cuh"
+
+namespace {
+
+using namespace fb;
+
+__device__ __forceinline__ float round_to(float v, int dtype) {
+  return dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
+}
+__device__ __forceinline__ unsigned short to_bits(float v, int dtype) {
+  return dtype == FB_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+}
+
+// One warp per head (q heads first, then k heads, then v heads which are only copied).
+// Arithmetic per head follows the stock modules: RMSNorm (fp32 statistics, cast, weight), then
+// out = T(T(v*cos) + rotate_half(v)*sin).
+__global__ void qknorm_rope_cache_kernel(const unsigned short* __restrict__ q, const unsigned short* __restrict__ k,
+                                         const unsigned short* __restrict__ v, const unsigned short* __restrict__ q_weight,
+                                         const unsigned short* __restrict__ k_weight, const unsigned short* __restrict__ cosv,
+                                         const unsigned short* __restrict__ sinv, unsigned short* __restrict__ q_out,
+                                         unsigned short* __restrict__ k_cache, unsigned short* __restrict__ v_cache,
+                                         int q_heads, int kv_heads, int dim, int position, int max_positions, float eps,
+                                         int dtype) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int head = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, lane = threadIdx.x & 31;
+  if (head >= q_heads + 2 * kv_heads) return;
+  if (head >= q_heads + kv_heads) {  // v: straight into the cache
+    const int hv = head - q_heads - kv_heads;
+    for (int i = lane; i < dim; i += 32) v_cache[((size_t)hv * max_positions + position) * dim + i] = v[(size_t)hv * dim + i];
+    return;
+  }
+  const bool is_q = head < q_heads;
+  const unsigned short* src = is_q ? q + (size_t)head * dim : k + (size_t)(head - q_heads) * dim;
+  const unsigned short* weight = is_q ? q_weight : k_weight;
+  unsigned short* dst = is_q ? q_out + (size_t)head * dim : k_cache + ((size_t)(head - q_heads) * max_positions + position) * dim;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float x = bits_to_float(src[i], dtype);
+    ss += x * x;
+  }
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+  const float inv = rsqrtf(ss / (float)dim + eps);
+  const int half = dim / 2;
+  for (int i = lane; i < half; i += 32) {
+    const float lo = bits_to_float(weight[i], dtype) * round_to(bits_to_float(src[i], dtype) * inv, dtype);
+    const float hi = bits_to_float(weight[i + half], dtype) * round_to(bits_to_float(src[i + half], dtype) * inv, dtype);
+    const float nlo = round_to(lo, dtype), nhi = round_to(hi, dtype);  // the normed head, as stored
+    const float y0 = round_to(nlo * bits_to_float(cosv[i], dtype), dtype) + (-nhi) * bits_to_float(sinv[i], dtype);
+    const float y1 = round_to(nhi * bits_to_float(cosv[i + half], dtype), dtype) + nlo * bits_to_float(sinv[i + half], dtype);
+    dst[i] = to_bits(y0, dtype);
+    dst[i + half] = to_bits(y1, dtype);
+  }
+}
+
+// One CTA (8 warps) per query head; warps stride over the cached positions with an online
+// softmax each, then merge.  head_dim 128: a lane holds four consecutive dims.
+constexpr int kAttnWarps = 8;
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsigned short* __restrict__ q,
+                                                                      const unsigned short* __restrict__ k_cache,
+                                                                      const unsigned short* __restrict__ v_cache,
+                                                                      unsigned short* __restrict__ out, int q_heads, int kv_heads,
+                                                                      int length, int max_positions, float scale, int dtype) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr int D = 128;
+  const int head = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = head / (q_heads / kv_heads);
+  const unsigned short* kbase = k_cache + (size_t)kvh * max_positions * D;
+  const unsigned short* vbase = v_cache + (size_t)kvh * max_positions * D;
+  float qv[4];
+  {
+    const uint2 raw = *reinterpret_cast<const uint2*>(q + (size_t)head * D + lane * 4);
+    qv[0] = bits_to_float((unsigned short)(raw.x & 0xffff), dtype) * scale;
+    qv[1] = bits_to_float((unsigned short)(raw.x >> 16), dtype) * scale;
+    qv[2] = bits_to_float((unsigned short)(raw.y & 0xffff), dtype) * scale;
+    qv[3] = bits_to_float((unsigned short)(raw.y >> 16), dtype) * scale;
+  }
+  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int pos = warp; pos < length; pos += kAttnWarps) {
+    const uint2 kr = *reinterpret_cast<const uint2*>(kbase + (size_t)pos * D + lane * 4);
+    float s = qv[0] * bits_to_float((unsigned short)(kr.x & 0xffff), dtype) + qv[1] * bits_to_float((unsigned short)(kr.x >> 16), dtype) +
+              qv[2] * bits_to_float((unsigned short)(kr.y & 0xffff), dtype) + qv[3] * bits_to_float((unsigned short)(kr.y >> 16), dtype);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    const float m_new = fmaxf(m, s);
+    const float correction = __expf(m - m_new), p = __expf(s - m_new);
+    const uint2 vr = *reinterpret_cast<const uint2*>(vbase + (size_t)pos * D + lane * 4);
+    acc[0] = acc[0] * correction + p * bits_to_float((unsigned short)(vr.x & 0xffff), dtype);
+    acc[1] = acc[1] * correction + p * bits_to_float((unsigned short)(vr.x >> 16), dtype);
+    acc[2] = acc[2] * correction + p * bits_to_float((unsigned short)(vr.y & 0xffff), dtype);
+    acc[3] = acc[3] * correction + p * bits_to_float((unsigned short)(vr.y >> 16), dtype);
+    l = l * correction + p;
+    m = m_new;
+  }
+  __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps], sm_acc[kAttnWarps][D];
+  if (lane == 0) {
+    sm_m[warp] = m;
+    sm_l[warp] = l;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sm_acc[warp][lane * 4 + i] = acc[i];
+  __syncthreads();
+  if (warp == 0) {
+    float gm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) gm = fmaxf(gm, sm_m[w]);
+    float total = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float f = sm_m[w] == -INFINITY ? 0.f : __expf(sm_m[w] - gm);
+      total += sm_l[w] * f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] += sm_acc[w][lane * 4 + i] * f;
+    }
+    const float inv = 1.f / total;
+    uint2 packed;
+    packed.x = (uint32_t)to_bits(o[0] * inv, dtype) | ((uint32_t)to_bits(o[1] * inv, dtype) << 16);
+    packed.y = (uint32_t)to_bits(o[2] * inv, dtype) | ((uint32_t)to_bits(o[3] * inv, dtype) << 16);
+    *reinterpret_cast<uint2*>(out + (size_t)head * D + lane * 4) = packed;
+  }
+}
+
+__global__ void silu_mul_kernel(const unsigned short* __restrict__ gate, const unsigned short* __restrict__ up,
+                                unsigned short* __restrict__ out, int n, int dtype) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float g = bits_to_float(gate[i], dtype);
+  const float s = round_to(g / (1.f + __expf(-g)), dtype);  // silu in the activation dtype, as torch does
+  out[i] = to_bits(s * bits_to_float(up[i], dtype), dtype);
+}
+
+template <class Kernel, class... Args>
+int launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const char* what, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl_allowed() ? 1 : 0;
+  cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
+  if (err != cudaSuccess) return cuda_fail(err, what);
+  return FB_OK;
+}
+
+inline const unsigned short* u16(const void* p) { return static_cast<const unsigned short*>(p); }
+inline unsigned short* u16(void* p) { return static_cast<unsigned short*>(p); }
+
+}  // namespace
+
+extern "C" int fb_qknorm_rope_cache(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
+                                    const void* cosv, const void* sinv, void* q_out, void* k_cache, void* v_cache, int q_heads,
+                                    int kv_heads, int head_dim, int position, int max_positions, float eps, int dtype,
+                                    fb_stream_t stream) {
+  if (!q || !k || !v || !q_weight || !k_weight || !cosv || !sinv || !q_out || !k_cache || !v_cache) return fail(FB_EINVAL, "fb_qknorm_rope_cache: null pointer");
+  if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_qknorm_rope_cache: dtype must be FB_F16 or FB_BF16");
+  if (q_heads < 1 || kv_heads < 1 || head_dim < 2 || head_dim % 2 || head_dim > 1024) return fail(FB_ELIMIT, "fb_qknorm_rope_cache: head geometry outside bounds");
+  if (position < 0 || position >= max_positions) return fail(FB_ELIMIT, "fb_qknorm_rope_cache: position %d outside the cache of %d", position, max_positions);
+  const int heads = q_heads + 2 * kv_heads;
+  return launch_pdl(qknorm_rope_cache_kernel, dim3((heads + 3) / 4), dim3(128), static_cast<cudaStream_t>(stream), "qknorm_rope_cache launch",
+                    u16(q), u16(k), u16(v), u16(q_weight), u16(k_weight), u16(cosv), u16(sinv), u16(q_out), u16(k_cache), u16(v_cache),
+                    q_heads, kv_heads, head_dim, position, max_positions, eps, dtype);
+}
+
+extern "C" int fb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, int q_heads, int kv_heads,
+                              int head_dim, int length, int max_positions, float scale, int dtype, fb_stream_t stream) {
+  if (!q || !k_cache || !v_cache || !out) return fail(FB_EINVAL, "fb_attn_decode: null pointer");
+  if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_attn_decode: dtype must be FB_F16 or FB_BF16");
+  if (head_dim != 128) return fail(FB_ELIMIT, "fb_attn_decode: head_dim must be 128");
+  if (q_heads < 1 || kv_heads < 1 || q_heads % kv_heads) return fail(FB_ELIMIT, "fb_attn_decode: q_heads must be a multiple of kv_heads");
+  if (length < 1 || length > max_positions) return fail(FB_ELIMIT, "fb_attn_decode: length %d outside 1..%d", length, max_positions);
+  if (!aligned(q, 8) || !aligned(k_cache, 8) || !aligned(v_cache, 8) || !aligned(out, 8)) return fail(FB_EINVAL, "fb_attn_decode: tensors must be 8-byte aligned");
+  return launch_pdl(attn_decode_kernel, dim3(q_heads), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode launch",
+                    u16(q), u16(k_cache), u16(v_cache), u16(out), q_heads, kv_heads, length, max_positions, scale, dtype);
+}
+
+extern "C" int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream) {
+  if (!gate || !up || !out) return fail(FB_EINVAL, "fb_silu_mul: null pointer");
+  if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_silu_mul: dtype must be FB_F16 or FB_BF16");
+  if (n < 1) return fail(FB_ELIMIT, "fb_silu_mul: n must be positive");
+  return launch_pdl(silu_mul_kernel, dim3((n + 255) / 256), dim3(256), static_cast<cudaStream_t>(stream), "silu_mul launch",
+                    u16(gate), u16(up), u16(out), n, dtype);
+}

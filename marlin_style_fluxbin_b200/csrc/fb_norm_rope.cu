@@ -20,6 +20,7 @@ __device__ __forceinline__ float round_to(float v, int dtype) {
 template <int LANES>
 __global__ void rmsnorm_kernel(const unsigned short* __restrict__ x, const unsigned short* __restrict__ weight,
                                unsigned short* __restrict__ out, int rows, int dim, float eps, int dtype) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int row = LANES == 32 ? (int)(blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32) : (int)blockIdx.x;
   const int t = LANES == 32 ? (int)(threadIdx.x & 31) : (int)threadIdx.x;
@@ -53,6 +54,7 @@ __global__ void rope_kernel(const unsigned short* __restrict__ q, const unsigned
                             const unsigned short* __restrict__ cosv, const unsigned short* __restrict__ sinv,
                             unsigned short* __restrict__ q_out, unsigned short* __restrict__ k_out,
                             int q_heads, int k_heads, int dim, int dtype) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int half = dim / 2;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -80,7 +82,7 @@ int launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
-  config.numAttrs = 1;
+  config.numAttrs = pdl_allowed() ? 1 : 0;
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
   if (err != cudaSuccess) return cuda_fail(err, what);
   return FB_OK;

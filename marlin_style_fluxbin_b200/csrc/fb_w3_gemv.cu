@@ -532,7 +532,7 @@ int launch(const W3Params& p, const Plan& plan, int max_smem, bool pdl, cudaStre
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
-  config.numAttrs = pdl ? 1 : 0;
+  config.numAttrs = pdl && pdl_allowed() ? 1 : 0;
   cudaError_t err = cudaLaunchKernelEx(&config, w3_gemv_kernel<M, CORRECT>, p);
   if (err != cudaSuccess) return cuda_fail(err, "w3_gemv_kernel launch");
   return FB_OK;

@@ -1,0 +1,308 @@
+"""Batch-1 Qwen3 decode engine on the packed W3 kernels: nine launches per layer, one CUDA graph.
+
+The reference drives an unmodified HF ``Qwen3ForCausalLM`` whose Linears were swapped
+(``static_decode.py:15-138``); that drop-in route is kept in ``static_decode.py`` here.  This
+engine is the B200-first route for the same decode step: fused q/k/v and gate/up GEMV launches,
+residual adds folded into the o/down GEMV epilogues, one kernel each for RMSNorm, q/k-norm +
+RoPE + KV-cache write, single-query attention and the SwiGLU gate, all chained with programmatic
+dependent launch and captured, for a whole continuation, in one CUDA graph.
+
+The same engine runs a BF16 arm (dense dequantised weights through cuBLAS, identical glue
+kernels), which is the same-box baseline the packed path is compared with, and shards itself
+tensor-parallel: q/k/v/gate/up by output rows, o/down by input groups, one NCCL sum-allreduce
+after each of the two row-split GEMVs of a layer.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+from torch.nn import functional as F
+
+from . import _native
+from .gptq_deployment import restore_planar_w3
+
+
+@dataclass(frozen=True)
+class ModelShape:
+    layers: int
+    hidden: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    intermediate: int
+    vocab: int
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+
+    @property
+    def q_width(self):
+        return self.q_heads * self.head_dim
+
+    @property
+    def kv_width(self):
+        return self.kv_heads * self.head_dim
+
+
+QWEN3_8B = ModelShape(36, 4096, 32, 8, 128, 12288, 151936)
+QWEN3_32B = ModelShape(64, 5120, 64, 8, 128, 25600, 151936)
+
+
+def synthetic_w3(out_features, in_features, device, generator):
+    """A W3 g128 Linear drawn as the benchmark configs state: uniform codes (uniform random
+    plane bytes), fp16 scales U(0.005, 0.02), zero points in {3, 4}, contiguous groups."""
+    groups = in_features // 128
+    return {
+        "planes": torch.randint(0, 256, (groups, 3, out_features, 16), dtype=torch.uint8, device=device, generator=generator),
+        "scales": (torch.rand(groups, out_features, device=device, generator=generator) * 0.015 + 0.005).half(),
+        "zeros": torch.randint(3, 5, (groups, out_features), dtype=torch.uint8, device=device, generator=generator),
+        "perm": torch.arange(in_features, dtype=torch.int16, device=device),
+    }
+
+
+def shard_rows(layout, rank, size):
+    """Column-parallel shard: a contiguous slice of the output rows (all groups)."""
+    o = layout["planes"].shape[2]
+    lo, hi = rank * o // size, (rank + 1) * o // size
+    return {"planes": layout["planes"][:, :, lo:hi].contiguous(), "scales": layout["scales"][:, lo:hi].contiguous(),
+            "zeros": layout["zeros"][:, lo:hi].contiguous(), "perm": layout["perm"]}
+
+
+def shard_groups(layout, rank, size):
+    """Row-parallel shard: a contiguous slice of the input groups (all output rows)."""
+    g = layout["planes"].shape[0]
+    lo, hi = rank * g // size, (rank + 1) * g // size
+    return {"planes": layout["planes"][lo:hi].contiguous(), "scales": layout["scales"][lo:hi].contiguous(),
+            "zeros": layout["zeros"][lo:hi].contiguous(), "perm": torch.arange((hi - lo) * 128, dtype=torch.int16, device=layout["perm"].device)}
+
+
+class _Layer:
+    __slots__ = ("q", "k", "v", "o", "gate", "up", "down", "ln1", "ln2", "q_norm", "k_norm", "dense", "qkv_list", "gu_list", "o_list", "down_list")
+
+
+class DecodeEngine:
+    """``arm`` is ``"w3"`` (packed kernels) or ``"bf16"`` (dense dequantised weights, cuBLAS)."""
+
+    def __init__(self, shape: ModelShape, *, device, max_positions: int, arm: str = "w3", seed: int = 20260916,
+                 tp_rank: int = 0, tp_size: int = 1, group=None, dtype=torch.bfloat16):
+        if arm not in ("w3", "bf16"):
+            raise ValueError("arm must be w3 or bf16")
+        if shape.q_heads % tp_size or shape.kv_heads % tp_size or (shape.hidden // 128) % tp_size or (shape.intermediate // 128) % tp_size:
+            raise ValueError("heads and group counts must divide by the tensor-parallel size")
+        self.shape, self.device, self.arm, self.dtype = shape, torch.device(device), arm, dtype
+        self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
+        self.max_positions = max_positions
+        s, p = shape, tp_size
+        self.q_heads, self.kv_heads = s.q_heads // p, s.kv_heads // p
+        self.inter = s.intermediate // p
+        gen = torch.Generator(device=self.device).manual_seed(seed)  # same stream of draws on every rank
+        normal = lambda *size: (torch.randn(*size, device=self.device, generator=gen) * 0.02).to(dtype)  # noqa: E731
+        self.embedding = normal(s.vocab, s.hidden)
+        self.lm_head = normal(s.vocab, s.hidden)
+        self.final_norm = torch.ones(s.hidden, device=self.device, dtype=dtype)
+        self.layers = []
+        for _ in range(s.layers):
+            layer = _Layer()
+            full = {name: synthetic_w3(o, k, self.device, gen) for name, o, k in (
+                ("q", s.q_width, s.hidden), ("k", s.kv_width, s.hidden), ("v", s.kv_width, s.hidden), ("o", s.hidden, s.q_width),
+                ("gate", s.intermediate, s.hidden), ("up", s.intermediate, s.hidden), ("down", s.hidden, s.intermediate))}
+            for name in ("q", "k", "v", "gate", "up"):
+                setattr(layer, name, shard_rows(full[name], tp_rank, p))
+            for name in ("o", "down"):
+                setattr(layer, name, shard_groups(full[name], tp_rank, p))
+            del full
+            layer.ln1 = torch.ones(s.hidden, device=self.device, dtype=dtype)
+            layer.ln2 = torch.ones(s.hidden, device=self.device, dtype=dtype)
+            layer.q_norm = torch.ones(s.head_dim, device=self.device, dtype=dtype)
+            layer.k_norm = torch.ones(s.head_dim, device=self.device, dtype=dtype)
+            layer.dense = self._dense(layer) if arm == "bf16" else None
+            self.layers.append(layer)
+        # rotary table, fp32 angles cast to the activation dtype (as the HF rotary module does)
+        inv_freq = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, device=self.device, dtype=torch.float32) / s.head_dim))
+        angles = torch.arange(max_positions, device=self.device, dtype=torch.float32)[:, None] * inv_freq[None, :]
+        angles = torch.cat((angles, angles), dim=-1)
+        self.cos, self.sin = angles.cos().to(dtype).contiguous(), angles.sin().to(dtype).contiguous()
+        self.k_cache = torch.zeros(s.layers, self.kv_heads, max_positions, s.head_dim, device=self.device, dtype=dtype)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        # activation buffers of one token
+        buf = lambda n: torch.zeros(1, n, device=self.device, dtype=dtype)  # noqa: E731
+        self.h, self.h_next, self.xn = buf(s.hidden), buf(s.hidden), buf(s.hidden)
+        self.q, self.k, self.v = buf(self.q_heads * s.head_dim), buf(self.kv_heads * s.head_dim), buf(self.kv_heads * s.head_dim)
+        self.q_rot, self.attn = buf(self.q_heads * s.head_dim), buf(self.q_heads * s.head_dim)
+        self.gate, self.up, self.act = buf(self.inter), buf(self.inter), buf(self.inter)
+        self.logits = torch.zeros(1, s.vocab, device=self.device, dtype=dtype)
+        self.next_token = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.launches_per_step = 0
+        if arm == "w3":
+            self._build_matrix_lists()
+
+    # ------------------------------------------------------------------ weights
+    def _dense(self, layer):
+        """Dequantised 16-bit weights of this rank's shards (fused q/k/v and gate/up)."""
+        d = lambda lay: restore_planar_w3(lay, dtype=self.dtype)  # noqa: E731
+        return {"qkv": torch.cat((d(layer.q), d(layer.k), d(layer.v)), 0), "o": d(layer.o),
+                "gate_up": torch.cat((d(layer.gate), d(layer.up)), 0), "down": d(layer.down)}
+
+    def _build_matrix_lists(self):
+        first = self.tp_rank == 0  # the residual is added by exactly one rank before the allreduce
+        for layer in self.layers:
+            entry = lambda lay, out, residual=None: (lay["planes"], lay["scales"], lay["zeros"], out, residual)  # noqa: E731
+            layer.qkv_list = _native.w3_matrix_list([entry(layer.q, self.q), entry(layer.k, self.k), entry(layer.v, self.v)])
+            layer.gu_list = _native.w3_matrix_list([entry(layer.gate, self.gate), entry(layer.up, self.up)])
+            layer.o_list = _native.w3_matrix_list([entry(layer.o, self.h_next, self.h if first else None)])
+            layer.down_list = _native.w3_matrix_list([entry(layer.down, self.h, self.h_next if first else None)])
+        need = max(_native.w3_scratch_bytes(1, 2 * self.inter, self.shape.hidden),
+                   _native.w3_scratch_bytes(1, self.shape.hidden, self.inter))
+        self.scratch = torch.zeros(need, dtype=torch.uint8, device=self.device)
+
+    # ------------------------------------------------------------------ collectives
+    def _allreduce(self, tensor):
+        if self.tp_size > 1:
+            torch.distributed.all_reduce(tensor, group=self.group)
+
+    # ------------------------------------------------------------------ prefill (dense, not timed)
+    @torch.inference_mode()
+    def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """Run the prompt through dense (dequantised) weights with plain tensor operations, fill
+        the KV cache for positions ``0..T-1`` and return the logits of the last position."""
+        s = self.shape
+        tokens = input_ids.reshape(-1).to(self.device)
+        t = tokens.numel()
+        if not 1 <= t < self.max_positions:
+            raise ValueError("prompt does not fit the KV cache")
+        h = self.embedding[tokens]
+        cos, sin = self.cos[:t].unsqueeze(0), self.sin[:t].unsqueeze(0)
+        rotate = lambda x: torch.cat((-x[..., s.head_dim // 2:], x[..., :s.head_dim // 2]), dim=-1)  # noqa: E731
+        norm = lambda x, w: (w * (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + s.eps)).to(self.dtype))  # noqa: E731
+        for index, layer in enumerate(self.layers):
+            dense = layer.dense if layer.dense is not None else self._dense(layer)
+            x = norm(h, layer.ln1)
+            qkv = F.linear(x, dense["qkv"])
+            q, k, v = qkv.split((self.q_heads * s.head_dim, self.kv_heads * s.head_dim, self.kv_heads * s.head_dim), dim=-1)
+            q = norm(q.reshape(t, self.q_heads, s.head_dim), layer.q_norm).transpose(0, 1)
+            k = norm(k.reshape(t, self.kv_heads, s.head_dim), layer.k_norm).transpose(0, 1)
+            v = v.reshape(t, self.kv_heads, s.head_dim).transpose(0, 1)
+            q = q * cos + rotate(q) * sin
+            k = k * cos + rotate(k) * sin
+            self.k_cache[index, :, :t] = k
+            self.v_cache[index, :, :t] = v
+            attn = F.scaled_dot_product_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), is_causal=True, enable_gqa=True)
+            y = F.linear(attn[0].transpose(0, 1).reshape(t, -1), dense["o"])
+            self._allreduce(y)
+            h = h + y
+            x = norm(h, layer.ln2)
+            gate, up = F.linear(x, dense["gate_up"]).split(self.inter, dim=-1)
+            y = F.linear(F.silu(gate) * up, dense["down"])
+            self._allreduce(y)
+            h = h + y
+            del dense
+        last = norm(h[-1:], self.final_norm)
+        return F.linear(last, self.lm_head)
+
+    # ------------------------------------------------------------------ one decode step
+    def _linear(self, layer, which, x):
+        """BF16 arm: cuBLAS on the dense shard.  Returns a new tensor."""
+        return F.linear(x, layer.dense[which])
+
+    @torch.inference_mode()
+    def step(self, token: torch.Tensor, position: int) -> None:
+        """Decode one token (``token``: device int64 ``[1]``) at ``position``; leaves the logits in
+        ``self.logits`` and the greedy choice in ``self.next_token``.  No allocation, no host sync."""
+        s, nat = self.shape, _native
+        w3 = self.arm == "w3"
+        f16 = torch.float16
+        torch.index_select(self.embedding, 0, token, out=self.h)
+        cos, sin = self.cos[position], self.sin[position]
+        scale = 1.0 / math.sqrt(s.head_dim)
+        launches = 1
+        for index, layer in enumerate(self.layers):
+            nat.rmsnorm(self.h, layer.ln1, self.xn, s.eps)
+            if w3:
+                nat.w3_gemv_multi(self.xn, layer.qkv_list, 3, self.q.numel() + 2 * self.k.numel(), f16, None, scratch=self.scratch)
+            else:
+                qkv = self._linear(layer, "qkv", self.xn)
+                self.q.copy_(qkv[:, :self.q.numel()])
+                self.k.copy_(qkv[:, self.q.numel():self.q.numel() + self.k.numel()])
+                self.v.copy_(qkv[:, self.q.numel() + self.k.numel():])
+                launches += 3
+            nat.qknorm_rope_cache(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.q_rot,
+                                  self.k_cache[index], self.v_cache[index], position, s.eps)
+            nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale)
+            if w3:
+                nat.w3_gemv_multi(self.attn, layer.o_list, 1, s.hidden, f16, None, scratch=self.scratch)
+            else:
+                torch.mm(self.attn, layer.dense["o"].t(), out=self.h_next)
+                if self.tp_rank == 0:
+                    self.h_next.add_(self.h)
+                    launches += 1
+            self._allreduce(self.h_next)
+            nat.rmsnorm(self.h_next, layer.ln2, self.xn, s.eps)
+            if w3:
+                nat.w3_gemv_multi(self.xn, layer.gu_list, 2, 2 * self.inter, f16, None, scratch=self.scratch)
+            else:
+                gu = self._linear(layer, "gate_up", self.xn)
+                self.gate.copy_(gu[:, :self.inter])
+                self.up.copy_(gu[:, self.inter:])
+                launches += 2
+            nat.silu_mul(self.gate, self.up, self.act)
+            if w3:
+                nat.w3_gemv_multi(self.act, layer.down_list, 1, s.hidden, f16, None, scratch=self.scratch)
+            else:
+                torch.mm(self.act, layer.dense["down"].t(), out=self.h)
+                if self.tp_rank == 0:
+                    self.h.add_(self.h_next)
+                    launches += 1
+            self._allreduce(self.h)
+            launches += 9 + (2 if self.tp_size > 1 else 0)
+        nat.rmsnorm(self.h, self.final_norm, self.xn, s.eps)
+        torch.mm(self.xn, self.lm_head.t(), out=self.logits)
+        torch.argmax(self.logits, dim=-1, out=self.next_token)
+        self.launches_per_step = launches + 3
+
+    # ------------------------------------------------------------------ whole continuation
+    @torch.inference_mode()
+    def decode(self, first_token: torch.Tensor, start: int, steps: int, forced: torch.Tensor | None = None):
+        """Eagerly decode ``steps`` tokens from ``start``; returns (tokens fed, greedy predictions, logits)."""
+        fed, predicted, logits = [], [], []
+        token = first_token.reshape(1).to(self.device)
+        for i in range(steps):
+            if forced is not None:
+                token = forced[i:i + 1].to(self.device)
+            fed.append(token.clone())
+            self.step(token, start + i)
+            predicted.append(self.next_token.clone())
+            logits.append(self.logits.clone())
+            token = self.next_token
+        return torch.cat(fed), torch.cat(predicted), torch.cat(logits)
+
+    @torch.inference_mode()
+    def capture(self, first_token: torch.Tensor, start: int, steps: int, forced: torch.Tensor | None = None):
+        """Capture the whole continuation in one CUDA graph (greedy feedback through a device
+        buffer, or teacher-forced tokens).  Returns ``(graph, predictions [steps], last logits)``;
+        replaying needs the KV cache prefix in place (later positions are simply overwritten)."""
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        self.token_in = first_token.reshape(1).to(self.device).clone()
+        forced_dev = None if forced is None else forced.to(self.device).clone()
+        predictions = torch.zeros(steps, dtype=torch.long, device=self.device)
+        # the graph holds raw addresses of these tensors: keep them alive as long as the engine
+        self._graph_inputs = getattr(self, "_graph_inputs", []) + [self.token_in, forced_dev, predictions]
+
+        def body():
+            token = self.token_in
+            for i in range(steps):
+                if forced_dev is not None:
+                    token = forced_dev[i:i + 1]
+                self.step(token, start + i)
+                predictions[i:i + 1].copy_(self.next_token)
+                token = self.next_token
+
+        with torch.cuda.stream(stream):
+            self.step(self.token_in, start)  # warm-up: kernel attributes, scratch, cuBLAS handles
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                body()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        return graph, predictions, self.logits
