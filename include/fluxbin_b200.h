@@ -168,15 +168,18 @@ int fb_rope_qk(const void* q, const void* k, const void* cosv, const void* sinv,
  *   and k (weights [D]), rotary embedding with cos/sin [D], rotated q to q_out, rotated k and v
  *   into k_cache / v_cache [kv_heads, max_positions, D] at `position`.
  * fb_attn_decode: softmax(q k^T * scale) v over cache positions 0..length-1, grouped-query heads,
- *   D = 128; out [q_heads, D].
+ *   D = 128; out [q_heads, D].  Positions are split over CTAs; `scratch` (fb_attn_decode_scratch_bytes,
+ *   zero-filled once, 16-byte aligned) holds the per-split partial results and one ticket per head.
  * fb_silu_mul: out[i] = T(silu(gate[i])) * up[i].
  */
 int fb_qknorm_rope_cache(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
                          const void* cosv, const void* sinv, void* q_out, void* k_cache, void* v_cache, int q_heads,
                          int kv_heads, int head_dim, int position, int max_positions, float eps, int dtype,
                          fb_stream_t stream);
+size_t fb_attn_decode_scratch_bytes(int q_heads);
 int fb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, int q_heads, int kv_heads,
-                   int head_dim, int length, int max_positions, float scale, int dtype, fb_stream_t stream);
+                   int head_dim, int length, int max_positions, float scale, int dtype, void* scratch,
+                   size_t scratch_bytes, fb_stream_t stream);
 int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream);
 
 /*

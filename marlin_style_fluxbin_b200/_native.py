@@ -74,7 +74,9 @@ def library() -> ctypes.CDLL:
         lib.fb_qknorm_rope_cache.restype = ctypes.c_int
         lib.fb_qknorm_rope_cache.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
         lib.fb_attn_decode.restype = ctypes.c_int
-        lib.fb_attn_decode.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_attn_decode.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        lib.fb_attn_decode_scratch_bytes.restype = ctypes.c_size_t
+        lib.fb_attn_decode_scratch_bytes.argtypes = [ctypes.c_int]
         lib.fb_silu_mul.restype = ctypes.c_int
         lib.fb_silu_mul.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         lib.fb_w3_gemv_static.restype = ctypes.c_int
@@ -263,11 +265,17 @@ def qknorm_rope_cache(q, k, v, q_weight, k_weight, cos, sin, q_out, k_cache, v_c
                                              k_cache.shape[-2], float(eps), dtype_tag(q.dtype), stream_handle(q.device)))
 
 
-def attn_decode(q, k_cache, v_cache, out, length: int, scale: float) -> None:
+def attn_scratch_bytes(q_heads: int) -> int:
+    return int(library().fb_attn_decode_scratch_bytes(q_heads))
+
+
+def attn_decode(q, k_cache, v_cache, out, length: int, scale: float, scratch) -> None:
+    """Single-query attention over cache positions ``0..length-1``; ``scratch``: zeroed uint8 buffer of ``attn_scratch_bytes``."""
     dim = k_cache.shape[-1]
     with torch.cuda.device(q.device):
         check(library().fb_attn_decode(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), q.numel() // dim, k_cache.shape[-3], dim,
-                                       int(length), k_cache.shape[-2], float(scale), dtype_tag(q.dtype), stream_handle(q.device)))
+                                       int(length), k_cache.shape[-2], float(scale), dtype_tag(q.dtype), ptr(scratch),
+                                       scratch.numel(), stream_handle(q.device)))
 
 
 def silu_mul(gate, up, out) -> None:

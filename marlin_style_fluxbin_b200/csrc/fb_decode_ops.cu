@@ -62,47 +62,79 @@ __global__ void qknorm_rope_cache_kernel(const unsigned short* __restrict__ q, c
   }
 }
 
-// One CTA (8 warps) per query head; warps stride over the cached positions with an online
-// softmax each, then merge.  head_dim 128: a lane holds four consecutive dims.
+// Single-query attention, split over the cached positions: grid (query heads, splits); a CTA
+// of 8 warps takes one contiguous chunk of positions, each warp four positions at a time (all
+// eight loads issued before any use) with an online softmax; the CTA's (max, sum, output) goes to
+// a scratch slot and the last CTA of a head (ticket) merges the splits in ascending order.
+// head_dim 128: a lane holds four consecutive dims.
 constexpr int kAttnWarps = 8;
+constexpr int kAttnMaxSplits = 16;
+constexpr int kAttnSlot = 132;  // 128 outputs + max + sum, padded
+
+__device__ __forceinline__ void unpack4(uint2 raw, int dtype, float* f) {
+  f[0] = bits_to_float((unsigned short)(raw.x & 0xffff), dtype);
+  f[1] = bits_to_float((unsigned short)(raw.x >> 16), dtype);
+  f[2] = bits_to_float((unsigned short)(raw.y & 0xffff), dtype);
+  f[3] = bits_to_float((unsigned short)(raw.y >> 16), dtype);
+}
+
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsigned short* __restrict__ q,
                                                                       const unsigned short* __restrict__ k_cache,
                                                                       const unsigned short* __restrict__ v_cache,
-                                                                      unsigned short* __restrict__ out, int q_heads, int kv_heads,
+                                                                      unsigned short* __restrict__ out, float* __restrict__ scratch,
+                                                                      unsigned* __restrict__ tickets, int q_heads, int kv_heads,
                                                                       int length, int max_positions, float scale, int dtype) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int D = 128;
-  const int head = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = head / (q_heads / kv_heads);
-  const unsigned short* kbase = k_cache + (size_t)kvh * max_positions * D;
-  const unsigned short* vbase = v_cache + (size_t)kvh * max_positions * D;
+  const unsigned short* kbase = k_cache + (size_t)kvh * max_positions * D + lane * 4;
+  const unsigned short* vbase = v_cache + (size_t)kvh * max_positions * D + lane * 4;
+  const int chunk = (length + splits - 1) / splits;
+  const int p0 = split * chunk, p1 = min(length, p0 + chunk);
   float qv[4];
-  {
-    const uint2 raw = *reinterpret_cast<const uint2*>(q + (size_t)head * D + lane * 4);
-    qv[0] = bits_to_float((unsigned short)(raw.x & 0xffff), dtype) * scale;
-    qv[1] = bits_to_float((unsigned short)(raw.x >> 16), dtype) * scale;
-    qv[2] = bits_to_float((unsigned short)(raw.y & 0xffff), dtype) * scale;
-    qv[3] = bits_to_float((unsigned short)(raw.y >> 16), dtype) * scale;
-  }
-  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int pos = warp; pos < length; pos += kAttnWarps) {
-    const uint2 kr = *reinterpret_cast<const uint2*>(kbase + (size_t)pos * D + lane * 4);
-    float s = qv[0] * bits_to_float((unsigned short)(kr.x & 0xffff), dtype) + qv[1] * bits_to_float((unsigned short)(kr.x >> 16), dtype) +
-              qv[2] * bits_to_float((unsigned short)(kr.y & 0xffff), dtype) + qv[3] * bits_to_float((unsigned short)(kr.y >> 16), dtype);
+  unpack4(*reinterpret_cast<const uint2*>(q + (size_t)head * D + lane * 4), dtype, qv);
 #pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-    const float m_new = fmaxf(m, s);
-    const float correction = __expf(m - m_new), p = __expf(s - m_new);
-    const uint2 vr = *reinterpret_cast<const uint2*>(vbase + (size_t)pos * D + lane * 4);
-    acc[0] = acc[0] * correction + p * bits_to_float((unsigned short)(vr.x & 0xffff), dtype);
-    acc[1] = acc[1] * correction + p * bits_to_float((unsigned short)(vr.x >> 16), dtype);
-    acc[2] = acc[2] * correction + p * bits_to_float((unsigned short)(vr.y & 0xffff), dtype);
-    acc[3] = acc[3] * correction + p * bits_to_float((unsigned short)(vr.y >> 16), dtype);
-    l = l * correction + p;
-    m = m_new;
+  for (int i = 0; i < 4; ++i) qv[i] *= scale;
+  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int base = p0 + warp * 4; base < p1; base += kAttnWarps * 4) {
+    uint2 kr[4], vr[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int pos = min(base + j, p1 - 1);
+      kr[j] = *reinterpret_cast<const uint2*>(kbase + (size_t)pos * D);
+      vr[j] = *reinterpret_cast<const uint2*>(vbase + (size_t)pos * D);
+    }
+    float s[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float kf[4];
+      unpack4(kr[j], dtype, kf);
+      s[j] = qv[0] * kf[0] + qv[1] * kf[1] + qv[2] * kf[2] + qv[3] * kf[3];
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], d);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (base + j < p1) {
+        const float m_new = fmaxf(m, s[j]);
+        const float correction = __expf(m - m_new), pj = __expf(s[j] - m_new);
+        float vf[4];
+        unpack4(vr[j], dtype, vf);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = acc[i] * correction + pj * vf[i];
+        l = l * correction + pj;
+        m = m_new;
+      }
+    }
   }
   __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps], sm_acc[kAttnWarps][D];
+  __shared__ unsigned last_flag;
   if (lane == 0) {
     sm_m[warp] = m;
     sm_l[warp] = l;
@@ -110,6 +142,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
   for (int i = 0; i < 4; ++i) sm_acc[warp][lane * 4 + i] = acc[i];
   __syncthreads();
+  float* slot = scratch + ((size_t)head * kAttnMaxSplits + split) * kAttnSlot;
   if (warp == 0) {
     float gm = -INFINITY;
 #pragma unroll
@@ -122,12 +155,36 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[i] += sm_acc[w][lane * 4 + i] * f;
     }
-    const float inv = 1.f / total;
-    uint2 packed;
-    packed.x = (uint32_t)to_bits(o[0] * inv, dtype) | ((uint32_t)to_bits(o[1] * inv, dtype) << 16);
-    packed.y = (uint32_t)to_bits(o[2] * inv, dtype) | ((uint32_t)to_bits(o[3] * inv, dtype) << 16);
-    *reinterpret_cast<uint2*>(out + (size_t)head * D + lane * 4) = packed;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) slot[lane * 4 + i] = o[i];
+    if (lane == 0) {
+      slot[128] = gm;
+      slot[129] = total;
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) last_flag = atomicAdd(&tickets[head], 1u) == (unsigned)splits - 1u;
   }
+  __syncthreads();
+  if (!last_flag || warp != 0) return;
+  __threadfence();
+  const float* base_slot = scratch + (size_t)head * kAttnMaxSplits * kAttnSlot;
+  float gm = -INFINITY;
+  for (int sp = 0; sp < splits; ++sp) gm = fmaxf(gm, __ldcg(base_slot + sp * kAttnSlot + 128));
+  float total = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int sp = 0; sp < splits; ++sp) {
+    const float sm = __ldcg(base_slot + sp * kAttnSlot + 128);
+    const float f = sm == -INFINITY ? 0.f : __expf(sm - gm);
+    total += __ldcg(base_slot + sp * kAttnSlot + 129) * f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] += __ldcg(base_slot + sp * kAttnSlot + lane * 4 + i) * f;
+  }
+  const float inv = 1.f / total;
+  uint2 packed;
+  packed.x = (uint32_t)to_bits(o[0] * inv, dtype) | ((uint32_t)to_bits(o[1] * inv, dtype) << 16);
+  packed.y = (uint32_t)to_bits(o[2] * inv, dtype) | ((uint32_t)to_bits(o[3] * inv, dtype) << 16);
+  *reinterpret_cast<uint2*>(out + (size_t)head * D + lane * 4) = packed;
+  if (lane == 0) tickets[head] = 0u;
 }
 
 __global__ void silu_mul_kernel(const unsigned short* __restrict__ gate, const unsigned short* __restrict__ up,
@@ -176,16 +233,28 @@ extern "C" int fb_qknorm_rope_cache(const void* q, const void* k, const void* v,
                     q_heads, kv_heads, head_dim, position, max_positions, eps, dtype);
 }
 
+extern "C" size_t fb_attn_decode_scratch_bytes(int q_heads) {
+  if (q_heads < 1) return 0;
+  return (size_t)q_heads * kAttnMaxSplits * kAttnSlot * sizeof(float) + (size_t)q_heads * sizeof(unsigned);
+}
+
 extern "C" int fb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, int q_heads, int kv_heads,
-                              int head_dim, int length, int max_positions, float scale, int dtype, fb_stream_t stream) {
+                              int head_dim, int length, int max_positions, float scale, int dtype, void* scratch,
+                              size_t scratch_bytes, fb_stream_t stream) {
   if (!q || !k_cache || !v_cache || !out) return fail(FB_EINVAL, "fb_attn_decode: null pointer");
   if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_attn_decode: dtype must be FB_F16 or FB_BF16");
   if (head_dim != 128) return fail(FB_ELIMIT, "fb_attn_decode: head_dim must be 128");
   if (q_heads < 1 || kv_heads < 1 || q_heads % kv_heads) return fail(FB_ELIMIT, "fb_attn_decode: q_heads must be a multiple of kv_heads");
   if (length < 1 || length > max_positions) return fail(FB_ELIMIT, "fb_attn_decode: length %d outside 1..%d", length, max_positions);
   if (!aligned(q, 8) || !aligned(k_cache, 8) || !aligned(v_cache, 8) || !aligned(out, 8)) return fail(FB_EINVAL, "fb_attn_decode: tensors must be 8-byte aligned");
-  return launch_pdl(attn_decode_kernel, dim3(q_heads), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode launch",
-                    u16(q), u16(k_cache), u16(v_cache), u16(out), q_heads, kv_heads, length, max_positions, scale, dtype);
+  const size_t need = fb_attn_decode_scratch_bytes(q_heads);
+  if (!scratch || scratch_bytes < need || !aligned(scratch, 16)) return fail(FB_ESCRATCH, "fb_attn_decode: 16-byte aligned scratch of %zu bytes needed", need);
+  int splits = (length + 63) / 64;  // about 64 positions per CTA
+  if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
+  float* partial = static_cast<float*>(scratch);
+  unsigned* tickets = reinterpret_cast<unsigned*>(partial + (size_t)q_heads * kAttnMaxSplits * kAttnSlot);
+  return launch_pdl(attn_decode_kernel, dim3(q_heads, splits), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode launch",
+                    u16(q), u16(k_cache), u16(v_cache), u16(out), partial, tickets, q_heads, kv_heads, length, max_positions, scale, dtype);
 }
 
 extern "C" int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream) {

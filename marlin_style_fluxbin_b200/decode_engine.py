@@ -134,6 +134,7 @@ class DecodeEngine:
         self.logits = torch.zeros(1, s.vocab, device=self.device, dtype=dtype)
         self.next_token = torch.zeros(1, dtype=torch.long, device=self.device)
         self.launches_per_step = 0
+        self.attn_scratch = torch.zeros(_native.attn_scratch_bytes(self.q_heads), dtype=torch.uint8, device=self.device)
         if arm == "w3":
             self._build_matrix_lists()
 
@@ -228,7 +229,7 @@ class DecodeEngine:
                 launches += 3
             nat.qknorm_rope_cache(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.q_rot,
                                   self.k_cache[index], self.v_cache[index], position, s.eps)
-            nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale)
+            nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale, self.attn_scratch)
             if w3:
                 nat.w3_gemv_multi(self.attn, layer.o_list, 1, s.hidden, f16, None, scratch=self.scratch)
             else:
@@ -281,13 +282,14 @@ class DecodeEngine:
         """Capture the whole continuation in one CUDA graph (greedy feedback through a device
         buffer, or teacher-forced tokens).  Returns ``(graph, predictions [steps], last logits)``;
         replaying needs the KV cache prefix in place (later positions are simply overwritten)."""
-        stream = torch.cuda.Stream(self.device)
-        stream.wait_stream(torch.cuda.current_stream(self.device))
         self.token_in = first_token.reshape(1).to(self.device).clone()
         forced_dev = None if forced is None else forced.to(self.device).clone()
         predictions = torch.zeros(steps, dtype=torch.long, device=self.device)
         # the graph holds raw addresses of these tensors: keep them alive as long as the engine
         self._graph_inputs = getattr(self, "_graph_inputs", []) + [self.token_in, forced_dev, predictions]
+        # the side stream must see the tensors above initialised: order it after the current stream now
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
 
         def body():
             token = self.token_in
