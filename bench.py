@@ -200,6 +200,60 @@ def run_ours(args, rank, world, local_rank):
     }
 
 
+def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=("bf16", "w3"), repeats=5):
+    """Full-model batch-1 decode (BASELINE.json configs[3] / [4]): random-init Qwen3 shape, all Linears
+    W3 g128, LM head bf16; prefill `prompt` random ids, then `steps` tokens from ONE CUDA graph.  The
+    BF16 arm runs the same engine with dense dequantised weights through cuBLAS.  Tensor parallel
+    over `world` ranks when world > 1."""
+    from marlin_style_fluxbin_b200.decode_engine import QWEN3_8B, QWEN3_32B, DecodeEngine
+
+    shape = {"qwen3-8b": QWEN3_8B, "qwen3-32b": QWEN3_32B}[shape_name]
+    device = torch.device("cuda", local_rank)
+    ids = torch.randint(0, shape.vocab, (1, prompt), generator=torch.Generator().manual_seed(1))
+    out, forced, reference = {}, None, None
+    for arm in arms:
+        engine = DecodeEngine(shape, device=device, max_positions=prompt + steps + 8, arm=arm,
+                              tp_rank=rank, tp_size=world)
+        first = engine.prefill(ids).argmax(-1)
+        fed, greedy, logits = engine.decode(first, prompt, steps, forced=forced)
+        engine.prefill(ids)
+        graph, predictions, _ = engine.capture(first, prompt, steps, forced=forced)
+        engine.prefill(ids)
+        graph.replay()
+        torch.cuda.synchronize(device)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        times = []
+        for _ in range(repeats):
+            if world > 1:
+                torch.distributed.barrier()
+            begin.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize(device)
+            times.append(begin.elapsed_time(end))
+        ms = sorted(times)[len(times) // 2]
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t[0])
+        entry = {"tokens_per_s": round(steps / ms * 1e3, 1), "ms_per_token": round(ms / steps, 4),
+                 "launches_per_token": engine.launches_per_step, "graph_equals_eager": bool(torch.equal(predictions, greedy))}
+        if forced is None:
+            forced, reference = fed, (greedy, logits)
+        else:
+            a, b = logits.double(), reference[1].double()
+            entry["greedy_agreement_forced"] = round(float((greedy == reference[0]).float().mean()), 4)
+            entry["logits_nrmse_vs_bf16_arm"] = round(float((a - b).square().mean().sqrt() / b.square().mean().sqrt()), 5)
+        out[arm] = entry
+        del engine, graph
+        torch.cuda.empty_cache()
+    if "w3" in out and "bf16" in out:
+        out["w3_over_bf16"] = round(out["w3"]["tokens_per_s"] / out["bf16"]["tokens_per_s"], 3)
+    out["config"] = {"model": shape_name, "prompt_tokens": prompt, "decode_tokens": steps, "tensor_parallel": world,
+                     "graph": "whole continuation, teacher-forced from the bf16 arm's greedy tokens"}
+    return out
+
+
 def cpu_reference(steps: int, warmup: int):
     """The reference's CPU path (dequantise, then fp32 matmul) restated in the oracle, timed
     on the host cores over ONE layer's seven Linears per step (a bounded sample)."""
@@ -262,6 +316,8 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--workload", default="gemv", choices=("gemv", "decode-8b", "tp-decode-32b"),
+                        help="gemv (default): the seven Linear shapes plus the 8B decode; tp-decode-32b: tensor-parallel decode over --gpus ranks")
     parser.add_argument("--case", default=None, metavar="OxK",
                         help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
     parser.add_argument("--copies", type=int, default=8)
@@ -298,7 +354,22 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the packed kernels have no CPU path")
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.workload == "tp-decode-32b":
+        torch.cuda.set_device(local_rank)
+        decode = run_decode(torch, "qwen3-32b", 1024, 64, rank, world, local_rank, arms=("w3",) if world > 1 else ("bf16", "w3"))
+        if rank == 0:
+            print(json.dumps({"metric": "batch-1 decode tokens/s, Qwen3-32B-shaped W3 g128, tensor parallel", "unit": "tokens/s",
+                              "value": decode["w3"]["tokens_per_s"], "n_gpus": world, "higher_is_better": True, "scaling": "strong",
+                              "data": "synthetic", "dtype": "f32", "decode": decode}))
+        if world > 1:
+            torch.distributed.barrier()
+            torch.distributed.destroy_process_group()
+        return
     result = run_ours(args, rank, world, local_rank)
+    decode = None
+    if world == 1:
+        torch.cuda.empty_cache()
+        decode = run_decode(torch, "qwen3-8b", 512, 32, 0, 1, local_rank)
     if rank == 0:
         peak, peak_kind = measured_peak()
         total_bytes = result["step_bytes"] * world
@@ -326,6 +397,8 @@ def main():
         # algorithmic (profiles/w3_gemv_12288x4096_m1.md); traffic grows with the bytes a launch
         # streams, so the average launch of this mixed-shape step is scaled by the same ratio.
         line["roofline"]["traffic"] = int(DRAM_TRAFFIC_RATIO * line["roofline"]["bytes_per_launch_avg"])
+        if decode is not None:
+            line["decode"] = decode
         if cpu is not None:
             line["cpu_baseline"] = {"value": round(cpu["value"], 3), "unit": "GB/s", "cores": cpu["cores"], "kind": "port", "sample": cpu["sample"]}
         print(json.dumps(line))
