@@ -72,7 +72,7 @@ size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_features);
  *   perm    int16 [K] sorted position -> input column (desc_act), or NULL for identity
  * W[o, perm[k]] = scale[k/128, o] * (code - zero); accumulation in fp32; the split over
  * K is reduced inside the kernel in a fixed order, so results are repeat-exact.
- * M = 1..4.  O % 32 == 0, G <= 255 (K <= 32640), O <= 65536; x, planes 16-byte aligned.
+ * M = 1..4.  O % 32 == 0, G <= 255 (K <= 32640), O <= 65536; x, planes, scales, zeros 16-byte aligned.
  *
  * Replaces the reference's pybind entry points inline_main + finish and m1_out
  * (csrc/w3_lut.cu:251-332) and their launchers (:153-189).

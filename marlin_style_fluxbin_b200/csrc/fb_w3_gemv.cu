@@ -61,7 +61,10 @@ constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
 constexpr int kWarps = 8;
 constexpr int kCtasPerSm = 2;
 constexpr int kRing = 3;                           // waves staged per CTA
-constexpr int kWaveBytes = kWarps * kUnitBytes;    // 24 KB: one unit per warp
+constexpr int kWavePlanes = kWarps * kUnitBytes;   // 24 KB of bit planes: one unit per warp
+constexpr int kWaveScales = 2 * kWarps * kUnitRows * 2;  // 1 KB: 16-bit scales of two groups
+constexpr int kWaveZeros = 2 * kWarps * kUnitRows;       // 512 B: zero points of two groups
+constexpr int kWaveBytes = kWavePlanes + kWaveScales + kWaveZeros;
 constexpr int kMaxM = 4;
 
 constexpr int kMaxMatrices = 4;
@@ -104,18 +107,6 @@ struct LutGeom {
   static constexpr int kBytes = 256 << kStrideLog;
 };
 
-// acc.{lo,hi} += {a, b} with one packed fp32x2 add
-__device__ __forceinline__ void add_pair(unsigned long long& acc, float a, float b) {
-  unsigned long long v;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(a), "f"(b));
-  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc) : "l"(v));
-}
-__device__ __forceinline__ float pair_sum(unsigned long long acc) {
-  float lo, hi;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc));
-  return lo + hi;
-}
-
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -135,25 +126,28 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   // The next kernel in the stream may start its own prologue (weight prefetch) now; it
   // orders itself after this grid with its own wait before touching activations or scratch.
   pdl_launch_dependents();
+  FB_MARK(10);
 
   const int nV = p.nKB * p.ctas_per_kb;
   if ((int)blockIdx.x >= nV) return;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRing; ++s) {
-      mbar_init(smem_u32(&full_bars[s]), 6);        // six issuing lanes, one per (half, plane)
+      mbar_init(smem_u32(&full_bars[s]), kWarps);   // every warp's lane 0 issues part of a wave
       mbar_init(smem_u32(&empty_bars[s]), kWarps);  // every warp releases a wave after reading it
     }
     mbar_init_fence();
   }
   __syncthreads();
+  FB_MARK(11);
 
   // Work of virtual CTA v: K block v / c, the row units [first, first + count) of slice v % c.
   auto share = [&](int v, int& kb, int& first, int& count) {
-    kb = v / p.ctas_per_kb;
+    kb = (int)((unsigned)v / (unsigned)p.ctas_per_kb);
     const int slice = v - kb * p.ctas_per_kb;
-    first = (int)((long long)slice * p.nRU / p.ctas_per_kb);
-    count = (int)((long long)(slice + 1) * p.nRU / p.ctas_per_kb) - first;
+    // 32-bit arithmetic on purpose (slice * nRU < 2^21): 64-bit division is slow on the GPU
+    first = (int)((unsigned)(slice * p.nRU) / (unsigned)p.ctas_per_kb);
+    count = (int)((unsigned)((slice + 1) * p.nRU) / (unsigned)p.ctas_per_kb) - first;
   };
   // Matrix that owns 32-row unit `ru` of the concatenated row space.
   auto locate = [&](int ru) {
@@ -166,24 +160,56 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   // block kb.  Lane 0 of warps 0..5 each copy one (half, plane); a slot is reused only after
   // all warps have released the wave that occupied it.
   auto issue_wave = [&](int seq, int kb, int first, int n) {
-    if (warp < 6 && lane == 0) {
+    if (lane == 0) {
       const int slot = seq % kRing;
       if (seq >= kRing && !mbar_wait_bounded(smem_u32(&empty_bars[slot]), (uint32_t)((seq / kRing - 1) & 1)))
         atomicExch(p.status, 2u);
-      const bool present = warp < 3 * min(2, p.G - 2 * kb);
+      const int ngroups = min(2, p.G - 2 * kb);
       const uint32_t bar = smem_u32(&full_bars[slot]);
-      mbar_expect_tx(bar, present ? (uint32_t)(n * kPlaneTile) : 0u);
-      uint32_t dst = smem_u32(ring + (size_t)slot * kWaveBytes + (size_t)warp * kWarps * kPlaneTile);
-      while (present && n > 0) {  // one copy per matrix the wave touches
-        const int j = locate(first);
-        const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
-        const int run = min(n, end - first);
-        const uint8_t* src = p.mats[j].planes +
-                             (((size_t)(2 * kb) * 3 + warp) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * 16;
-        bulk_g2s(dst, src, (uint32_t)(run * kPlaneTile), bar);
-        dst += run * kPlaneTile;
-        first += run;
-        n -= run;
+      const uint32_t slot_u32 = smem_u32(ring + (size_t)slot * kWaveBytes);
+      if (warp < 6) {  // bit planes: warp = group half * 3 + plane
+        const bool present = warp < 3 * ngroups;
+        mbar_expect_tx(bar, present ? (uint32_t)(n * kPlaneTile) : 0u);
+        uint32_t dst = slot_u32 + (uint32_t)(warp * kWarps * kPlaneTile);
+        while (present && n > 0) {  // one copy per matrix the wave touches
+          const int j = locate(first);
+          const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
+          const int run = min(n, end - first);
+          const uint8_t* src = p.mats[j].planes +
+                               (((size_t)(2 * kb) * 3 + warp) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * 16;
+          bulk_g2s(dst, src, (uint32_t)(run * kPlaneTile), bar);
+          dst += run * kPlaneTile;
+          first += run;
+          n -= run;
+        }
+      } else {  // warp 6: the scales of both groups, warp 7: their zero points (if any)
+        const int elem = warp == 6 ? 2 : 1;  // bytes per row
+        uint32_t bytes = 0;
+        for (int u = first, left = n; left > 0;) {
+          const int j = locate(u);
+          const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
+          const int run = min(left, end - u);
+          if (warp == 6 || p.mats[j].zeros) bytes += (uint32_t)(ngroups * run * kUnitRows * elem);
+          u += run;
+          left -= run;
+        }
+        mbar_expect_tx(bar, bytes);
+        uint32_t dst = slot_u32 + (uint32_t)(warp == 6 ? kWavePlanes : kWavePlanes + kWaveScales);
+        while (n > 0) {
+          const int j = locate(first);
+          const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
+          const int run = min(n, end - first);
+          const unsigned char* base = warp == 6 ? reinterpret_cast<const unsigned char*>(p.mats[j].scales) : p.mats[j].zeros;
+          if (base) {
+            for (int h = 0; h < ngroups; ++h)
+              bulk_g2s(dst + (uint32_t)(h * kWarps * kUnitRows * elem),
+                       base + ((size_t)(2 * kb + h) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * elem,
+                       (uint32_t)(run * kUnitRows * elem), bar);
+          }
+          dst += run * kUnitRows * elem;
+          first += run;
+          n -= run;
+        }
       }
     }
   };
@@ -199,18 +225,33 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
 
   // Lane rotation (byte, half, word): at every step the 32 lanes hit 32 different tables.
   const int rb = lane & 3, rh = (lane >> 2) & 1, rw = (lane >> 3) & 3;
-  // Rotation amounts and table offsets, fixed per lane.
-  uint32_t rot[4], xoff[2][4][4];
+  // Per-lane constants of the rotated walk, all as 32-bit shared-memory addresses / offsets so
+  // that the hot loop does no 64-bit pointer arithmetic.  A lookup is: byte-permute (weight byte
+  // to the low byte), one integer multiply-add (entry * stride + table address, on the FMA
+  // pipe, which keeps the half-rate integer ALU pipe nearly idle), the shared-memory load, one add.
+  const uint32_t lut_u32 = smem_u32(lut), ring_u32 = smem_u32(ring);
+  uint32_t sel[4], xl[2][4][4], woff[2][4];
 #pragma unroll
-  for (int b = 0; b < 4; ++b) rot[b] = (uint32_t)((8 * ((b + rb) & 3) - Geom::kStrideLog) & 31);
-  constexpr uint32_t kEntryMask = 0xffu << Geom::kStrideLog;
-  auto entry_address = [&](uint32_t word, int b, uint32_t offset) { return (__funnelshift_r(word, word, rot[b]) & kEntryMask) | offset; };
+  for (int b = 0; b < 4; ++b) sel[b] = 0x4440u | (uint32_t)((b + rb) & 3);  // byte (b+rb)%4 of a, zeros above
 #pragma unroll
   for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
-    for (int jw = 0; jw < 4; ++jw)
+    for (int jw = 0; jw < 4; ++jw) {
+      woff[jh][jw] = (uint32_t)(((jh ^ rh) * 3) * kWarps * kPlaneTile + ((jw + rw) & 3) * 4);
 #pragma unroll
-      for (int b = 0; b < 4; ++b) xoff[jh][jw][b] = (uint32_t)(64 * (jh ^ rh) + 16 * ((jw + rw) & 3) + 4 * ((b + rb) & 3));
+      for (int b = 0; b < 4; ++b)
+        xl[jh][jw][b] = lut_u32 + (uint32_t)(64 * (jh ^ rh) + 16 * ((jw + rw) & 3) + 4 * ((b + rb) & 3));
+    }
+  auto lookup_address = [&](uint32_t word, int b, uint32_t table) {
+    uint32_t entry = __byte_perm(word, 0u, sel[b]), address;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(address) : "r"(entry), "n"(Geom::kStride), "r"(table));
+    return address;
+  };
+  auto lds_f32 = [](uint32_t address) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address));
+    return v;
+  };
   auto table_of = [&](int m) { return lut + m * 128; };
 
   bool first_pass = true;
@@ -218,6 +259,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
 
   int kb, cta_first, cta_count;
   share((int)blockIdx.x, kb, cta_first, cta_count);
+  FB_MARK(12);
   for (int w = 0; w < kRing && w * kWarps < cta_count; ++w)  // weights never change: no need to wait
     issue_wave(w, kb, cta_first + w * kWarps, min(kWarps, cta_count - w * kWarps));
   FB_MARK(1);
@@ -305,28 +347,30 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       const int row = ru * kUnitRows + lane;  // in the concatenated row space
       const W3Matrix& mat = p.mats[locate(ru)];
       const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
-      // scale / zero loads first: their latency overlaps the wait below
-      unsigned short sbitsA = 0, sbitsB = 0;
-      float zcA = 0.f, zcB = 0.f;
-      if (mine) {
-        sbitsA = mat.scales[(size_t)gA * mat.O + lrow];
-        if (hasB) sbitsB = mat.scales[(size_t)gB * mat.O + lrow];
-        if (mat.zeros) {
-          zcA = 4.f - (float)mat.zeros[(size_t)gA * mat.O + lrow];
-          if (hasB) zcB = 4.f - (float)mat.zeros[(size_t)gB * mat.O + lrow];
-        }
-      }
-
       bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[slot]), (uint32_t)((seq / kRing) & 1));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && !dead) {
         dead = true;
         if (lane == 0) atomicExch(p.status, 1u);
       }
+      // scales and zero points of this unit were staged with the wave
+      unsigned short sbitsA = 0, sbitsB = 0;
+      float zcA = 0.f, zcB = 0.f;
+      if (mine && !dead) {
+        const unsigned char* side = ring + (size_t)slot * kWaveBytes + kWavePlanes;
+        const unsigned short* sc = reinterpret_cast<const unsigned short*>(side) + warp * kUnitRows + lane;
+        sbitsA = sc[0];
+        if (hasB) sbitsB = sc[kWarps * kUnitRows];
+        if (mat.zeros) {
+          const unsigned char* zp = side + kWaveScales + warp * kUnitRows + lane;
+          zcA = 4.f - (float)zp[0];
+          if (hasB) zcB = 4.f - (float)zp[kWarps * kUnitRows];
+        }
+      }
       FB_MARK(4);
 
-      // per activation row, group half and plane: a pair of partial sums (even / odd byte steps)
-      unsigned long long acc2[M][2][3];
+      // per activation row, group half and plane: two partial sums (even / odd byte steps)
+      float acc2[M][2][3][2];
       float corr[M][2];
 #pragma unroll
       for (int m = 0; m < M; ++m)
@@ -334,67 +378,69 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         for (int jh = 0; jh < 2; ++jh) {
           corr[m][jh] = 0.f;
 #pragma unroll
-          for (int pl = 0; pl < 3; ++pl) acc2[m][jh][pl] = 0ull;
+          for (int pl = 0; pl < 3; ++pl) acc2[m][jh][pl][0] = acc2[m][jh][pl][1] = 0.f;
         }
 
-      if (!dead && mine) {
-        const unsigned char* const buf = ring + (size_t)slot * kWaveBytes + warp * kPlaneTile + lane * 16;
+#ifndef FB_W3_ABLATE
+#define FB_W3_ABLATE 0
+#endif
+      if (!dead && mine && !(FB_W3_ABLATE & 1)) {
+        const uint32_t wbase = ring_u32 + (uint32_t)(slot * kWaveBytes + warp * kPlaneTile + lane * 16);
+        // staged words are fetched one (half, word) step ahead of their use: six live registers
+        auto fetch = [&](int jh, int jw, uint32_t (&dst)[3]) {
+          const uint32_t wa = wbase + woff[jh][jw];
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(dst[0]) : "r"(wa));
+          asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[1]) : "r"(wa), "n"(kWarps * kPlaneTile));
+          asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[2]) : "r"(wa), "n"(2 * kWarps * kPlaneTile));
+        };
+        uint32_t cur[3], nxt[3];
+        fetch(0, 0, cur);
 #pragma unroll
-        for (int jh = 0; jh < 2; ++jh) {
-          const int h = jh ^ rh;
+        for (int step = 0; step < 8; ++step) {
+          const int jh = step >> 2, jw = step & 3;
+          if (step + 1 < 8) fetch((step + 1) >> 2, (step + 1) & 3, nxt);
+          uint32_t plus3 = 0, minus3 = 0;
+          if (CORRECT) {
+            plus3 = cur[0] & cur[1] & ~cur[2];   // code 7 (stored high plane is inverted)
+            minus3 = cur[0] & ~cur[1] & cur[2];  // code 1
+          }
 #pragma unroll
-          for (int jw = 0; jw < 4; ++jw) {
-            const int ws = (jw + rw) & 3;
-            const unsigned char* wp = buf + (h * 3) * kWarps * kPlaneTile + ws * 4;
-            uint32_t w[3];
+          for (int b = 0; b < 4; ++b) {
 #pragma unroll
-            for (int pl = 0; pl < 3; ++pl) w[pl] = *reinterpret_cast<const uint32_t*>(wp + pl * kWarps * kPlaneTile);
-            uint32_t plus3 = 0, minus3 = 0;
-            if (CORRECT) {
-              plus3 = w[0] & w[1] & ~w[2];   // code 7 (stored high plane is inverted)
-              minus3 = w[0] & ~w[1] & w[2];  // code 1
+            for (int pl = 0; pl < 3; ++pl) {
+              const uint32_t a = lookup_address(cur[pl], b, xl[jh][jw][b]);
+#pragma unroll
+              for (int m = 0; m < M; ++m) acc2[m][jh][pl][b & 1] += lds_f32(a + m * 128);
             }
+            if (CORRECT) {
+              const uint32_t ap = lookup_address(plus3, b, xl[jh][jw][b]);
+              const uint32_t am = lookup_address(minus3, b, xl[jh][jw][b]);
 #pragma unroll
-            for (int b = 0; b < 4; b += 2) {
-#pragma unroll
-              for (int pl = 0; pl < 3; ++pl) {
-                const uint32_t a0 = entry_address(w[pl], b, xoff[jh][jw][b]);
-                const uint32_t a1 = entry_address(w[pl], b + 1, xoff[jh][jw][b + 1]);
-#pragma unroll
-                for (int m = 0; m < M; ++m)
-                  add_pair(acc2[m][jh][pl], *reinterpret_cast<const float*>(table_of(m) + a0),
-                           *reinterpret_cast<const float*>(table_of(m) + a1));
-              }
-              if (CORRECT) {
-#pragma unroll
-                for (int bb = b; bb < b + 2; ++bb) {
-                  const uint32_t ap = entry_address(plus3, bb, xoff[jh][jw][bb]);
-                  const uint32_t am = entry_address(minus3, bb, xoff[jh][jw][bb]);
-#pragma unroll
-                  for (int m = 0; m < M; ++m)
-                    corr[m][jh] += *reinterpret_cast<const float*>(table_of(m) + ap) - *reinterpret_cast<const float*>(table_of(m) + am);
-                }
-              }
+              for (int m = 0; m < M; ++m) corr[m][jh] += lds_f32(ap + m * 128) - lds_f32(am + m * 128);
             }
           }
+#pragma unroll
+          for (int pl = 0; pl < 3; ++pl) cur[pl] = nxt[pl];
         }
       }
       FB_MARK(5);
 
-      // all lanes are done with the staged bytes: release the wave; when every warp has,
-      // the issuing lanes refill the slot with a later wave
+      // all lanes are done with the staged bytes: release the wave.  The slot released one
+      // iteration AGO is refilled now: by this time the other warps have normally released it
+      // too, so the issuing lanes do not stall on the slowest warp of the current wave.
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bars[slot])) : "memory");
-      if (!dead && (i + kRing) * kWarps < cta_count)
-        issue_wave(seq + kRing, kb, cta_first + (i + kRing) * kWarps, min(kWarps, cta_count - (i + kRing) * kWarps));
+      if (!dead && i >= 1 && (i - 1 + kRing) * kWarps < cta_count)
+        issue_wave(seq - 1 + kRing, kb, cta_first + (i - 1 + kRing) * kWarps, min(kWarps, cta_count - (i - 1 + kRing) * kWarps));
 
       if (!dead && mine) {
         const float sA = bits_to_float(sbitsA, p.scale_dtype);
         const float sB = bits_to_float(sbitsB, p.scale_dtype);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          const float first = pair_sum(acc2[m][0][0]) + 2.f * pair_sum(acc2[m][0][1]) - 4.f * pair_sum(acc2[m][0][2]);
-          const float second = pair_sum(acc2[m][1][0]) + 2.f * pair_sum(acc2[m][1][1]) - 4.f * pair_sum(acc2[m][1][2]);
+          auto plane_sum = [&](int jh, int pl) { return acc2[m][jh][pl][0] + acc2[m][jh][pl][1]; };
+          const float first = plane_sum(0, 0) + 2.f * plane_sum(0, 1) - 4.f * plane_sum(0, 2);
+          const float second = plane_sum(1, 0) + 2.f * plane_sum(1, 1) - 4.f * plane_sum(1, 2);
           float dA = rh ? second : first, dB = rh ? first : second;
           if (mat.zeros) {
             dA += zcA * __shfl_sync(0xffffffffu, sx_m[m], 0);
@@ -423,6 +469,9 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         }
       }
     }
+    // the refill that the last iteration would have issued one step later
+    if (!dead && waves >= 1 && (waves - 1 + kRing) * kWarps < cta_count)
+      issue_wave(seq_base + waves - 1 + kRing, kb, cta_first + (waves - 1 + kRing) * kWarps, min(kWarps, cta_count - (waves - 1 + kRing) * kWarps));
     seq_base += waves;
   }
 
@@ -444,40 +493,27 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
         __syncwarp();
         FB_MARK(7);
-        // Units whose last ticket this warp drew are reduced four at a time so that their
-        // L2 round trips overlap; each row's partials are still summed in ascending K order.
-        const unsigned mine = __ballot_sync(0xffffffffu, my_ru >= 0 && prior == (unsigned)p.nKB - 1u);
-        unsigned todo = mine;
+        // Units whose last ticket this warp drew: sixteen partial loads in flight at a time
+        // (one L2 round trip for K <= 4096); the sum is still taken in ascending K order.
+        unsigned todo = __ballot_sync(0xffffffffu, my_ru >= 0 && prior == (unsigned)p.nKB - 1u);
         while (todo) {
-          int rows[4], owner[4];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            if (todo) {
-              const int j = __ffs(todo) - 1;
-              todo &= todo - 1;
-              const int ru = cta_first + (base + j) * kWarps + warp;
-              rows[t] = ru * kUnitRows + lane;
-              owner[t] = locate(ru);
-            } else {
-              rows[t] = -1;
-              owner[t] = 0;
-            }
-          }
+          const int j = __ffs(todo) - 1;
+          todo &= todo - 1;
+          const int ru = cta_first + (base + j) * kWarps + warp;
+          const W3Matrix& owner = p.mats[locate(ru)];
+          const int row = ru * kUnitRows + lane;
 #pragma unroll
           for (int m = 0; m < M; ++m) {
-            float total[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-            for (int k2 = 0; k2 < p.nKB; ++k2) {
-              float part[4];
+            float total = 0.f;
+            for (int k0 = 0; k0 < p.nKB; k0 += 16) {
+              float part[16];
 #pragma unroll
-              for (int t = 0; t < 4; ++t)
-                part[t] = rows[t] >= 0 ? __ldcg(&p.partials[((size_t)k2 * M + m) * p.O + rows[t]]) : 0.f;
+              for (int t = 0; t < 16; ++t)
+                part[t] = k0 + t < p.nKB ? __ldcg(&p.partials[((size_t)(k0 + t) * M + m) * p.O + row]) : 0.f;
 #pragma unroll
-              for (int t = 0; t < 4; ++t) total[t] += part[t];
+              for (int t = 0; t < 16; ++t) total += part[t];
             }
-#pragma unroll
-            for (int t = 0; t < 4; ++t)
-              if (rows[t] >= 0) emit(p.mats[owner[t]], m, rows[t] - p.mats[owner[t]].ru_begin * kUnitRows, total[t]);
+            emit(owner, m, row - owner.ru_begin * kUnitRows, total);
           }
         }
         if (my_ru >= 0 && prior == (unsigned)p.nKB - 1u) p.tickets[my_ru] = 0u;
@@ -589,7 +625,8 @@ extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3
     const int O = in.out_features;
     if (!in.planes || !in.scales || !in.out) return fail(FB_EINVAL, "fb_w3_gemv: planes, scales and out must be non-null");
     if (O < 32 || O > 65536 || O % 32) return fail(FB_ELIMIT, "fb_w3_gemv: O=%d must be a multiple of 32 in 32..65536", O);
-    if (!aligned(in.planes, 16)) return fail(FB_EINVAL, "fb_w3_gemv: planes must be 16-byte aligned");
+    if (!aligned(in.planes, 16) || !aligned(in.scales, 16) || !aligned(in.zeros, 16))
+      return fail(FB_EINVAL, "fb_w3_gemv: planes, scales and zeros must be 16-byte aligned");
     if (!aligned(in.scales, 2) || !aligned(in.out, group_partials ? 4 : 2) || !aligned(in.residual, 2))
       return fail(FB_EINVAL, "fb_w3_gemv: 16-bit tensors must be 2-byte aligned");
     if ((flags & FB_W3_DECODED_BF16) && in.zeros)
