@@ -104,6 +104,20 @@ int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* 
                      size_t scratch_bytes, unsigned flags, fb_stream_t stream);
 
 /*
+ * fb_w3_gemv_multi (M = 1, identity column order) with the producer of x fused into the table
+ * build, which removes a launch from the decode step:
+ *   FB_W3_INPUT_RMSNORM   x' = operand * T(x * rsqrt(mean(x^2) + eps)),  operand = norm weight [K]
+ *   FB_W3_INPUT_SILU_MUL  x' = T(silu(x)) * operand,                     operand = the `up` vector [K]
+ * with the roundings of the separate kernels (fb_rmsnorm, fb_silu_mul).  No counterpart in the
+ * reference, where these are separate modules (fused_modules.py:30-63 and the stock MLP).
+ */
+#define FB_W3_INPUT_RMSNORM 1
+#define FB_W3_INPUT_SILU_MUL 2
+int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transform, const void* operand, float eps,
+                           const fb_w3_matrix_t* matrices, int n_matrices, int scale_dtype, int in_features,
+                           void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream);
+
+/*
  * out[o] = T( sum_s partials[s, o] ), rows summed in ascending order.
  * partials fp32 [splits, O]; out f16|bf16 [O].
  * Replaces the reference's finish (csrc/w3_lut.cu:275-296, kernel :142-150).

@@ -57,6 +57,10 @@ def library() -> ctypes.CDLL:
         lib.fb_w3_gemv_multi.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(W3Matrix), ctypes.c_int,
                                          ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
                                          ctypes.c_uint, ctypes.c_void_p]
+        lib.fb_w3_gemv_fused_input.restype = ctypes.c_int
+        lib.fb_w3_gemv_fused_input.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_float,
+                                               ctypes.POINTER(W3Matrix), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                               ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.fb_bb_gemv_scratch_bytes.restype = ctypes.c_size_t
@@ -281,3 +285,18 @@ def attn_decode(q, k_cache, v_cache, out, length: int, scale: float, scratch) ->
 def silu_mul(gate, up, out) -> None:
     with torch.cuda.device(gate.device):
         check(library().fb_silu_mul(ptr(gate), ptr(up), ptr(out), gate.numel(), dtype_tag(gate.dtype), stream_handle(gate.device)))
+
+
+W3_INPUT_RMSNORM, W3_INPUT_SILU_MUL = 1, 2
+
+
+def w3_gemv_fused_input(x, transform: int, operand, eps: float, matrices, n_matrices, total_out, scale_dtype, *,
+                        pdl=True, scratch=None) -> None:
+    """``w3_gemv_multi`` for one activation row whose producer (RMSNorm or the SwiGLU gate) runs inside the launch."""
+    k = x.shape[-1]
+    if scratch is None:
+        scratch = scratch_for(x.device, w3_scratch_bytes(1, total_out, k))
+    with torch.cuda.device(x.device):
+        check(library().fb_w3_gemv_fused_input(ptr(x), dtype_tag(x.dtype), transform, ptr(operand), float(eps), matrices, n_matrices,
+                                               dtype_tag(scale_dtype), k, ptr(scratch), scratch.numel() * scratch.element_size(),
+                                               0 if pdl else FB_W3_NO_PDL, stream_handle(x.device)))

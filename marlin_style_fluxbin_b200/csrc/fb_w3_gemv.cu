@@ -42,10 +42,20 @@
     if (threadIdx.x == 0 && blockIdx.x == 0) reinterpret_cast<long long*>(p.status)[8 + (i)] = clock64(); \
     if (threadIdx.x == 0 && ((i) == 0 || (i) == 8))                                                  \
       reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.status) + (3 << 20))[blockIdx.x * 2 + ((i) == 8)] = fb::global_timer_ns(); \
+    if (threadIdx.x == 0 && (i) == 0) { unsigned smid_; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));  \
+      reinterpret_cast<unsigned*>(reinterpret_cast<char*>(p.status) + (3 << 20) + 65536)[blockIdx.x] = smid_; } \
+  } while (0)
+#define FB_WAVE_MARK(w, which)                                                                         \
+  do {                                                                                               \
+    if (lane == 0 && (warp == 0 || warp == 7) && (w) < 8)                                            \
+      reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((blockIdx.x * 2 + (warp == 7)) * 8 + (w)) * 4 + (which)] = clock64(); \
   } while (0)
 #else
 #define FB_MARK(i) \
   do {             \
+  } while (0)
+#define FB_WAVE_MARK(w, which) \
+  do {                         \
   } while (0)
 #endif
 
@@ -86,12 +96,16 @@ struct W3Params {
   W3Matrix mats[kMaxMatrices];
   int n_mats;
   const int16_t* perm;
-  float* partials;  // [nKB, M, O]
+  const void* prologue_arg;  // RMSNorm weight [K] (kind 1) or the `up` vector [K] (kind 2)
+  int prologue;              // 0 none, 1 RMSNorm of x, 2 x = silu(x) * up  (M = 1, identity order)
+  float eps;
+  float* partials;  // [nSB, M, O]
   unsigned* tickets;
   unsigned* status;
   int O, K, G, nKB, nRU;
   int act_dtype, scale_dtype;
-  int ctas_per_kb;     // row slices per K block
+  int S, nSB;          // K blocks per super-block (one CTA walks them in turn), super-blocks
+  int ctas_per_kb;     // row slices per super-block
   int group_partials;  // write scale-multiplied per-group sums instead of reducing
 };
 
@@ -128,7 +142,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   pdl_launch_dependents();
   FB_MARK(10);
 
-  const int nV = p.nKB * p.ctas_per_kb;
+  const int nV = p.nSB * p.ctas_per_kb;
   if ((int)blockIdx.x >= nV) return;
 
   if (threadIdx.x == 0) {
@@ -141,10 +155,10 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   __syncthreads();
   FB_MARK(11);
 
-  // Work of virtual CTA v: K block v / c, the row units [first, first + count) of slice v % c.
-  auto share = [&](int v, int& kb, int& first, int& count) {
-    kb = (int)((unsigned)v / (unsigned)p.ctas_per_kb);
-    const int slice = v - kb * p.ctas_per_kb;
+  // Work of CTA v: super-block v / c (K blocks sb*S ..), the row units [first, first + count) of slice v % c.
+  auto share = [&](int v, int& sb, int& first, int& count) {
+    sb = (int)((unsigned)v / (unsigned)p.ctas_per_kb);
+    const int slice = v - sb * p.ctas_per_kb;
     // 32-bit arithmetic on purpose (slice * nRU < 2^21): 64-bit division is slow on the GPU
     first = (int)((unsigned)(slice * p.nRU) / (unsigned)p.ctas_per_kb);
     count = (int)((unsigned)((slice + 1) * p.nRU) / (unsigned)p.ctas_per_kb) - first;
@@ -254,28 +268,54 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   };
   auto table_of = [&](int m) { return lut + m * 128; };
 
-  bool first_pass = true;
-  int seq_base = 0;  // waves staged before the current virtual CTA
-
-  int kb, cta_first, cta_count;
-  share((int)blockIdx.x, kb, cta_first, cta_count);
+  // This CTA walks the K blocks kb_begin .. kb_begin + nS - 1 over the same rows; its staged
+  // waves form one sequence across them: wave j = (K block j / waves, row wave j % waves).
+  int sb, cta_first, cta_count;
+  share((int)blockIdx.x, sb, cta_first, cta_count);
+  const int kb_begin = sb * p.S, nS = min(p.S, p.nKB - kb_begin);
+  const int waves = (cta_count + kWarps - 1) / kWarps, total_waves = nS * waves;
+  auto issue_seq = [&](int j) {
+    const int s = (int)((unsigned)j / (unsigned)waves), i = j - s * waves;
+    issue_wave(j, kb_begin + s, cta_first + i * kWarps, min(kWarps, cta_count - i * kWarps));
+  };
   FB_MARK(12);
-  for (int w = 0; w < kRing && w * kWarps < cta_count; ++w)  // weights never change: no need to wait
-    issue_wave(w, kb, cta_first + w * kWarps, min(kWarps, cta_count - w * kWarps));
+  for (int j = 0; j < kRing && j < total_waves; ++j) issue_seq(j);  // weights never change: no need to wait
   FB_MARK(1);
 
   // Everything below reads activations and writes scratch / outputs of this stream.
   pdl_wait_prior_grid();
   FB_MARK(9);
 
-  for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
-    if (!first_pass) {
-      __syncthreads();  // everyone has finished reading the previous tables
-      share(v, kb, cta_first, cta_count);
-      for (int w = 0; w < kRing && w * kWarps < cta_count; ++w)
-        issue_wave(seq_base + w, kb, cta_first + w * kWarps, min(kWarps, cta_count - w * kWarps));
+  // Optional fused input transform.  For RMSNorm every CTA reduces the whole activation row
+  // itself (K 16-bit values: a few KB out of L2), which costs far less than a separate launch.
+  float inv_rms = 1.f;
+  if (p.prologue == 1) {
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < p.K; i += kWarps * 32 * 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + i);
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float v = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+        ss += v * v;
+      }
     }
-    first_pass = false;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+    float* scratch_f = reinterpret_cast<float*>(lut);  // the table area is still free here
+    if (lane == 0) scratch_f[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) ss += scratch_f[w];
+    inv_rms = rsqrtf(ss / (float)p.K + p.eps);
+    __syncthreads();
+  }
+  auto round16 = [&](float v) { return p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v)); };
+
+  for (int s = 0; s < nS; ++s) {
+    const int kb = kb_begin + s;
+    if (s > 0) __syncthreads();  // everyone has finished reading the previous tables
 
     // ---- build the 32 tables of this K block: lane = table, warp = 32 consecutive entries ----
     float sx_m[M];  // lanes 0..15: sum of group A's activations, lanes 16..31: group B's
@@ -299,6 +339,16 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) v8[j] = 0.f;
+        }
+        if (p.prologue != 0 && g < p.G) {
+          // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
+          // SwiGLU rounds silu(gate) before the product
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float other = load_act(p.prologue_arg, p.act_dtype, kbase + j);
+            v8[j] = p.prologue == 1 ? round16(other * round16(v8[j] * inv_rms))
+                                    : round16(round16(v8[j] / (1.f + __expf(-v8[j]))) * other);
+          }
         }
         // ascending-order subset sums of the low four values ...
         float lo[16];
@@ -339,14 +389,14 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     // ---- this warp's units ----
     const int gA = 2 * kb, gB = 2 * kb + 1;
     const bool hasB = gB < p.G;
-    const int waves = (cta_count + kWarps - 1) / kWarps;
     for (int i = 0; i < waves; ++i) {
-      const int seq = seq_base + i, slot = seq % kRing;
+      const int seq = s * waves + i, slot = seq % kRing;
       const bool mine = i * kWarps + warp < cta_count;  // the last wave may be short
       const int ru = cta_first + i * kWarps + (mine ? warp : 0);
       const int row = ru * kUnitRows + lane;  // in the concatenated row space
       const W3Matrix& mat = p.mats[locate(ru)];
       const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
+      FB_WAVE_MARK(i, 0);
       bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[slot]), (uint32_t)((seq / kRing) & 1));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && !dead) {
@@ -367,7 +417,13 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           if (hasB) zcB = 4.f - (float)zp[kWarps * kUnitRows];
         }
       }
+      // later K blocks of the super-block add to the partial this same thread stored before
+      float prev[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+        prev[m] = (s > 0 && mine && !dead && p.nKB > 1 && !p.group_partials) ? __ldcg(&p.partials[((size_t)sb * M + m) * p.O + row]) : 0.f;
       FB_MARK(4);
+      FB_WAVE_MARK(i, 1);
 
       // per activation row, group half and plane: two partial sums (even / odd byte steps)
       float acc2[M][2][3][2];
@@ -424,14 +480,14 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         }
       }
       FB_MARK(5);
+      FB_WAVE_MARK(i, 2);
 
       // all lanes are done with the staged bytes: release the wave.  The slot released one
       // iteration AGO is refilled now: by this time the other warps have normally released it
       // too, so the issuing lanes do not stall on the slowest warp of the current wave.
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bars[slot])) : "memory");
-      if (!dead && i >= 1 && (i - 1 + kRing) * kWarps < cta_count)
-        issue_wave(seq - 1 + kRing, kb, cta_first + (i - 1 + kRing) * kWarps, min(kWarps, cta_count - (i - 1 + kRing) * kWarps));
+      if (!dead && seq >= 1 && seq - 1 + kRing < total_waves) issue_seq(seq - 1 + kRing);
 
       if (!dead && mine) {
         const float sA = bits_to_float(sbitsA, p.scale_dtype);
@@ -464,15 +520,12 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           } else if (p.nKB == 1) {
             emit(mat, m, lrow, vA + vB);
           } else {
-            p.partials[((size_t)kb * M + m) * p.O + row] = vA + vB;
+            p.partials[((size_t)sb * M + m) * p.O + row] = prev[m] + (vA + vB);
           }
         }
       }
+      FB_WAVE_MARK(i, 3);
     }
-    // the refill that the last iteration would have issued one step later
-    if (!dead && waves >= 1 && (waves - 1 + kRing) * kWarps < cta_count)
-      issue_wave(seq_base + waves - 1 + kRing, kb, cta_first + (waves - 1 + kRing) * kWarps, min(kWarps, cta_count - (waves - 1 + kRing) * kWarps));
-    seq_base += waves;
   }
 
   // ---- split-K hand-over, once per warp so that its global round trips are not paid per
@@ -481,50 +534,64 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   FB_MARK(6);
   if (p.nKB > 1 && !p.group_partials && !dead) {
     __syncwarp();  // orders every lane's partial stores before the releases below
-    for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
-      share(v, kb, cta_first, cta_count);
-      // this warp's units are cta_first + warp, + kWarps, ...
-      const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
-      for (int base = 0; base < my_count; base += 32) {
-        const int count = min(32, my_count - base);
-        const int my_ru = lane < count ? cta_first + (base + lane) * kWarps + warp : -1;
-        unsigned prior = 0;
-        if (my_ru >= 0)
-          asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
-        __syncwarp();
-        FB_MARK(7);
-        // Units whose last ticket this warp drew: sixteen partial loads in flight at a time
-        // (one L2 round trip for K <= 4096); the sum is still taken in ascending K order.
-        unsigned todo = __ballot_sync(0xffffffffu, my_ru >= 0 && prior == (unsigned)p.nKB - 1u);
-        while (todo) {
-          const int j = __ffs(todo) - 1;
-          todo &= todo - 1;
-          const int ru = cta_first + (base + j) * kWarps + warp;
-          const W3Matrix& owner = p.mats[locate(ru)];
-          const int row = ru * kUnitRows + lane;
+    // this warp's units are cta_first + warp, + kWarps, ...
+    const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
+    for (int base = 0; base < my_count; base += 32) {
+      const int count = min(32, my_count - base);
+      const int my_ru = lane < count ? cta_first + (base + lane) * kWarps + warp : -1;
+      unsigned prior = 0;
+      if (my_ru >= 0)
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
+      __syncwarp();
+      FB_MARK(7);
+      // Units whose last ticket this warp drew, two at a time with all their partial loads in
+      // flight together (one L2 round trip for up to 16 super-blocks); the sum is taken in
+      // ascending K order whoever computes it.
+      const bool last = my_ru >= 0 && prior == (unsigned)p.nSB - 1u;
+      unsigned todo = __ballot_sync(0xffffffffu, last);
+      while (todo) {
+        const int j0 = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const int j1 = todo ? __ffs(todo) - 1 : j0;
+        todo &= todo - 1;  // no-op on zero
+        const int ru0 = cta_first + (base + j0) * kWarps + warp, ru1 = cta_first + (base + j1) * kWarps + warp;
+        const int row0 = ru0 * kUnitRows + lane, row1 = ru1 * kUnitRows + lane;
 #pragma unroll
-          for (int m = 0; m < M; ++m) {
-            float total = 0.f;
-            for (int k0 = 0; k0 < p.nKB; k0 += 16) {
-              float part[16];
+        for (int m = 0; m < M; ++m) {
+          float total0 = 0.f, total1 = 0.f;
+          for (int k0 = 0; k0 < p.nSB; k0 += 16) {
+            float part0[16], part1[16];
 #pragma unroll
-              for (int t = 0; t < 16; ++t)
-                part[t] = k0 + t < p.nKB ? __ldcg(&p.partials[((size_t)(k0 + t) * M + m) * p.O + row]) : 0.f;
-#pragma unroll
-              for (int t = 0; t < 16; ++t) total += part[t];
+            for (int t = 0; t < 16; ++t) {
+              const bool in = k0 + t < p.nSB;
+              const size_t at = ((size_t)(k0 + t) * M + m) * p.O;
+              part0[t] = in ? __ldcg(&p.partials[at + row0]) : 0.f;
+              part1[t] = in ? __ldcg(&p.partials[at + row1]) : 0.f;
             }
-            emit(owner, m, row - owner.ru_begin * kUnitRows, total);
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+              total0 += part0[t];
+              total1 += part1[t];
+            }
+          }
+          const W3Matrix& owner0 = p.mats[locate(ru0)];
+          emit(owner0, m, row0 - owner0.ru_begin * kUnitRows, total0);
+          if (j1 != j0) {
+            const W3Matrix& owner1 = p.mats[locate(ru1)];
+            emit(owner1, m, row1 - owner1.ru_begin * kUnitRows, total1);
           }
         }
-        if (my_ru >= 0 && prior == (unsigned)p.nKB - 1u) p.tickets[my_ru] = 0u;
       }
+      if (last) p.tickets[my_ru] = 0u;
     }
   }
   FB_MARK(8);
 }
 
+constexpr int kMaxSplits = 16;
+
 struct Plan {
-  int grid, ctas_per_kb;
+  int grid, ctas_per_kb, S, nSB;
   size_t smem;
 };
 
@@ -534,12 +601,15 @@ size_t lut_bytes(int m) { return (size_t)32768 << (m == 1 ? 0 : (m == 2 ? 1 : 2)
 // of the next kernel in the stream can be resident (and prefetching) beside one of this kernel.
 Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   Plan plan;
-  int c = kCtasPerSm * info.sm_count / nKB;
+  // At most kMaxSplits partial sums per output: beyond that one CTA walks several K blocks of
+  // its rows in turn, so that the final reduction stays one round of loads.
+  plan.S = (nKB + kMaxSplits - 1) / kMaxSplits;
+  plan.nSB = (nKB + plan.S - 1) / plan.S;
+  int c = kCtasPerSm * info.sm_count / plan.nSB;
   if (c < 1) c = 1;
   if (c > nRU) c = nRU;
   plan.ctas_per_kb = c;
-  const int nV = nKB * c;
-  plan.grid = nV < kCtasPerSm * info.sm_count ? nV : kCtasPerSm * info.sm_count;
+  plan.grid = plan.nSB * c;
   plan.smem = lut_bytes(m) + (size_t)kRing * kWaveBytes + 2 * kRing * sizeof(uint64_t);
   return plan;
 }
@@ -592,10 +662,14 @@ extern "C" size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_featu
   return kPartialsOffset + partial_bytes(m, out_features, in_features);
 }
 
-extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices,
-                                int scale_dtype, const int16_t* perm, int in_features, void* scratch,
-                                size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
+namespace {
+int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices, int scale_dtype,
+              const int16_t* perm, int in_features, void* scratch, size_t scratch_bytes, unsigned flags,
+              fb_stream_t stream, int prologue, const void* prologue_arg, float eps) {
   const int K = in_features;
+  if (prologue < 0 || prologue > 2) return fail(FB_EINVAL, "fb_w3_gemv: unknown input transform %d", prologue);
+  if (prologue != 0 && (m != 1 || perm || !prologue_arg || !aligned(prologue_arg, 2)))
+    return fail(FB_EINVAL, "fb_w3_gemv: a fused input transform needs M = 1, identity column order and its operand");
   const bool group_partials = (flags & FB_W3_GROUP_PARTIALS) != 0;
   if (!x || !matrices) return fail(FB_EINVAL, "fb_w3_gemv: x and the matrix list must be non-null");
   if (n_matrices < 1 || n_matrices > kMaxMatrices) return fail(FB_ELIMIT, "fb_w3_gemv: %d matrices given, 1..%d supported", n_matrices, kMaxMatrices);
@@ -613,6 +687,9 @@ extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3
   W3Params p;
   p.x = x;
   p.perm = perm;
+  p.prologue = prologue;
+  p.prologue_arg = prologue_arg;
+  p.eps = eps;
   p.n_mats = n_matrices;
   long long total = 0;
   for (int j = 0; j < kMaxMatrices; ++j) {
@@ -666,6 +743,8 @@ extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3
   p.partials = reinterpret_cast<float*>(base + kPartialsOffset);
   const Plan plan = make_plan(m, p.nKB, p.nRU, *info);
   p.ctas_per_kb = plan.ctas_per_kb;
+  p.S = plan.S;
+  p.nSB = plan.nSB;
   p.group_partials = group_partials ? 1 : 0;
   if (plan.smem > (size_t)info->max_smem_optin) return fail(FB_ELIMIT, "fb_w3_gemv: plan needs %zu bytes of shared memory", plan.smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -682,6 +761,23 @@ extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3
   }
 #undef FB_DISPATCH
   return fail(FB_ELIMIT, "fb_w3_gemv: unsupported M");
+}
+}  // namespace
+
+extern "C" int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices,
+                                int scale_dtype, const int16_t* perm, int in_features, void* scratch,
+                                size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
+  return run_multi(x, act_dtype, m, matrices, n_matrices, scale_dtype, perm, in_features, scratch, scratch_bytes, flags, stream,
+                   0, nullptr, 0.f);
+}
+
+extern "C" int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transform, const void* operand, float eps,
+                                      const fb_w3_matrix_t* matrices, int n_matrices, int scale_dtype, int in_features,
+                                      void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
+  if (transform != FB_W3_INPUT_RMSNORM && transform != FB_W3_INPUT_SILU_MUL)
+    return fail(FB_EINVAL, "fb_w3_gemv_fused_input: transform must be FB_W3_INPUT_RMSNORM or FB_W3_INPUT_SILU_MUL");
+  return run_multi(x, act_dtype, 1, matrices, n_matrices, scale_dtype, nullptr, in_features, scratch, scratch_bytes, flags, stream,
+                   transform, operand, eps);
 }
 
 extern "C" int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales,

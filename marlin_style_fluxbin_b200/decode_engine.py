@@ -85,7 +85,7 @@ class DecodeEngine:
     """``arm`` is ``"w3"`` (packed kernels) or ``"bf16"`` (dense dequantised weights, cuBLAS)."""
 
     def __init__(self, shape: ModelShape, *, device, max_positions: int, arm: str = "w3", seed: int = 20260916,
-                 tp_rank: int = 0, tp_size: int = 1, group=None, dtype=torch.bfloat16):
+                 tp_rank: int = 0, tp_size: int = 1, group=None, dtype=torch.bfloat16, fuse_inputs: bool = True):
         if arm not in ("w3", "bf16"):
             raise ValueError("arm must be w3 or bf16")
         if shape.q_heads % tp_size or shape.kv_heads % tp_size or (shape.hidden // 128) % tp_size or (shape.intermediate // 128) % tp_size:
@@ -93,6 +93,8 @@ class DecodeEngine:
         self.shape, self.device, self.arm, self.dtype = shape, torch.device(device), arm, dtype
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
         self.max_positions = max_positions
+        # RMSNorm and the SwiGLU gate run inside the GEMV that consumes them (w3 arm only)
+        self.fuse_inputs = fuse_inputs
         s, p = shape, tp_size
         self.q_heads, self.kv_heads = s.q_heads // p, s.kv_heads // p
         self.inter = s.intermediate // p
@@ -218,8 +220,13 @@ class DecodeEngine:
         scale = 1.0 / math.sqrt(s.head_dim)
         launches = 1
         for index, layer in enumerate(self.layers):
-            nat.rmsnorm(self.h, layer.ln1, self.xn, s.eps)
-            if w3:
+            fuse = w3 and self.fuse_inputs
+            if not fuse:
+                nat.rmsnorm(self.h, layer.ln1, self.xn, s.eps)
+            if fuse:
+                nat.w3_gemv_fused_input(self.h, nat.W3_INPUT_RMSNORM, layer.ln1, s.eps, layer.qkv_list, 3,
+                                        self.q.numel() + 2 * self.k.numel(), f16, scratch=self.scratch)
+            elif w3:
                 nat.w3_gemv_multi(self.xn, layer.qkv_list, 3, self.q.numel() + 2 * self.k.numel(), f16, None, scratch=self.scratch)
             else:
                 qkv = self._linear(layer, "qkv", self.xn)
@@ -238,16 +245,24 @@ class DecodeEngine:
                     self.h_next.add_(self.h)
                     launches += 1
             self._allreduce(self.h_next)
-            nat.rmsnorm(self.h_next, layer.ln2, self.xn, s.eps)
-            if w3:
+            if not fuse:
+                nat.rmsnorm(self.h_next, layer.ln2, self.xn, s.eps)
+            if fuse:
+                nat.w3_gemv_fused_input(self.h_next, nat.W3_INPUT_RMSNORM, layer.ln2, s.eps, layer.gu_list, 2, 2 * self.inter, f16,
+                                        scratch=self.scratch)
+            elif w3:
                 nat.w3_gemv_multi(self.xn, layer.gu_list, 2, 2 * self.inter, f16, None, scratch=self.scratch)
             else:
                 gu = self._linear(layer, "gate_up", self.xn)
                 self.gate.copy_(gu[:, :self.inter])
                 self.up.copy_(gu[:, self.inter:])
                 launches += 2
-            nat.silu_mul(self.gate, self.up, self.act)
-            if w3:
+            if not fuse:
+                nat.silu_mul(self.gate, self.up, self.act)
+            if fuse:
+                nat.w3_gemv_fused_input(self.gate, nat.W3_INPUT_SILU_MUL, self.up, 0.0, layer.down_list, 1, s.hidden, f16,
+                                        scratch=self.scratch)
+            elif w3:
                 nat.w3_gemv_multi(self.act, layer.down_list, 1, s.hidden, f16, None, scratch=self.scratch)
             else:
                 torch.mm(self.act, layer.dense["down"].t(), out=self.h)
@@ -255,7 +270,7 @@ class DecodeEngine:
                     self.h.add_(self.h_next)
                     launches += 1
             self._allreduce(self.h)
-            launches += 9 + (2 if self.tp_size > 1 else 0)
+            launches += (6 if fuse else 9) + (2 if self.tp_size > 1 else 0)
         nat.rmsnorm(self.h, self.final_norm, self.xn, s.eps)
         torch.mm(self.xn, self.lm_head.t(), out=self.logits)
         torch.argmax(self.logits, dim=-1, out=self.next_token)

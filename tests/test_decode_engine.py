@@ -73,3 +73,18 @@ def test_packed_arm_matches_dense_arm_and_graph_replays_exactly():
     graph2.replay()
     torch.cuda.synchronize()
     assert torch.equal(predictions2, own)
+
+
+def test_fused_input_launches_match_separate_glue_kernels():
+    """Six launches per layer (RMSNorm and the SwiGLU gate inside the GEMVs) against nine."""
+    from marlin_style_fluxbin_b200.decode_engine import DecodeEngine
+
+    shape, prompt = small_shape(), 20
+    ids = torch.randint(0, 640, (1, prompt), generator=torch.Generator().manual_seed(3))
+    logits = {}
+    for fuse in (True, False):
+        engine = DecodeEngine(shape, device="cuda", max_positions=64, arm="w3", seed=7, fuse_inputs=fuse)
+        first = engine.prefill(ids).argmax(-1)
+        _, _, logits[fuse] = engine.decode(first, prompt, 4)
+        assert engine.launches_per_step == 4 + shape.layers * (6 if fuse else 9)
+    assert nrmse(logits[True], logits[False]) < 5e-3, nrmse(logits[True], logits[False])

@@ -272,3 +272,54 @@ def test_fused_matrices_share_one_launch_and_residual_epilogue():
     torch.cuda.synchronize()
     assert torch.equal(entries[0][3], (singles[0].float() + residual.float()).bfloat16())
     assert torch.equal(entries[1][3], singles[1]) and torch.equal(entries[2][3], singles[2])
+
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+def test_fused_input_transforms_equal_separate_kernels(dtype):
+    """RMSNorm / SwiGLU-gate fused into the table build give the rows of the two-launch form.
+    The SwiGLU form is bit-identical (same per-element arithmetic); RMSNorm sums the squares in a
+    different order, so its 1/rms may differ in the last bit: 16-bit-level tolerance there."""
+    from marlin_style_fluxbin_b200 import _native
+
+    k, o = 2048, 384
+    layout, x_host = make_case(o, k, seed=41, zeros=True, act_dtype=dtype)
+    lg, x = to_cuda(layout), (x_host * 3).to(dtype).cuda()
+    gen = torch.Generator().manual_seed(5)
+    weight = (1 + 0.1 * torch.randn(k, generator=gen)).to(dtype).cuda()
+    up = torch.randn(1, k, generator=gen).to(dtype).cuda()
+
+    def two_launch(x_eff):
+        out = torch.empty(1, o, device="cuda", dtype=dtype)
+        _native.w3_gemv(x_eff.contiguous(), lg["planes"], lg["scales"], lg["zeros"], None, out)
+        return out
+
+    def fused(kind, operand, eps):
+        out = torch.full((1, o), float("nan"), device="cuda", dtype=dtype)
+        array = _native.w3_matrix_list([(lg["planes"], lg["scales"], lg["zeros"], out, None)])
+        _native.w3_gemv_fused_input(x, kind, operand, eps, array, 1, o, torch.float16)
+        torch.cuda.synchronize()
+        return out
+
+    act = torch.empty_like(x)
+    _native.silu_mul(x, up, act)
+    assert torch.equal(fused(_native.W3_INPUT_SILU_MUL, up, 0.0), two_launch(act))
+    # and against plain tensor math through the oracle's dequantised product
+    silu = (torch.nn.functional.silu(x.float()).to(dtype).float() * up.float()).to(dtype)
+    reference, _ = oracle_outputs(layout, silu.cpu())
+    assert_parity(fused(_native.W3_INPUT_SILU_MUL, up, 0.0), reference)
+
+    normed = torch.empty_like(x)
+    _native.rmsnorm(x, weight, normed, 1e-6)
+    got, want = fused(_native.W3_INPUT_RMSNORM, weight, 1e-6), two_launch(normed)
+    assert (got.float() - want.float()).abs().max() <= 2e-2 * want.float().abs().max()
+    reference, _ = oracle_outputs(layout, normed.cpu())
+    assert_parity(got, reference)
+    # repeat-exact
+    assert torch.equal(got, fused(_native.W3_INPUT_RMSNORM, weight, 1e-6))
+    # a permuted column order or M > 1 is refused
+    two = torch.cat([x, x])
+    out2 = torch.empty(2, o, device="cuda", dtype=dtype)
+    lib = _native.library()
+    array = _native.w3_matrix_list([(lg["planes"], lg["scales"], lg["zeros"], out2, None)])
+    assert lib.fb_w3_gemv_fused_input(two.data_ptr(), _native.dtype_tag(dtype), 3, weight.data_ptr(), 1e-6, array, 1,
+                                      _native.dtype_tag(torch.float16), k, None, 0, 0, None) == -1
