@@ -56,9 +56,9 @@ const char* fb_last_error(void);
  *  Returns the value, or FB_EINVAL for an unknown key. */
 int64_t fb_query(const char* key);
 
-/* Bytes of scratch fb_w3_gemv needs for a problem of this size (partials of the K
- * split plus one ticket word per 32 output rows).  The scratch must be zero-filled
- * once after allocation; every call leaves it ready for the next.  One scratch may be
+/* Bytes of scratch fb_w3_gemv needs for a problem of this size (a status word, 2 MiB of
+ * 64-bit combine words for the K split, and fp32 partials when K exceeds 4096).  The
+ * scratch must be zero-filled once after allocation; every call leaves it ready for the next.  One scratch may be
  * shared by all calls that are ordered on one stream; calls that can overlap on the
  * GPU need separate scratch. */
 size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_features);
@@ -70,8 +70,11 @@ size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_features);
  *   scales  f16|bf16 [G,O]
  *   zeros   uint8 [G,O] zero points, or NULL for the constant zero point 4
  *   perm    int16 [K] sorted position -> input column (desc_act), or NULL for identity
- * W[o, perm[k]] = scale[k/128, o] * (code - zero); accumulation in fp32; the split over
- * K is reduced inside the kernel in a fixed order, so results are repeat-exact.
+ * W[o, perm[k]] = scale[k/128, o] * (code - zero); accumulation in fp32.  The split over K
+ * (up to 16 partial sums per output) is combined inside the kernel by 64-bit integer adds of
+ * the partial sums in fixed point (steps of 2^-26), so results do not depend on arrival order:
+ * repeat-exact and graph-replay-exact.  A partial sum that is not finite, or is 2^21 or more
+ * in magnitude, has no fixed-point form: that output is written as NaN.
  * M = 1..4.  O % 32 == 0, G <= 255 (K <= 32640), O <= 65536; x, planes, scales, zeros 16-byte aligned.
  *
  * Replaces the reference's pybind entry points inline_main + finish and m1_out

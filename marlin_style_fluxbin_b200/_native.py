@@ -121,12 +121,14 @@ def w3_scratch_bytes(m: int, out_features: int, in_features: int) -> int:
 # One zero-initialised scratch per (device, stream): calls ordered on one stream may share
 # it; the kernels leave it ready for the next call.  Grown on demand, which allocates, so
 # the first call of a given size must happen before CUDA-graph capture (warm-up).
-_scratch: dict[tuple[int, int], torch.Tensor] = {}
+_scratch: dict[tuple[int, int, str], torch.Tensor] = {}
 
 
-def scratch_for(device: torch.device, nbytes: int) -> torch.Tensor:
+def scratch_for(device: torch.device, nbytes: int, family: str = "w3") -> torch.Tensor:
+    """Zero-filled scratch per (device, stream, kernel family).  Families lay their control words
+    out differently, and each kernel relies on finding its own words zero, so they never share."""
     key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
+           torch.cuda.current_stream(device).cuda_stream, family)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         if torch.cuda.is_current_stream_capturing():
@@ -210,7 +212,7 @@ def bb_gemv(x, layout, out, *, pdl=True, scratch=None) -> None:
     groups, o = codes.shape[0], codes.shape[1]
     k = groups * 128
     if scratch is None:
-        scratch = scratch_for(x.device, bb_scratch_bytes(o, k, False))
+        scratch = scratch_for(x.device, bb_scratch_bytes(o, k, False), "bb")
     with torch.cuda.device(x.device):
         check(library().fb_bb_gemv(
             ptr(x), dtype_tag(x.dtype), ptr(codes), int(codes.ndim == 4), ptr(layout["rows"]), ptr(layout["columns"]),
@@ -224,7 +226,7 @@ def bb_global_gemv(x, codes, row_scales, col_scales, salient_idx, salient, out, 
     groups, o = codes.shape[0], codes.shape[1]
     k = groups * 128
     if scratch is None:
-        scratch = scratch_for(x.device, bb_scratch_bytes(o, k, True))
+        scratch = scratch_for(x.device, bb_scratch_bytes(o, k, True), "bb")
     n_sal = 0 if salient_idx is None else salient_idx.numel()
     with torch.cuda.device(x.device):
         check(library().fb_bb_global_gemv(

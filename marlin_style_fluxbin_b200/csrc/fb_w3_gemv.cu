@@ -16,15 +16,16 @@
 //    bytes) are staged into shared memory with bulk asynchronous copies (cp.async.bulk
 //    + mbarrier), a wave of one unit per warp at a time, one (group, plane) copy per
 //    issuing lane; a lookup address is a rotate and one logic op on the staged weight word.
-//  * One CTA per SM at most: each K block is served by floor(SMs / K blocks) CTAs that
-//    split its rows, so a CTA builds the tables of exactly one K block.
+//  * Two CTAs per SM: each K block is served by floor(2 SMs / K blocks) CTAs that split its rows.
 //  * Launched with programmatic dependent launch: a kernel's prologue and first weight
 //    copies overlap the tail of the previous kernel in the stream; everything that
 //    reads activations or touches scratch comes after griddepcontrol.wait.  A CTA stays
 //    near 104 KB of shared memory (M = 1) so that two can be resident on an SM.
-//  * Split-K is reduced inside the kernel: fp32 partials go to a small L2-resident
-//    scratch, a ticket per 32-row unit elects the last contributor, which sums the
-//    partials in ascending K order (deterministic, repeat-exact) and writes the output.
+//  * Split-K is combined inside the kernel with ONE 64-bit atomic add per contribution: the
+//    partial sum in fixed point (2^-26 units) plus an arrival count in the low bits.  Integer
+//    addition is associative, so the result is independent of arrival order (deterministic,
+//    repeat-exact); the contributor that reads back the last count writes the output.  A K
+//    longer than 16 K blocks is walked in turn by the same CTA (at most 16 contributions).
 //
 // Arithmetic follows the reference kernel (csrc/w3_lut.cu:38-139): per group
 // dot = a0 + 2*a1 - 4*a2 over the stored planes (plane 2 inverted), times the group
@@ -76,6 +77,7 @@ constexpr int kWaveScales = 2 * kWarps * kUnitRows * 2;  // 1 KB: 16-bit scales 
 constexpr int kWaveZeros = 2 * kWarps * kUnitRows;       // 512 B: zero points of two groups
 constexpr int kWaveBytes = kWavePlanes + kWaveScales + kWaveZeros;
 constexpr int kMaxM = 4;
+constexpr int kMaxSplits = 16;  // partial sums per output (one arrival count of 6 bits, 52-bit fixed-point sum)
 
 constexpr int kMaxMatrices = 4;
 
@@ -100,7 +102,7 @@ struct W3Params {
   int prologue;              // 0 none, 1 RMSNorm of x, 2 x = silu(x) * up  (M = 1, identity order)
   float eps;
   float* partials;  // [nSB, M, O]
-  unsigned* tickets;
+  unsigned long long* combine;  // [M, O] split-K accumulators, zero between launches
   unsigned* status;
   int O, K, G, nKB, nRU;
   int act_dtype, scale_dtype;
@@ -313,11 +315,52 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   }
   auto round16 = [&](float v) { return p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v)); };
 
+  // Raw 16-bit activations of one lane's table (8 values) and of the fused transform's operand;
+  // the next K block's are fetched while the current one is being computed.
+  const bool fast_x = M == 1 && !p.perm;
+  auto fetch_x = [&](int kb_, uint4& raw, uint4& op) {
+    const int g = 2 * kb_ + (lane >> 4);
+    raw = make_uint4(0u, 0u, 0u, 0u);
+    op = raw;
+    if (g < p.G) {
+      const int kbase = g * 128 + (lane & 15) * 8;
+      raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + kbase);
+      if (p.prologue != 0) op = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.prologue_arg) + kbase);
+    }
+  };
+  // Split-K combine.  A contribution is ONE 64-bit atomic add: the partial sum in fixed point
+  // (units of 2^-26) in bits 12..63, an arrival count in bits 0..5, a count of non-finite or
+  // out-of-range partials in bits 6..11.  Integer addition is associative, so the result does
+  // not depend on arrival order (repeat- and replay-exact); whoever reads back the last count
+  // converts, writes the output and zeroes the word.  The answer of an add is only needed one
+  // unit later, so its round trip hides behind the next unit's lookups.
+  unsigned long long pend_old[M], pend_add[M];
+  int pend_ru = -1;
+  auto settle = [&]() {
+    if (pend_ru < 0) return;
+    const W3Matrix& owner = p.mats[locate(pend_ru)];
+    const int lrow = (pend_ru - owner.ru_begin) * kUnitRows + lane;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      if ((int)(pend_old[m] & 63ull) == p.nSB - 1) {
+        const unsigned long long total = pend_old[m] + pend_add[m];
+        float value = __ll2float_rn((long long)total >> 12) * 1.4901161193847656e-08f;  // 2^-26
+        if ((total >> 6) & 63ull) value = __int_as_float(0x7fc00000);
+        emit(owner, m, lrow, value);
+        p.combine[(size_t)m * p.O + pend_ru * kUnitRows + lane] = 0ull;
+      }
+    }
+    pend_ru = -1;
+  };
+  uint4 raw_next = make_uint4(0u, 0u, 0u, 0u), op_next = raw_next;
+  if (fast_x) fetch_x(kb_begin, raw_next, op_next);
+
   for (int s = 0; s < nS; ++s) {
     const int kb = kb_begin + s;
     if (s > 0) __syncthreads();  // everyone has finished reading the previous tables
 
-    // ---- build the 32 tables of this K block: lane = table, warp = 32 consecutive entries ----
+    // ---- build the 32 tables of this K block: lane = table; warp w owns the entries whose low
+    // nibble is 2w or 2w+1, so that the walk over the high nibble unrolls with constant offsets ----
     float sx_m[M];  // lanes 0..15: sum of group A's activations, lanes 16..31: group B's
     {
       const int g = 2 * kb + (lane >> 4);
@@ -325,7 +368,22 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
 #pragma unroll
       for (int m = 0; m < M; ++m) {
         float v8[8];
-        if (g < p.G) {
+        if (fast_x) {
+          const uint32_t words[4] = {raw_next.x, raw_next.y, raw_next.z, raw_next.w};
+          const uint32_t owords[4] = {op_next.x, op_next.y, op_next.z, op_next.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+            if (p.prologue != 0) {
+              // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
+              // SwiGLU rounds silu(gate) before the product
+              const float other = bits_to_float((unsigned short)((owords[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+              v8[j] = p.prologue == 1 ? round16(other * round16(v8[j] * inv_rms))
+                                      : round16(round16(v8[j] / (1.f + __expf(-v8[j]))) * other);
+            }
+          }
+          if (s + 1 < nS) fetch_x(kb + 1, raw_next, op_next);
+        } else if (g < p.G) {
           if (p.perm) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) v8[j] = load_act(p.x, p.act_dtype, m * p.K + p.perm[kbase + j]);
@@ -340,39 +398,25 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
 #pragma unroll
           for (int j = 0; j < 8; ++j) v8[j] = 0.f;
         }
-        if (p.prologue != 0 && g < p.G) {
-          // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
-          // SwiGLU rounds silu(gate) before the product
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float other = load_act(p.prologue_arg, p.act_dtype, kbase + j);
-            v8[j] = p.prologue == 1 ? round16(other * round16(v8[j] * inv_rms))
-                                    : round16(round16(v8[j] / (1.f + __expf(-v8[j]))) * other);
-          }
-        }
-        // ascending-order subset sums of the low four values ...
-        float lo[16];
-        lo[0] = 0.f;
-#pragma unroll
-        for (int q = 1; q < 16; ++q) {
-          const int top = q >= 8 ? 3 : (q >= 4 ? 2 : (q >= 2 ? 1 : 0));
-          lo[q] = lo[q & ~(1 << top)] + v8[top];
-        }
-        // ... then the high four, still in ascending order; this warp owns the entries
-        // whose high nibble is 2*warp or 2*warp+1.
+        // Every entry is the ascending-order subset sum of its activations (as the reference's
+        // tables are): first the low nibble's, then one add per step of the high nibble's tree.
         unsigned char* const column = table_of(m) + lane * 4;
 #pragma unroll
-        for (int hh = 0; hh < 16 / kWarps; ++hh) {
-          const int hi = warp * (16 / kWarps) + hh;
+        for (int qq = 0; qq < 16 / kWarps; ++qq) {
+          const int q = warp * (16 / kWarps) + qq;
+          float hi[16];
+          hi[0] = 0.f;
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            float s = lo[q];
-            if (hi & 1) s += v8[4];
-            if (hi & 2) s += v8[5];
-            if (hi & 4) s += v8[6];
-            if (hi & 8) s += v8[7];
-            *reinterpret_cast<float*>(column + (size_t)(hi * 16 + q) * Geom::kStride) = s;
+          for (int b = 0; b < 4; ++b)
+            if ((q >> b) & 1) hi[0] += v8[b];
+#pragma unroll
+          for (int h = 1; h < 16; ++h) {
+            const int top = h >= 8 ? 3 : (h >= 4 ? 2 : (h >= 2 ? 1 : 0));
+            hi[h] = hi[h & ~(1 << top)] + v8[4 + top];
           }
+          unsigned char* const at = column + (size_t)q * Geom::kStride;
+#pragma unroll
+          for (int h = 0; h < 16; ++h) *reinterpret_cast<float*>(at + (size_t)h * 16 * Geom::kStride) = hi[h];
         }
         float total = 0.f;
 #pragma unroll
@@ -396,7 +440,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       const int row = ru * kUnitRows + lane;  // in the concatenated row space
       const W3Matrix& mat = p.mats[locate(ru)];
       const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
-      FB_WAVE_MARK(i, 0);
+      FB_WAVE_MARK(seq, 0);
       bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[slot]), (uint32_t)((seq / kRing) & 1));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && !dead) {
@@ -423,7 +467,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       for (int m = 0; m < M; ++m)
         prev[m] = (s > 0 && mine && !dead && p.nKB > 1 && !p.group_partials) ? __ldcg(&p.partials[((size_t)sb * M + m) * p.O + row]) : 0.f;
       FB_MARK(4);
-      FB_WAVE_MARK(i, 1);
+      FB_WAVE_MARK(seq, 1);
 
       // per activation row, group half and plane: two partial sums (even / odd byte steps)
       float acc2[M][2][3][2];
@@ -480,7 +524,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         }
       }
       FB_MARK(5);
-      FB_WAVE_MARK(i, 2);
+      FB_WAVE_MARK(seq, 2);
 
       // all lanes are done with the staged bytes: release the wave.  The slot released one
       // iteration AGO is refilled now: by this time the other warps have normally released it
@@ -520,75 +564,30 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           } else if (p.nKB == 1) {
             emit(mat, m, lrow, vA + vB);
           } else {
-            p.partials[((size_t)sb * M + m) * p.O + row] = prev[m] + (vA + vB);
+            const float v = prev[m] + (vA + vB);
+            if (s + 1 < nS) {
+              p.partials[((size_t)sb * M + m) * p.O + row] = v;
+            } else {
+              if (m == 0) settle();  // the previous unit's answers have long arrived
+              const bool fits = fabsf(v) < 2097152.f;  // 2^21: sixteen of them stay inside 52 bits
+              pend_add[m] = fits ? ((unsigned long long)__float2ll_rn(v * 67108864.f) << 12) + 1ull : 65ull;
+              asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;"
+                           : "=l"(pend_old[m])
+                           : "l"(p.combine + (size_t)m * p.O + row), "l"(pend_add[m])
+                           : "memory");
+              pend_ru = ru;
+            }
           }
         }
       }
-      FB_WAVE_MARK(i, 3);
+      FB_WAVE_MARK(seq, 3);
     }
   }
 
-  // ---- split-K hand-over, once per warp so that its global round trips are not paid per
-  // unit: lane i announces the warp's i-th unit with one release/acquire ticket increment;
-  // whoever draws the last ticket of a row unit sums the partials in ascending K order.
   FB_MARK(6);
-  if (p.nKB > 1 && !p.group_partials && !dead) {
-    __syncwarp();  // orders every lane's partial stores before the releases below
-    // this warp's units are cta_first + warp, + kWarps, ...
-    const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
-    for (int base = 0; base < my_count; base += 32) {
-      const int count = min(32, my_count - base);
-      const int my_ru = lane < count ? cta_first + (base + lane) * kWarps + warp : -1;
-      unsigned prior = 0;
-      if (my_ru >= 0)
-        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
-      __syncwarp();
-      FB_MARK(7);
-      // Units whose last ticket this warp drew, two at a time with all their partial loads in
-      // flight together (one L2 round trip for up to 16 super-blocks); the sum is taken in
-      // ascending K order whoever computes it.
-      const bool last = my_ru >= 0 && prior == (unsigned)p.nSB - 1u;
-      unsigned todo = __ballot_sync(0xffffffffu, last);
-      while (todo) {
-        const int j0 = __ffs(todo) - 1;
-        todo &= todo - 1;
-        const int j1 = todo ? __ffs(todo) - 1 : j0;
-        todo &= todo - 1;  // no-op on zero
-        const int ru0 = cta_first + (base + j0) * kWarps + warp, ru1 = cta_first + (base + j1) * kWarps + warp;
-        const int row0 = ru0 * kUnitRows + lane, row1 = ru1 * kUnitRows + lane;
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float total0 = 0.f, total1 = 0.f;
-          for (int k0 = 0; k0 < p.nSB; k0 += 16) {
-            float part0[16], part1[16];
-#pragma unroll
-            for (int t = 0; t < 16; ++t) {
-              const bool in = k0 + t < p.nSB;
-              const size_t at = ((size_t)(k0 + t) * M + m) * p.O;
-              part0[t] = in ? __ldcg(&p.partials[at + row0]) : 0.f;
-              part1[t] = in ? __ldcg(&p.partials[at + row1]) : 0.f;
-            }
-#pragma unroll
-            for (int t = 0; t < 16; ++t) {
-              total0 += part0[t];
-              total1 += part1[t];
-            }
-          }
-          const W3Matrix& owner0 = p.mats[locate(ru0)];
-          emit(owner0, m, row0 - owner0.ru_begin * kUnitRows, total0);
-          if (j1 != j0) {
-            const W3Matrix& owner1 = p.mats[locate(ru1)];
-            emit(owner1, m, row1 - owner1.ru_begin * kUnitRows, total1);
-          }
-        }
-      }
-      if (last) p.tickets[my_ru] = 0u;
-    }
-  }
+  settle();
   FB_MARK(8);
 }
-
-constexpr int kMaxSplits = 16;
 
 struct Plan {
   int grid, ctas_per_kb, S, nSB;
@@ -645,14 +644,16 @@ int launch(const W3Params& p, const Plan& plan, int max_smem, bool pdl, cudaStre
 }
 
 // Scratch layout, identical for every problem size so that one scratch can serve calls of
-// different shapes: [0,256) status word; [256,16384) one ticket per 32-row unit (at most
-// 2048); partials from byte 16384.  Tickets are zero between calls.
-constexpr size_t kTicketsOffset = 256;
-constexpr size_t kPartialsOffset = 16384;
+// different shapes: [0,256) status word; from byte 16384 the split-K combine words (one 64-bit
+// word per activation row and output row, 2 MiB for the largest launch), which are zero between
+// calls; after them the fp32 partials that a CTA walking several K blocks keeps between them.
+constexpr size_t kCombineOffset = 16384;
+constexpr size_t kPartialsOffset = kCombineOffset + (size_t)kMaxM * 65536 * sizeof(unsigned long long);
 
 size_t partial_bytes(int m, int O, int K) {
   const int nKB = (K / 128 + 1) / 2;
-  return nKB > 1 ? (size_t)nKB * m * O * sizeof(float) : 0;
+  const int S = (nKB + kMaxSplits - 1) / kMaxSplits, nSB = (nKB + S - 1) / S;
+  return S > 1 ? (size_t)nSB * m * O * sizeof(float) : 0;
 }
 
 }  // namespace
@@ -739,7 +740,7 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   p.scale_dtype = scale_dtype;
   unsigned char* base = static_cast<unsigned char*>(scratch);
   p.status = reinterpret_cast<unsigned*>(base);
-  p.tickets = reinterpret_cast<unsigned*>(base + kTicketsOffset);
+  p.combine = reinterpret_cast<unsigned long long*>(base + kCombineOffset);
   p.partials = reinterpret_cast<float*>(base + kPartialsOffset);
   const Plan plan = make_plan(m, p.nKB, p.nRU, *info);
   p.ctas_per_kb = plan.ctas_per_kb;

@@ -17,7 +17,7 @@
 namespace {
 
 constexpr size_t kStaticScratchBytes = (size_t)FB_W3_STATIC_SCRATCH_BYTES;
-constexpr size_t kControlBytes = 16384;  // status word and tickets: must be zero when a call starts
+constexpr size_t kControlBytes = 16384;  // status word; the split-K combine words follow it (8 bytes per activation row and output row)
 
 static __device__ __align__(256) unsigned char g_w3_static_scratch[kStaticScratchBytes];
 
@@ -62,8 +62,9 @@ extern "C" int fb_w3_gemv_static(const void* x, int act_dtype, int m, const uint
                     need, kStaticScratchBytes);
   void* scratch = static_scratch_address();
   if (!scratch) return FB_ECUDA;
-  // The array keeps whatever the previous call left; the control block has to start at zero.
-  cudaError_t err = cudaMemsetAsync(scratch, 0, kControlBytes, static_cast<cudaStream_t>(stream));
+  // The array keeps whatever the previous call left (a call that failed on the device may leave
+  // combine words behind); the status word and this call's combine words have to start at zero.
+  cudaError_t err = cudaMemsetAsync(scratch, 0, kControlBytes + (size_t)m * out_features * 8, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) return fb::cuda_fail(err, "cudaMemsetAsync(static W3 scratch control block)");
   return fb_w3_gemv(x, act_dtype, m, planes, scales, scale_dtype, zeros, perm, out, out_features, in_features,
                     scratch, kStaticScratchBytes, flags, stream);

@@ -292,7 +292,7 @@ class PackedHybridLinear(nn.Module):
         load_extension(self.kernel)
         self._workspace = torch.empty(workspace_shape(self.out_features, self.in_features, self.groups_per_split,
                                                       kernel=self.kernel), device=device, dtype=torch.float32)
-        _native.scratch_for(device, _native.bb_scratch_bytes(self.out_features, self.in_features, False))
+        _native.scratch_for(device, _native.bb_scratch_bytes(self.out_features, self.in_features, False), "bb")
         self._decode_output = torch.empty((1, self.out_features), device=device, dtype=dtype)
         output = self._decode_output
         shaped = output.view(1, 1, self.out_features)

@@ -43,8 +43,9 @@ def test_library_exports_every_declared_symbol():
     for symbol in declared:
         assert hasattr(lib, symbol), symbol
     lib.fb_w3_gemv_scratch_bytes.restype = ctypes.c_size_t
-    assert lib.fb_w3_gemv_scratch_bytes(1, 4096, 4096) == 16384 + 16 * 4096 * 4
-    assert lib.fb_w3_gemv_scratch_bytes(1, 64, 256) == 16384  # one K block: no partials
+    assert lib.fb_w3_gemv_scratch_bytes(1, 4096, 4096) == 16384 + (2 << 20)  # status block + combine words
+    assert lib.fb_w3_gemv_scratch_bytes(1, 4096, 12288) == 16384 + (2 << 20) + 16 * 4096 * 4  # + partials of 16 super-blocks
+    assert lib.fb_w3_gemv_scratch_bytes(1, 64, 256) == 16384 + (2 << 20)  # the layout does not depend on the problem
 
 
 def test_workspace_and_extension_variants():

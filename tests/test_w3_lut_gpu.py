@@ -134,10 +134,15 @@ def test_benchmark_shapes_with_zero_points(name):
     lg, xg = to_cuda(layout), x.cuda()
     out, _ = run(lg, xg, row_tile=1024)
     assert_parity(out, reference)
-    # size-independent properties: exact scaling by two, exact under a shift of the rows
-    # by a whole 32-row unit, and zero for all-zero signed codes
+    # size-independent properties: scaling by two (exact in every fp32 step; the K split is
+    # combined in fixed point with steps of 2^-26, which can move a 16-bit rounding boundary in
+    # a rare row, by one ulp), exact under a shift of the rows by a whole 32-row unit, and zero
+    # for all-zero signed codes
     doubled, _ = run(lg, (x * 2).cuda(), row_tile=1024)
-    assert torch.equal(doubled.float(), out.float() * 2)
+    twice = out.float() * 2
+    differing = doubled.float() != twice
+    assert float(differing.float().mean()) <= 2e-3
+    assert float((doubled.float() - twice).abs().max()) <= float(twice.abs().max()) * 2.0 ** -7
     rolled = dict(lg, planes=lg["planes"].roll(32, dims=2), scales=lg["scales"].roll(32, dims=1), zeros=lg["zeros"].roll(32, dims=1))
     assert torch.equal(run(rolled, xg, row_tile=1024)[0], out.roll(32, dims=1))
     flat = dict(lg)
@@ -323,3 +328,31 @@ def test_fused_input_transforms_equal_separate_kernels(dtype):
     array = _native.w3_matrix_list([(lg["planes"], lg["scales"], lg["zeros"], out2, None)])
     assert lib.fb_w3_gemv_fused_input(two.data_ptr(), _native.dtype_tag(dtype), 3, weight.data_ptr(), 1e-6, array, 1,
                                       _native.dtype_tag(torch.float16), k, None, 0, 0, None) == -1
+
+
+def test_split_k_combine_flags_non_finite_partials_and_resets():
+    """The K split is combined in 64-bit fixed point; a non-finite (or absurdly large) partial sum
+    cannot be represented there and is reported as NaN, and the combine words are left clean."""
+    from marlin_style_fluxbin_b200 import _native
+
+    o, k = 96, 1024
+    layout, x_host = make_case(o, k, seed=77)
+    lg = to_cuda(layout)
+    scratch = torch.zeros(_native.w3_scratch_bytes(1, o, k), dtype=torch.uint8, device="cuda")
+    good = torch.empty(1, o, device="cuda", dtype=torch.bfloat16)
+    _native.w3_gemv(x_host.cuda(), lg["planes"], lg["scales"], None, None, good, scratch=scratch)
+    for poison in (float("nan"), float("inf"), 3.0e38):
+        bad_x = x_host.clone()
+        bad_x[0, 300] = poison
+        bad = torch.zeros(1, o, device="cuda", dtype=torch.bfloat16)
+        _native.w3_gemv(bad_x.cuda(), lg["planes"], lg["scales"], None, None, bad, scratch=scratch)
+        torch.cuda.synchronize()
+        # a table lookup only meets the poisoned activation where one of the three plane bits of
+        # that input position is set (the reference's kernel has the same property)
+        touched = ((layout["planes"][300 // 128, :, :, (300 % 128) // 8] >> (300 % 8)) & 1).bool().any(dim=0)
+        assert bool(torch.isnan(bad[0].cpu())[touched].all()), poison
+        assert torch.equal(bad[0].cpu()[~touched], good[0].cpu()[~touched])
+        assert int(scratch.view(torch.int64).abs().sum()) == 0  # status, combine words: all back to zero
+        again = torch.empty_like(good)
+        _native.w3_gemv(x_host.cuda(), lg["planes"], lg["scales"], None, None, again, scratch=scratch)
+        assert torch.equal(again, good)

@@ -39,7 +39,7 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
 def test_static_scratch_rejects_oversized_problem_without_launching():
     from marlin_style_fluxbin_b200 import _native
 
-    o, k = 65536, 4096  # 16 K blocks x 65536 rows of fp32 partials = 4 MiB + control block
+    o, k = 65536, 32640  # 255 groups are walked as 16 super-blocks: 16 x 65536 fp32 partials = 4 MiB, plus the combine words
     assert _native.w3_scratch_bytes(1, o, k) > _native.FB_W3_STATIC_SCRATCH_BYTES
     x, planes, scales, zeros = _problem(64, 256, seed=1)
     out = torch.zeros(1, 64, device="cuda", dtype=torch.bfloat16)
