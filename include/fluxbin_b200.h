@@ -197,6 +197,18 @@ size_t fb_attn_decode_scratch_bytes(int q_heads);
 int fb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, int q_heads, int kv_heads,
                    int head_dim, int length, int max_positions, float scale, int dtype, void* scratch,
                    size_t scratch_bytes, fb_stream_t stream);
+
+/*
+ * fb_qknorm_rope_cache and fb_attn_decode in ONE launch: q, k, v are the raw rows of the new
+ * token; every CTA norms and rotates the q head it serves (and the new k) itself, uses the new
+ * token's k / v directly and one CTA per k/v head writes them into cache row `position`.
+ * Attends over positions 0..position.  Same results, bit for bit, as the two calls.
+ */
+int fb_attn_decode_fused(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
+                         const void* cosv, const void* sinv, void* k_cache, void* v_cache, void* out, int q_heads,
+                         int kv_heads, int head_dim, int position, int max_positions, float eps, float scale, int dtype,
+                         void* scratch, size_t scratch_bytes, fb_stream_t stream);
+
 int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream);
 
 /*

@@ -79,6 +79,9 @@ def library() -> ctypes.CDLL:
         lib.fb_qknorm_rope_cache.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p]
         lib.fb_attn_decode.restype = ctypes.c_int
         lib.fb_attn_decode.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        lib.fb_attn_decode_fused.restype = ctypes.c_int
+        lib.fb_attn_decode_fused.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_float, ctypes.c_int,
+                                                                                         ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
         lib.fb_attn_decode_scratch_bytes.restype = ctypes.c_size_t
         lib.fb_attn_decode_scratch_bytes.argtypes = [ctypes.c_int]
         lib.fb_silu_mul.restype = ctypes.c_int
@@ -282,6 +285,18 @@ def attn_decode(q, k_cache, v_cache, out, length: int, scale: float, scratch) ->
         check(library().fb_attn_decode(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), q.numel() // dim, k_cache.shape[-3], dim,
                                        int(length), k_cache.shape[-2], float(scale), dtype_tag(q.dtype), ptr(scratch),
                                        scratch.numel(), stream_handle(q.device)))
+
+
+def attn_decode_fused(q, k, v, q_weight, k_weight, cos, sin, k_cache, v_cache, out, position: int, eps: float, scale: float,
+                      scratch) -> None:
+    """``qknorm_rope_cache`` + ``attn_decode`` in one launch: raw q/k/v rows of the token at ``position``;
+    writes cache row ``position`` and attends over positions ``0..position``."""
+    dim = k_cache.shape[-1]
+    with torch.cuda.device(q.device):
+        check(library().fb_attn_decode_fused(ptr(q), ptr(k), ptr(v), ptr(q_weight), ptr(k_weight), ptr(cos), ptr(sin), ptr(k_cache),
+                                             ptr(v_cache), ptr(out), q.numel() // dim, k_cache.shape[-3], dim, int(position),
+                                             k_cache.shape[-2], float(eps), float(scale), dtype_tag(q.dtype), ptr(scratch),
+                                             scratch.numel(), stream_handle(q.device)))
 
 
 def silu_mul(gate, up, out) -> None:

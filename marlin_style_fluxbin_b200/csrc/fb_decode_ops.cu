@@ -69,6 +69,7 @@ __global__ void qknorm_rope_cache_kernel(const unsigned short* __restrict__ q, c
 // head_dim 128: a lane holds four consecutive dims.
 constexpr int kAttnWarps = 8;
 constexpr int kAttnMaxSplits = 16;
+constexpr int kAttnBatch = 8;
 constexpr int kAttnSlot = 132;  // 128 outputs + max + sum, padded
 
 __device__ __forceinline__ void unpack4(uint2 raw, int dtype, float* f) {
@@ -78,38 +79,106 @@ __device__ __forceinline__ void unpack4(uint2 raw, int dtype, float* f) {
   f[3] = bits_to_float((unsigned short)(raw.y >> 16), dtype);
 }
 
+// What the fused form needs besides the attention arguments: the raw q/k/v rows of the new
+// token (outputs of the q/k/v GEMV), the per-head norm weights and this position's rotary row.
+struct NewToken {
+  const unsigned short *q, *k, *v, *q_weight, *k_weight, *cosv, *sinv;
+  float eps;
+};
+
+// Per-head RMSNorm + rotary embedding of one 128-wide head by one warp, result (in the 16-bit
+// dtype's bits) into shared memory; the arithmetic of qknorm_rope_cache_kernel.
+__device__ __forceinline__ void norm_rope_head(const unsigned short* src, const unsigned short* weight, const unsigned short* cosv,
+                                               const unsigned short* sinv, float eps, int dtype, int lane, unsigned short* dst) {
+  constexpr int dim = 128, half = 64;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float x = bits_to_float(src[i], dtype);
+    ss += x * x;
+  }
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+  const float inv = rsqrtf(ss / (float)dim + eps);
+  for (int i = lane; i < half; i += 32) {
+    const float lo = bits_to_float(weight[i], dtype) * round_to(bits_to_float(src[i], dtype) * inv, dtype);
+    const float hi = bits_to_float(weight[i + half], dtype) * round_to(bits_to_float(src[i + half], dtype) * inv, dtype);
+    const float nlo = round_to(lo, dtype), nhi = round_to(hi, dtype);
+    const float y0 = round_to(nlo * bits_to_float(cosv[i], dtype), dtype) + (-nhi) * bits_to_float(sinv[i], dtype);
+    const float y1 = round_to(nhi * bits_to_float(cosv[i + half], dtype), dtype) + nlo * bits_to_float(sinv[i + half], dtype);
+    dst[i] = to_bits(y0, dtype);
+    dst[i + half] = to_bits(y1, dtype);
+  }
+}
+
+// FUSED: q arrives raw; the kernel norms and rotates q and the new k itself (every CTA of a head
+// repeats that small piece of work), takes the new token's k / v from shared memory instead of
+// the cache, and one CTA per k/v head writes them into the cache for the steps to come.
+template <bool FUSED>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsigned short* __restrict__ q,
-                                                                      const unsigned short* __restrict__ k_cache,
-                                                                      const unsigned short* __restrict__ v_cache,
+                                                                      unsigned short* __restrict__ k_cache,
+                                                                      unsigned short* __restrict__ v_cache,
                                                                       unsigned short* __restrict__ out, float* __restrict__ scratch,
                                                                       unsigned* __restrict__ tickets, int q_heads, int kv_heads,
-                                                                      int length, int max_positions, float scale, int dtype) {
+                                                                      int length, int max_positions, float scale, int dtype,
+                                                                      const NewToken nt) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int D = 128;
   const int head = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvh = head / (q_heads / kv_heads);
+  const int group = q_heads / kv_heads, kvh = head / group;
   const unsigned short* kbase = k_cache + (size_t)kvh * max_positions * D + lane * 4;
   const unsigned short* vbase = v_cache + (size_t)kvh * max_positions * D + lane * 4;
   const int chunk = (length + splits - 1) / splits;
   const int p0 = split * chunk, p1 = min(length, p0 + chunk);
+  const int newest = length - 1;  // FUSED: the token being decoded, not in the cache yet
+  __shared__ __align__(8) unsigned short sm_new[3][D];  // rotated q, rotated k, v of the new token
+  // A warp takes kAttnBatch positions at a time with all their loads in flight; the first batch
+  // is requested before the q/k prologue so that the two round trips overlap.
+  uint2 kr[kAttnBatch], vr[kAttnBatch];
+  auto fetch = [&](int base) {
+#pragma unroll
+    for (int j = 0; j < kAttnBatch; ++j) {
+      const int pos = min(base + j, p1 - 1);
+      if (base < p1 && !(FUSED && pos == newest)) {
+        kr[j] = *reinterpret_cast<const uint2*>(kbase + (size_t)pos * D);
+        vr[j] = *reinterpret_cast<const uint2*>(vbase + (size_t)pos * D);
+      } else {
+        kr[j] = vr[j] = make_uint2(0u, 0u);
+      }
+    }
+  };
+  fetch(p0 + warp * kAttnBatch);
   float qv[4];
-  unpack4(*reinterpret_cast<const uint2*>(q + (size_t)head * D + lane * 4), dtype, qv);
+  if (FUSED) {
+    if (warp == 0) norm_rope_head(nt.q + (size_t)head * D, nt.q_weight, nt.cosv, nt.sinv, nt.eps, dtype, lane, sm_new[0]);
+    if (warp == 1) norm_rope_head(nt.k + (size_t)kvh * D, nt.k_weight, nt.cosv, nt.sinv, nt.eps, dtype, lane, sm_new[1]);
+    if (warp == 2) *reinterpret_cast<uint2*>(&sm_new[2][lane * 4]) = *reinterpret_cast<const uint2*>(nt.v + (size_t)kvh * D + lane * 4);
+    __syncthreads();
+    if (head % group == 0 && split == splits - 1 && warp < 2) {  // the cache row of the new token
+      unsigned short* row = (warp == 0 ? k_cache : v_cache) + ((size_t)kvh * max_positions + newest) * D;
+      *reinterpret_cast<uint2*>(row + lane * 4) = *reinterpret_cast<const uint2*>(&sm_new[1 + warp][lane * 4]);
+    }
+    unpack4(*reinterpret_cast<const uint2*>(&sm_new[0][lane * 4]), dtype, qv);
+  } else {
+    unpack4(*reinterpret_cast<const uint2*>(q + (size_t)head * D + lane * 4), dtype, qv);
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) qv[i] *= scale;
   float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int base = p0 + warp * 4; base < p1; base += kAttnWarps * 4) {
-    uint2 kr[4], vr[4];
+  for (int base = p0 + warp * kAttnBatch; base < p1; base += kAttnWarps * kAttnBatch) {
+    if (base != p0 + warp * kAttnBatch) fetch(base);
+    if (FUSED) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int pos = min(base + j, p1 - 1);
-      kr[j] = *reinterpret_cast<const uint2*>(kbase + (size_t)pos * D);
-      vr[j] = *reinterpret_cast<const uint2*>(vbase + (size_t)pos * D);
+      for (int j = 0; j < kAttnBatch; ++j)
+        if (min(base + j, p1 - 1) == newest) {
+          kr[j] = *reinterpret_cast<const uint2*>(&sm_new[1][lane * 4]);
+          vr[j] = *reinterpret_cast<const uint2*>(&sm_new[2][lane * 4]);
+        }
     }
-    float s[4];
+    float s[kAttnBatch];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kAttnBatch; ++j) {
       float kf[4];
       unpack4(kr[j], dtype, kf);
       s[j] = qv[0] * kf[0] + qv[1] * kf[1] + qv[2] * kf[2] + qv[3] * kf[3];
@@ -117,10 +186,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
     for (int d = 16; d >= 1; d >>= 1) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], d);
+      for (int j = 0; j < kAttnBatch; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], d);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kAttnBatch; ++j) {
       if (base + j < p1) {
         const float m_new = fmaxf(m, s[j]);
         const float correction = __expf(m - m_new), pj = __expf(s[j] - m_new);
@@ -134,7 +203,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
     }
   }
   __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps], sm_acc[kAttnWarps][D];
-  __shared__ unsigned last_flag;
   if (lane == 0) {
     sm_m[warp] = m;
     sm_l[warp] = l;
@@ -155,6 +223,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[i] += sm_acc[w][lane * 4 + i] * f;
     }
+    if (splits == 1) {  // nothing to merge: no scratch round trip
+      const float inv1 = 1.f / total;
+      uint2 direct;
+      direct.x = (uint32_t)to_bits(o[0] * inv1, dtype) | ((uint32_t)to_bits(o[1] * inv1, dtype) << 16);
+      direct.y = (uint32_t)to_bits(o[2] * inv1, dtype) | ((uint32_t)to_bits(o[3] * inv1, dtype) << 16);
+      *reinterpret_cast<uint2*>(out + (size_t)head * D + lane * 4) = direct;
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) slot[lane * 4 + i] = o[i];
     if (lane == 0) {
@@ -163,21 +239,37 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
     }
     __threadfence();
     __syncwarp();
-    if (lane == 0) last_flag = atomicAdd(&tickets[head], 1u) == (unsigned)splits - 1u;
+    unsigned prior = 0;
+    if (lane == 0) prior = atomicAdd(&tickets[head], 1u);
+    prior = __shfl_sync(0xffffffffu, prior, 0);
+    if (prior != (unsigned)splits - 1u) return;
+    __threadfence();
+  } else {
+    return;
   }
-  __syncthreads();
-  if (!last_flag || warp != 0) return;
-  __threadfence();
+  // Merge of the splits by one warp with every load in flight at once: lane sp fetches the
+  // (max, sum) of split sp, the rescaling factors come from shuffles, and each lane fetches its
+  // four output dims of all splits before the first use.  Sums run in ascending split order.
   const float* base_slot = scratch + (size_t)head * kAttnMaxSplits * kAttnSlot;
-  float gm = -INFINITY;
-  for (int sp = 0; sp < splits; ++sp) gm = fmaxf(gm, __ldcg(base_slot + sp * kAttnSlot + 128));
-  float total = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int sp = 0; sp < splits; ++sp) {
-    const float sm = __ldcg(base_slot + sp * kAttnSlot + 128);
-    const float f = sm == -INFINITY ? 0.f : __expf(sm - gm);
-    total += __ldcg(base_slot + sp * kAttnSlot + 129) * f;
+  const float my_m = lane < splits ? __ldcg(base_slot + lane * kAttnSlot + 128) : -INFINITY;
+  const float my_l = lane < splits ? __ldcg(base_slot + lane * kAttnSlot + 129) : 0.f;
+  float4 part[kAttnMaxSplits];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] += __ldcg(base_slot + sp * kAttnSlot + lane * 4 + i) * f;
+  for (int sp = 0; sp < kAttnMaxSplits; ++sp)
+    part[sp] = sp < splits ? __ldcg(reinterpret_cast<const float4*>(base_slot + sp * kAttnSlot + lane * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float gm = my_m;
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, d));
+  const float my_f = my_m == -INFINITY ? 0.f : __expf(my_m - gm);
+  float total = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int sp = 0; sp < kAttnMaxSplits; ++sp) {
+    const float f = __shfl_sync(0xffffffffu, my_f, sp);
+    total += __shfl_sync(0xffffffffu, my_l, sp) * f;
+    o[0] += part[sp].x * f;
+    o[1] += part[sp].y * f;
+    o[2] += part[sp].z * f;
+    o[3] += part[sp].w * f;
   }
   const float inv = 1.f / total;
   uint2 packed;
@@ -253,8 +345,33 @@ extern "C" int fb_attn_decode(const void* q, const void* k_cache, const void* v_
   if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
   float* partial = static_cast<float*>(scratch);
   unsigned* tickets = reinterpret_cast<unsigned*>(partial + (size_t)q_heads * kAttnMaxSplits * kAttnSlot);
-  return launch_pdl(attn_decode_kernel, dim3(q_heads, splits), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode launch",
-                    u16(q), u16(k_cache), u16(v_cache), u16(out), partial, tickets, q_heads, kv_heads, length, max_positions, scale, dtype);
+  return launch_pdl(attn_decode_kernel<false>, dim3(q_heads, splits), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode launch",
+                    u16(q), const_cast<unsigned short*>(u16(k_cache)), const_cast<unsigned short*>(u16(v_cache)), u16(out), partial, tickets,
+                    q_heads, kv_heads, length, max_positions, scale, dtype, NewToken{});
+}
+
+extern "C" int fb_attn_decode_fused(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
+                                    const void* cosv, const void* sinv, void* k_cache, void* v_cache, void* out, int q_heads,
+                                    int kv_heads, int head_dim, int position, int max_positions, float eps, float scale, int dtype,
+                                    void* scratch, size_t scratch_bytes, fb_stream_t stream) {
+  if (!q || !k || !v || !q_weight || !k_weight || !cosv || !sinv || !k_cache || !v_cache || !out) return fail(FB_EINVAL, "fb_attn_decode_fused: null pointer");
+  if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_attn_decode_fused: dtype must be FB_F16 or FB_BF16");
+  if (head_dim != 128) return fail(FB_ELIMIT, "fb_attn_decode_fused: head_dim must be 128");
+  if (q_heads < 1 || kv_heads < 1 || q_heads % kv_heads) return fail(FB_ELIMIT, "fb_attn_decode_fused: q_heads must be a multiple of kv_heads");
+  if (position < 0 || position >= max_positions) return fail(FB_ELIMIT, "fb_attn_decode_fused: position %d outside the cache of %d", position, max_positions);
+  if (!aligned(q, 8) || !aligned(k, 8) || !aligned(v, 8) || !aligned(k_cache, 8) || !aligned(v_cache, 8) || !aligned(out, 8))
+    return fail(FB_EINVAL, "fb_attn_decode_fused: tensors must be 8-byte aligned");
+  const size_t need = fb_attn_decode_scratch_bytes(q_heads);
+  if (!scratch || scratch_bytes < need || !aligned(scratch, 16)) return fail(FB_ESCRATCH, "fb_attn_decode_fused: 16-byte aligned scratch of %zu bytes needed", need);
+  const int length = position + 1;
+  int splits = (length + 63) / 64;
+  if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
+  float* partial = static_cast<float*>(scratch);
+  unsigned* tickets = reinterpret_cast<unsigned*>(partial + (size_t)q_heads * kAttnMaxSplits * kAttnSlot);
+  const NewToken nt = {u16(q), u16(k), u16(v), u16(q_weight), u16(k_weight), u16(cosv), u16(sinv), eps};
+  return launch_pdl(attn_decode_kernel<true>, dim3(q_heads, splits), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode_fused launch",
+                    static_cast<const unsigned short*>(nullptr), u16(k_cache), u16(v_cache), u16(out), partial, tickets, q_heads, kv_heads, length,
+                    max_positions, scale, dtype, nt);
 }
 
 extern "C" int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream) {

@@ -49,7 +49,7 @@
 #define FB_WAVE_MARK(w, which)                                                                         \
   do {                                                                                               \
     if (lane == 0 && (warp == 0 || warp == 7) && (w) < 8)                                            \
-      reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((blockIdx.x * 2 + (warp == 7)) * 8 + (w)) * 4 + (which)] = clock64(); \
+      reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((blockIdx.x * 2 + (warp == 7)) * 8 + (w)) * 8 + (which)] = clock64(); \
   } while (0)
 #else
 #define FB_MARK(i) \
@@ -531,7 +531,9 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       // too, so the issuing lanes do not stall on the slowest warp of the current wave.
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bars[slot])) : "memory");
+      FB_WAVE_MARK(seq, 4);
       if (!dead && seq >= 1 && seq - 1 + kRing < total_waves) issue_seq(seq - 1 + kRing);
+      FB_WAVE_MARK(seq, 5);
 
       if (!dead && mine) {
         const float sA = bits_to_float(sbitsA, p.scale_dtype);

@@ -85,7 +85,8 @@ class DecodeEngine:
     """``arm`` is ``"w3"`` (packed kernels) or ``"bf16"`` (dense dequantised weights, cuBLAS)."""
 
     def __init__(self, shape: ModelShape, *, device, max_positions: int, arm: str = "w3", seed: int = 20260916,
-                 tp_rank: int = 0, tp_size: int = 1, group=None, dtype=torch.bfloat16, fuse_inputs: bool = True):
+                 tp_rank: int = 0, tp_size: int = 1, group=None, dtype=torch.bfloat16, fuse_inputs: bool = True,
+                 fuse_attention: bool = True):
         if arm not in ("w3", "bf16"):
             raise ValueError("arm must be w3 or bf16")
         if shape.q_heads % tp_size or shape.kv_heads % tp_size or (shape.hidden // 128) % tp_size or (shape.intermediate // 128) % tp_size:
@@ -95,6 +96,8 @@ class DecodeEngine:
         self.max_positions = max_positions
         # RMSNorm and the SwiGLU gate run inside the GEMV that consumes them (w3 arm only)
         self.fuse_inputs = fuse_inputs
+        # q/k-norm, RoPE and the cache write run inside the attention launch (both arms)
+        self.fuse_attention = fuse_attention
         s, p = shape, tp_size
         self.q_heads, self.kv_heads = s.q_heads // p, s.kv_heads // p
         self.inter = s.intermediate // p
@@ -234,9 +237,13 @@ class DecodeEngine:
                 self.k.copy_(qkv[:, self.q.numel():self.q.numel() + self.k.numel()])
                 self.v.copy_(qkv[:, self.q.numel() + self.k.numel():])
                 launches += 3
-            nat.qknorm_rope_cache(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.q_rot,
-                                  self.k_cache[index], self.v_cache[index], position, s.eps)
-            nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale, self.attn_scratch)
+            if self.fuse_attention:
+                nat.attn_decode_fused(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.k_cache[index],
+                                      self.v_cache[index], self.attn, position, s.eps, scale, self.attn_scratch)
+            else:
+                nat.qknorm_rope_cache(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.q_rot,
+                                      self.k_cache[index], self.v_cache[index], position, s.eps)
+                nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale, self.attn_scratch)
             if w3:
                 nat.w3_gemv_multi(self.attn, layer.o_list, 1, s.hidden, f16, None, scratch=self.scratch)
             else:
@@ -270,7 +277,7 @@ class DecodeEngine:
                     self.h.add_(self.h_next)
                     launches += 1
             self._allreduce(self.h)
-            launches += (6 if fuse else 9) + (2 if self.tp_size > 1 else 0)
+            launches += (6 if fuse else 9) - (1 if self.fuse_attention else 0) + (2 if self.tp_size > 1 else 0)
         nat.rmsnorm(self.h, self.final_norm, self.xn, s.eps)
         torch.mm(self.xn, self.lm_head.t(), out=self.logits)
         torch.argmax(self.logits, dim=-1, out=self.next_token)

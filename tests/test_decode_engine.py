@@ -86,5 +86,43 @@ def test_fused_input_launches_match_separate_glue_kernels():
         engine = DecodeEngine(shape, device="cuda", max_positions=64, arm="w3", seed=7, fuse_inputs=fuse)
         first = engine.prefill(ids).argmax(-1)
         _, _, logits[fuse] = engine.decode(first, prompt, 4)
-        assert engine.launches_per_step == 4 + shape.layers * (6 if fuse else 9)
+        assert engine.launches_per_step == 4 + shape.layers * (5 if fuse else 8)
     assert nrmse(logits[True], logits[False]) < 5e-3, nrmse(logits[True], logits[False])
+
+
+@pytest.mark.parametrize("position", (0, 5, 63, 200, 1500))
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+def test_fused_attention_equals_the_two_launch_form(position, dtype):
+    """q/k-norm + RoPE + cache write inside the attention launch: outputs and cache rows are
+    bit-identical to fb_qknorm_rope_cache followed by fb_attn_decode."""
+    from marlin_style_fluxbin_b200 import _native
+
+    q_heads, kv_heads, dim, max_positions = 8, 2, 128, 1536
+    gen = torch.Generator().manual_seed(position + 1)
+    rnd = lambda *shape: torch.randn(*shape, generator=gen).to(dtype).cuda()  # noqa: E731
+    q, k, v = rnd(1, q_heads * dim), rnd(1, kv_heads * dim), rnd(1, kv_heads * dim)
+    q_weight, k_weight = (1 + 0.1 * rnd(dim)), (1 + 0.1 * rnd(dim))
+    angle = torch.rand(dim // 2, generator=gen) * 6.28
+    cos, sin = torch.cat([angle.cos()] * 2).to(dtype).cuda(), torch.cat([angle.sin()] * 2).to(dtype).cuda()
+    caches = [rnd(kv_heads, max_positions, dim) for _ in range(2)]
+    scale = dim ** -0.5
+    scratch = torch.zeros(_native.attn_scratch_bytes(q_heads), dtype=torch.uint8, device="cuda")
+
+    k_a, v_a = caches[0].clone(), caches[1].clone()
+    q_rot, out_a = torch.empty_like(q), torch.empty_like(q)
+    _native.qknorm_rope_cache(q, k, v, q_weight, k_weight, cos, sin, q_rot, k_a, v_a, position, 1e-6)
+    _native.attn_decode(q_rot, k_a, v_a, out_a, position + 1, scale, scratch)
+
+    k_b, v_b = caches[0].clone(), caches[1].clone()
+    out_b = torch.full_like(q, float("nan"))
+    _native.attn_decode_fused(q, k, v, q_weight, k_weight, cos, sin, k_b, v_b, out_b, position, 1e-6, scale, scratch)
+    torch.cuda.synchronize()
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+    # and against plain tensor math (fp32 softmax over the 16-bit cache)
+    keys, values = k_a[:, :position + 1].float(), v_a[:, :position + 1].float()
+    heads = q_rot.view(q_heads, dim).float()
+    group = q_heads // kv_heads
+    scores = torch.einsum("hd,hpd->hp", heads, keys.repeat_interleave(group, dim=0)) * scale
+    want = torch.einsum("hp,hpd->hd", scores.softmax(-1), values.repeat_interleave(group, dim=0)).reshape(1, -1)
+    assert (out_b.float() - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
