@@ -12,10 +12,12 @@
 //    lanes address 32 different tables: all table lookups are bank-conflict free by
 //    construction, whatever the weights are.  The same rotation makes the reads of the
 //    staged weight words conflict free.
-//  * The three bit planes of a warp's units (contiguous rows, so 6 copies of n x 512
-//    bytes) are staged into shared memory with bulk asynchronous copies (cp.async.bulk
-//    + mbarrier), a wave of one unit per warp at a time, one (group, plane) copy per
-//    issuing lane; a lookup address is a rotate and one logic op on the staged weight word.
+//  * The three bit planes of a unit (6 runs of 512 bytes: group half x plane) are staged into
+//    shared memory with bulk asynchronous copies (cp.async.bulk + mbarrier), six lanes issuing
+//    one run each in the same instruction.  Every warp owns a private ring of three staged
+//    units and refills a slot as soon as it has read it, so warps never wait for one another
+//    between table builds; scales and zero points come straight from global memory, requested
+//    before the lookups and used after them.
 //  * Two CTAs per SM: each K block is served by floor(2 SMs / K blocks) CTAs that split its rows.
 //  * Launched with programmatic dependent launch: a kernel's prologue and first weight
 //    copies overlap the tail of the previous kernel in the stream; everything that
@@ -32,7 +34,11 @@
 // scale, fp32 accumulation; tables hold ascending-order subset sums as in
 // csrc/lut8_unsigned.cuh:12-27.  Extension over the reference: fp16 or bf16 scales and
 // an optional per-(group,row) zero point, y += scale*(4-zero)*sum(x_group).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 #include <mutex>
+#include <unordered_map>
 
 #ifndef FB_W3_TRACE
 #define FB_W3_TRACE 0
@@ -71,11 +77,7 @@ constexpr int kPlaneTile = kUnitRows * 16;  // 512 B: one plane of one group for
 constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
 constexpr int kWarps = 8;
 constexpr int kCtasPerSm = 2;
-constexpr int kRing = 3;                           // waves staged per CTA
-constexpr int kWavePlanes = kWarps * kUnitBytes;   // 24 KB of bit planes: one unit per warp
-constexpr int kWaveScales = 2 * kWarps * kUnitRows * 2;  // 1 KB: 16-bit scales of two groups
-constexpr int kWaveZeros = 2 * kWarps * kUnitRows;       // 512 B: zero points of two groups
-constexpr int kWaveBytes = kWavePlanes + kWaveScales + kWaveZeros;
+constexpr int kStages = 3;  // units staged ahead per warp (each warp owns a private ring)
 constexpr int kMaxM = 4;
 constexpr int kMaxSplits = 16;  // partial sums per output (one arrival count of 6 bits, 52-bit fixed-point sum)
 
@@ -94,6 +96,9 @@ struct W3Matrix {
 };
 
 struct W3Params {
+  // One tiled-copy descriptor per matrix: the planes seen as uint32 [G*3][O/32][128], so that a
+  // box of 6 x 1 x 128 is the six 512-byte runs of one unit (two groups x three planes).
+  alignas(64) CUtensorMap plane_maps[kMaxMatrices];
   const void* x;
   W3Matrix mats[kMaxMatrices];
   int n_mats;
@@ -127,16 +132,15 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 template <int M, bool CORRECT>
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const W3Params p) {
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const __grid_constant__ W3Params p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   using Geom = LutGeom<M>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* const lut = smem;
-  // Ring of kRing staged waves; a wave is one 32-row unit per warp (contiguous rows), laid out
-  // [group half * 3 + plane][warp][32 rows x 16 B], so each (half, plane) is ONE copy of up to 4 KB.
+  // Every warp owns a private ring of kStages staged units, [stage][group half * 3 + plane][32 rows
+  // x 16 B], and one mbarrier per stage: warps never wait for one another between table builds.
   unsigned char* const ring = smem + Geom::kBytes;
-  uint64_t* const full_bars = reinterpret_cast<uint64_t*>(smem + Geom::kBytes + (size_t)kRing * kWaveBytes);
-  uint64_t* const empty_bars = full_bars + kRing;
+  uint64_t* const full_bars = reinterpret_cast<uint64_t*>(smem + Geom::kBytes + (size_t)kWarps * kStages * kUnitBytes);
 
   FB_MARK(0);
   // The next kernel in the stream may start its own prologue (weight prefetch) now; it
@@ -148,10 +152,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   if ((int)blockIdx.x >= nV) return;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kRing; ++s) {
-      mbar_init(smem_u32(&full_bars[s]), kWarps);   // every warp's lane 0 issues part of a wave
-      mbar_init(smem_u32(&empty_bars[s]), kWarps);  // every warp releases a wave after reading it
-    }
+    for (int s = 0; s < kWarps * kStages; ++s) mbar_init(smem_u32(&full_bars[s]), 1);  // the issuing lane's expect_tx
     mbar_init_fence();
   }
   __syncthreads();
@@ -172,61 +173,33 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     return j;
   };
   bool dead = false;
-  // Stage wave number `seq` (counted over the whole kernel): units [first, first + n) of K
-  // block kb.  Lane 0 of warps 0..5 each copy one (half, plane); a slot is reused only after
-  // all warps have released the wave that occupied it.
-  auto issue_wave = [&](int seq, int kb, int first, int n) {
-    if (lane == 0) {
-      const int slot = seq % kRing;
-      if (seq >= kRing && !mbar_wait_bounded(smem_u32(&empty_bars[slot]), (uint32_t)((seq / kRing - 1) & 1)))
-        atomicExch(p.status, 2u);
-      const int ngroups = min(2, p.G - 2 * kb);
-      const uint32_t bar = smem_u32(&full_bars[slot]);
-      const uint32_t slot_u32 = smem_u32(ring + (size_t)slot * kWaveBytes);
-      if (warp < 6) {  // bit planes: warp = group half * 3 + plane
-        const bool present = warp < 3 * ngroups;
-        mbar_expect_tx(bar, present ? (uint32_t)(n * kPlaneTile) : 0u);
-        uint32_t dst = slot_u32 + (uint32_t)(warp * kWarps * kPlaneTile);
-        while (present && n > 0) {  // one copy per matrix the wave touches
-          const int j = locate(first);
-          const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
-          const int run = min(n, end - first);
-          const uint8_t* src = p.mats[j].planes +
-                               (((size_t)(2 * kb) * 3 + warp) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * 16;
-          bulk_g2s(dst, src, (uint32_t)(run * kPlaneTile), bar);
-          dst += run * kPlaneTile;
-          first += run;
-          n -= run;
-        }
-      } else {  // warp 6: the scales of both groups, warp 7: their zero points (if any)
-        const int elem = warp == 6 ? 2 : 1;  // bytes per row
-        uint32_t bytes = 0;
-        for (int u = first, left = n; left > 0;) {
-          const int j = locate(u);
-          const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
-          const int run = min(left, end - u);
-          if (warp == 6 || p.mats[j].zeros) bytes += (uint32_t)(ngroups * run * kUnitRows * elem);
-          u += run;
-          left -= run;
-        }
-        mbar_expect_tx(bar, bytes);
-        uint32_t dst = slot_u32 + (uint32_t)(warp == 6 ? kWavePlanes : kWavePlanes + kWaveScales);
-        while (n > 0) {
-          const int j = locate(first);
-          const int end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
-          const int run = min(n, end - first);
-          const unsigned char* base = warp == 6 ? reinterpret_cast<const unsigned char*>(p.mats[j].scales) : p.mats[j].zeros;
-          if (base) {
-            for (int h = 0; h < ngroups; ++h)
-              bulk_g2s(dst + (uint32_t)(h * kWarps * kUnitRows * elem),
-                       base + ((size_t)(2 * kb + h) * p.mats[j].O + (size_t)(first - p.mats[j].ru_begin) * kUnitRows) * elem,
-                       (uint32_t)(run * kUnitRows * elem), bar);
-          }
-          dst += run * kUnitRows * elem;
-          first += run;
-          n -= run;
-        }
+  // Stage this warp's task t (its t-th unit, counted over the K blocks the CTA walks) into ring
+  // slot t % kStages: lane 0 announces the bytes, then lanes 0..5 each copy one 512-byte
+  // (group half, plane) run in the same instruction.  The slot is free: the warp itself finished
+  // reading it (all lanes pass the __syncwarp before this is called).
+  auto issue_unit = [&](int t, int kb_, int ru) {
+    const int slot = t % kStages;
+    const int ngroups = min(2, p.G - 2 * kb_);
+    const uint32_t bar = smem_u32(&full_bars[warp * kStages + slot]);
+    if (ngroups == 2) {  // one tiled copy brings all six runs
+      if (lane == 0) {
+        const int j = locate(ru);
+        mbar_expect_tx(bar, (uint32_t)kUnitBytes);
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                smem_u32(ring + (size_t)(warp * kStages + slot) * kUnitBytes)),
+            "l"(&p.plane_maps[j]), "r"(0), "r"(ru - p.mats[j].ru_begin), "r"(6 * kb_), "r"(bar)
+            : "memory");
       }
+      return;
+    }
+    // a single trailing group: three plain runs
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(3 * ngroups * kPlaneTile));
+    __syncwarp();
+    if (lane < 3 * ngroups) {
+      const W3Matrix& mat = p.mats[locate(ru)];
+      const uint8_t* src = mat.planes + (((size_t)(2 * kb_) * 3 + lane) * mat.O + (size_t)(ru - mat.ru_begin) * kUnitRows) * 16;
+      bulk_g2s(smem_u32(ring + ((size_t)(warp * kStages + slot) * 6 + lane) * kPlaneTile), src, (uint32_t)kPlaneTile, bar);
     }
   };
   // Final value of one output element: rounded to the 16-bit dtype, then the optional residual
@@ -253,7 +226,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
     for (int jw = 0; jw < 4; ++jw) {
-      woff[jh][jw] = (uint32_t)(((jh ^ rh) * 3) * kWarps * kPlaneTile + ((jw + rw) & 3) * 4);
+      woff[jh][jw] = (uint32_t)(((jh ^ rh) * 3) * kPlaneTile + ((jw + rw) & 3) * 4);
 #pragma unroll
       for (int b = 0; b < 4; ++b)
         xl[jh][jw][b] = lut_u32 + (uint32_t)(64 * (jh ^ rh) + 16 * ((jw + rw) & 3) + 4 * ((b + rb) & 3));
@@ -270,18 +243,19 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   };
   auto table_of = [&](int m) { return lut + m * 128; };
 
-  // This CTA walks the K blocks kb_begin .. kb_begin + nS - 1 over the same rows; its staged
-  // waves form one sequence across them: wave j = (K block j / waves, row wave j % waves).
+  // This CTA walks the K blocks kb_begin .. kb_begin + nS - 1 over the same rows.  Warp w takes
+  // the units cta_first + w, + kWarps, ...; its tasks are numbered t = K block * my_count + unit.
   int sb, cta_first, cta_count;
   share((int)blockIdx.x, sb, cta_first, cta_count);
   const int kb_begin = sb * p.S, nS = min(p.S, p.nKB - kb_begin);
-  const int waves = (cta_count + kWarps - 1) / kWarps, total_waves = nS * waves;
-  auto issue_seq = [&](int j) {
-    const int s = (int)((unsigned)j / (unsigned)waves), i = j - s * waves;
-    issue_wave(j, kb_begin + s, cta_first + i * kWarps, min(kWarps, cta_count - i * kWarps));
+  const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
+  const int my_tasks = nS * my_count;
+  auto issue_task = [&](int t) {
+    const int s = (int)((unsigned)t / (unsigned)my_count), i = t - s * my_count;
+    issue_unit(t, kb_begin + s, cta_first + i * kWarps + warp);
   };
   FB_MARK(12);
-  for (int j = 0; j < kRing && j < total_waves; ++j) issue_seq(j);  // weights never change: no need to wait
+  for (int t = 0; t < kStages && t < my_tasks; ++t) issue_task(t);  // weights never change: no need to wait
   FB_MARK(1);
 
   // Everything below reads activations and writes scratch / outputs of this stream.
@@ -433,33 +407,31 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     // ---- this warp's units ----
     const int gA = 2 * kb, gB = 2 * kb + 1;
     const bool hasB = gB < p.G;
-    for (int i = 0; i < waves; ++i) {
-      const int seq = s * waves + i, slot = seq % kRing;
-      const bool mine = i * kWarps + warp < cta_count;  // the last wave may be short
-      const int ru = cta_first + i * kWarps + (mine ? warp : 0);
+    for (int i = 0; i < my_count; ++i) {
+      const int seq = s * my_count + i, slot = seq % kStages;
+      const bool mine = true;
+      const int ru = cta_first + i * kWarps + warp;
       const int row = ru * kUnitRows + lane;  // in the concatenated row space
       const W3Matrix& mat = p.mats[locate(ru)];
       const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
+      // scales and zero points straight from global memory (one coalesced 64-byte run per group):
+      // requested now, needed only after the lookups
+      unsigned short sbitsA = 0, sbitsB = 0;
+      unsigned char zA = 4, zB = 4;
+      if (!dead) {
+        sbitsA = __ldg(mat.scales + (size_t)gA * mat.O + lrow);
+        if (hasB) sbitsB = __ldg(mat.scales + (size_t)gB * mat.O + lrow);
+        if (mat.zeros) {
+          zA = __ldg(mat.zeros + (size_t)gA * mat.O + lrow);
+          if (hasB) zB = __ldg(mat.zeros + (size_t)gB * mat.O + lrow);
+        }
+      }
       FB_WAVE_MARK(seq, 0);
-      bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[slot]), (uint32_t)((seq / kRing) & 1));
+      bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[warp * kStages + slot]), (uint32_t)((seq / kStages) & 1));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && !dead) {
         dead = true;
         if (lane == 0) atomicExch(p.status, 1u);
-      }
-      // scales and zero points of this unit were staged with the wave
-      unsigned short sbitsA = 0, sbitsB = 0;
-      float zcA = 0.f, zcB = 0.f;
-      if (mine && !dead) {
-        const unsigned char* side = ring + (size_t)slot * kWaveBytes + kWavePlanes;
-        const unsigned short* sc = reinterpret_cast<const unsigned short*>(side) + warp * kUnitRows + lane;
-        sbitsA = sc[0];
-        if (hasB) sbitsB = sc[kWarps * kUnitRows];
-        if (mat.zeros) {
-          const unsigned char* zp = side + kWaveScales + warp * kUnitRows + lane;
-          zcA = 4.f - (float)zp[0];
-          if (hasB) zcB = 4.f - (float)zp[kWarps * kUnitRows];
-        }
       }
       // later K blocks of the super-block add to the partial this same thread stored before
       float prev[M];
@@ -485,13 +457,13 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
 #define FB_W3_ABLATE 0
 #endif
       if (!dead && mine && !(FB_W3_ABLATE & 1)) {
-        const uint32_t wbase = ring_u32 + (uint32_t)(slot * kWaveBytes + warp * kPlaneTile + lane * 16);
+        const uint32_t wbase = ring_u32 + (uint32_t)((warp * kStages + slot) * kUnitBytes + lane * 16);
         // staged words are fetched one (half, word) step ahead of their use: six live registers
         auto fetch = [&](int jh, int jw, uint32_t (&dst)[3]) {
           const uint32_t wa = wbase + woff[jh][jw];
           asm volatile("ld.shared.u32 %0, [%1];" : "=r"(dst[0]) : "r"(wa));
-          asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[1]) : "r"(wa), "n"(kWarps * kPlaneTile));
-          asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[2]) : "r"(wa), "n"(2 * kWarps * kPlaneTile));
+          asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[1]) : "r"(wa), "n"(kPlaneTile));
+          asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[2]) : "r"(wa), "n"(2 * kPlaneTile));
         };
         uint32_t cur[3], nxt[3];
         fetch(0, 0, cur);
@@ -526,13 +498,10 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       FB_MARK(5);
       FB_WAVE_MARK(seq, 2);
 
-      // all lanes are done with the staged bytes: release the wave.  The slot released one
-      // iteration AGO is refilled now: by this time the other warps have normally released it
-      // too, so the issuing lanes do not stall on the slowest warp of the current wave.
+      // all lanes are done with the staged bytes: the slot takes this warp's task kStages ahead
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bars[slot])) : "memory");
       FB_WAVE_MARK(seq, 4);
-      if (!dead && seq >= 1 && seq - 1 + kRing < total_waves) issue_seq(seq - 1 + kRing);
+      if (!dead && seq + kStages < my_tasks) issue_task(seq + kStages);
       FB_WAVE_MARK(seq, 5);
 
       if (!dead && mine) {
@@ -545,8 +514,8 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           const float second = plane_sum(1, 0) + 2.f * plane_sum(1, 1) - 4.f * plane_sum(1, 2);
           float dA = rh ? second : first, dB = rh ? first : second;
           if (mat.zeros) {
-            dA += zcA * __shfl_sync(0xffffffffu, sx_m[m], 0);
-            dB += zcB * __shfl_sync(0xffffffffu, sx_m[m], 16);
+            dA += (4.f - (float)zA) * __shfl_sync(0xffffffffu, sx_m[m], 0);
+            dB += (4.f - (float)zB) * __shfl_sync(0xffffffffu, sx_m[m], 16);
           }
           float vA = dA * sA, vB = dB * sB;
           if (CORRECT) {
@@ -598,7 +567,7 @@ struct Plan {
 
 size_t lut_bytes(int m) { return (size_t)32768 << (m == 1 ? 0 : (m == 2 ? 1 : 2)); }
 
-// Two CTAs per SM: with M = 1 a CTA needs 32 KB of tables + 72 KB of staged waves, so a CTA
+// Two CTAs per SM: with M = 1 a CTA needs 32 KB of tables + 72 KB of staged units, so a CTA
 // of the next kernel in the stream can be resident (and prefetching) beside one of this kernel.
 Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   Plan plan;
@@ -611,7 +580,7 @@ Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   if (c > nRU) c = nRU;
   plan.ctas_per_kb = c;
   plan.grid = plan.nSB * c;
-  plan.smem = lut_bytes(m) + (size_t)kRing * kWaveBytes + 2 * kRing * sizeof(uint64_t);
+  plan.smem = lut_bytes(m) + (size_t)kWarps * kStages * kUnitBytes + (size_t)kWarps * kStages * sizeof(uint64_t);
   return plan;
 }
 
@@ -666,6 +635,55 @@ extern "C" size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_featu
 }
 
 namespace {
+// Descriptor of one planes tensor for the tiled copies, cached per (address, O, G): encoding is
+// pure host work, but it would otherwise be repeated on every call.
+bool plane_map(const uint8_t* planes, int O, int G, CUtensorMap* out) {
+  static std::mutex lock;
+  static PFN_cuTensorMapEncodeTiled encode = nullptr;
+  struct Key {
+    const void* ptr;
+    int O, G;
+    bool operator==(const Key& other) const { return ptr == other.ptr && O == other.O && G == other.G; }
+  };
+  struct Hash {
+    size_t operator()(const Key& key) const { return std::hash<const void*>()(key.ptr) ^ ((size_t)key.O * 1315423911u) ^ ((size_t)key.G << 40); }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  std::lock_guard<std::mutex> guard(lock);
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+    if (err != cudaSuccess || status != cudaDriverEntryPointSuccess || !fn) {
+      cuda_fail(err, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+      return false;
+    }
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+  }
+  const Key key{planes, O, G};
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return true;
+  }
+  const cuuint64_t dims[3] = {128, (cuuint64_t)(O / kUnitRows), (cuuint64_t)G * 3};
+  const cuuint64_t strides[2] = {(cuuint64_t)kPlaneTile, (cuuint64_t)O * 16};  // bytes, dims 1 and 2
+  const cuuint32_t box[3] = {128, 1, 6};
+  const cuuint32_t step[3] = {1, 1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(planes), dims, strides, box, step,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    fail(FB_ECUDA, "cuTensorMapEncodeTiled failed with code %d for planes [%d,3,%d,16]", (int)rc, G, O);
+    return false;
+  }
+  if (cache.size() >= 8192) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return true;
+}
+
 int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices, int scale_dtype,
               const int16_t* perm, int in_features, void* scratch, size_t scratch_bytes, unsigned flags,
               fb_stream_t stream, int prologue, const void* prologue_arg, float eps) {
@@ -699,6 +717,7 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
     W3Matrix& mat = p.mats[j];
     if (j >= n_matrices) {
       mat = W3Matrix{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
+      p.plane_maps[j] = p.plane_maps[0];
       continue;
     }
     const fb_w3_matrix_t& in = matrices[j];
@@ -716,6 +735,7 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
         overlaps(in.out, out_bytes, in.scales, (size_t)G * O * 2))
       return fail(FB_EALIAS, "fb_w3_gemv: out overlaps an input");
     if (scratch && overlaps(scratch, scratch_bytes, in.out, out_bytes)) return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps out");
+    if (!plane_map(in.planes, O, G, &p.plane_maps[j])) return FB_ECUDA;
     mat.planes = in.planes;
     mat.scales = static_cast<const unsigned short*>(in.scales);
     mat.zeros = in.zeros;
