@@ -44,18 +44,19 @@
 #define FB_W3_TRACE 0
 #endif
 #if FB_W3_TRACE
+#define FB_CTA (blockIdx.y * gridDim.x + blockIdx.x)
 #define FB_MARK(i)                                                                                   \
   do {                                                                                               \
-    if (threadIdx.x == 0 && blockIdx.x == 0) reinterpret_cast<long long*>(p.status)[8 + (i)] = clock64(); \
+    if (threadIdx.x == 0 && FB_CTA == 0) reinterpret_cast<long long*>(p.status)[8 + (i)] = clock64(); \
     if (threadIdx.x == 0 && ((i) == 0 || (i) == 8))                                                  \
-      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.status) + (3 << 20))[blockIdx.x * 2 + ((i) == 8)] = fb::global_timer_ns(); \
+      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.status) + (3 << 20))[FB_CTA * 2 + ((i) == 8)] = fb::global_timer_ns(); \
     if (threadIdx.x == 0 && (i) == 0) { unsigned smid_; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));  \
-      reinterpret_cast<unsigned*>(reinterpret_cast<char*>(p.status) + (3 << 20) + 65536)[blockIdx.x] = smid_; } \
+      reinterpret_cast<unsigned*>(reinterpret_cast<char*>(p.status) + (3 << 20) + 65536)[FB_CTA] = smid_; } \
   } while (0)
 #define FB_WAVE_MARK(w, which)                                                                         \
   do {                                                                                               \
     if (lane == 0 && (warp == 0 || warp == 7) && (w) < 8)                                            \
-      reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((blockIdx.x * 2 + (warp == 7)) * 8 + (w)) * 8 + (which)] = clock64(); \
+      reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((FB_CTA * 2 + (warp == 7)) * 8 + (w)) * 8 + (which)] = clock64(); \
   } while (0)
 #else
 #define FB_MARK(i) \
@@ -113,6 +114,7 @@ struct W3Params {
   int act_dtype, scale_dtype;
   int S, nSB;          // K blocks per super-block (one CTA walks them in turn), super-blocks
   int ctas_per_kb;     // row slices per super-block
+  int units_per_slice, units_extra;  // nRU / slices and nRU % slices
   int group_partials;  // write scale-multiplied per-group sums instead of reducing
 };
 
@@ -148,23 +150,22 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   pdl_launch_dependents();
   FB_MARK(10);
 
-  const int nV = p.nSB * p.ctas_per_kb;
-  if ((int)blockIdx.x >= nV) return;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kWarps * kStages; ++s) mbar_init(smem_u32(&full_bars[s]), 1);  // the issuing lane's expect_tx
+  if (threadIdx.x < kWarps * kStages) {
+    mbar_init(smem_u32(&full_bars[threadIdx.x]), 1);  // the issuing lane's expect_tx
     mbar_init_fence();
   }
   __syncthreads();
   FB_MARK(11);
 
   // Work of CTA v: super-block v / c (K blocks sb*S ..), the row units [first, first + count) of slice v % c.
-  auto share = [&](int v, int& sb, int& first, int& count) {
-    sb = (int)((unsigned)v / (unsigned)p.ctas_per_kb);
-    const int slice = v - sb * p.ctas_per_kb;
-    // 32-bit arithmetic on purpose (slice * nRU < 2^21): 64-bit division is slow on the GPU
-    first = (int)((unsigned)(slice * p.nRU) / (unsigned)p.ctas_per_kb);
-    count = (int)((unsigned)((slice + 1) * p.nRU) / (unsigned)p.ctas_per_kb) - first;
+  // The grid is (row slices, super-blocks); the first nRU % c slices take one unit more.  No
+  // division on the device: the quotient and remainder come with the parameters.
+  auto share = [&](int& sb, int& first, int& count) {
+    sb = (int)blockIdx.y;
+    const int slice = (int)blockIdx.x;
+    first = slice * p.units_per_slice + min(slice, p.units_extra);
+    count = p.units_per_slice + (slice < p.units_extra ? 1 : 0);
   };
   // Matrix that owns 32-row unit `ru` of the concatenated row space.
   auto locate = [&](int ru) {
@@ -220,20 +221,35 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   // pipe, which keeps the half-rate integer ALU pipe nearly idle), the shared-memory load, one add.
   const uint32_t lut_u32 = smem_u32(lut), ring_u32 = smem_u32(ring);
   uint32_t sel[4], xl[2][4][4], woff[2][4];
+  uint32_t xa[2], xb[4], xc[4];
+  xa[0] = lut_u32 + 64u * rh;
+  xa[1] = lut_u32 + 64u * (rh ^ 1);
 #pragma unroll
-  for (int b = 0; b < 4; ++b) sel[b] = 0x4440u | (uint32_t)((b + rb) & 3);  // byte (b+rb)%4 of a, zeros above
+  for (int j = 0; j < 4; ++j) {
+    xb[j] = 16u * ((j + rw) & 3);
+    xc[j] = 4u * ((j + rb) & 3);
+  }
+#pragma unroll
+  for (int b = 0; b < 4; ++b) sel[b] = 128u << (8 * ((b + rb) & 3));  // weight 128 at byte (b+rb)%4
 #pragma unroll
   for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
     for (int jw = 0; jw < 4; ++jw) {
       woff[jh][jw] = (uint32_t)(((jh ^ rh) * 3) * kPlaneTile + ((jw + rw) & 3) * 4);
 #pragma unroll
-      for (int b = 0; b < 4; ++b)
-        xl[jh][jw][b] = lut_u32 + (uint32_t)(64 * (jh ^ rh) + 16 * ((jw + rw) & 3) + 4 * ((b + rb) & 3));
+      for (int b = 0; b < 4; ++b) xl[jh][jw][b] = xa[jh] + xb[jw] + xc[b];  // one three-input add each
     }
+  // entry * stride + table address in ONE instruction: a 4-way byte dot product whose only
+  // non-zero weight (the stride, 128 for M = 1) sits at the wanted byte of the staged word
   auto lookup_address = [&](uint32_t word, int b, uint32_t table) {
-    uint32_t entry = __byte_perm(word, 0u, sel[b]), address;
-    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(address) : "r"(entry), "n"(Geom::kStride), "r"(table));
+    uint32_t address;
+    if (Geom::kStride <= 128) {
+      asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(address) : "r"(word), "r"(sel[b]), "r"(table));
+    } else {  // the stride does not fit a byte weight: dot product with weight 128, then scale
+      uint32_t entry128;
+      asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(entry128) : "r"(word), "r"(sel[b]), "r"(0u));
+      address = entry128 * (Geom::kStride / 128) + table;
+    }
     return address;
   };
   auto lds_f32 = [](uint32_t address) {
@@ -246,16 +262,22 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   // This CTA walks the K blocks kb_begin .. kb_begin + nS - 1 over the same rows.  Warp w takes
   // the units cta_first + w, + kWarps, ...; its tasks are numbered t = K block * my_count + unit.
   int sb, cta_first, cta_count;
-  share((int)blockIdx.x, sb, cta_first, cta_count);
+  share(sb, cta_first, cta_count);
   const int kb_begin = sb * p.S, nS = min(p.S, p.nKB - kb_begin);
   const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
   const int my_tasks = nS * my_count;
-  auto issue_task = [&](int t) {
-    const int s = (int)((unsigned)t / (unsigned)my_count), i = t - s * my_count;
-    issue_unit(t, kb_begin + s, cta_first + i * kWarps + warp);
+  int pf_task = 0, pf_kb = kb_begin, pf_ru = cta_first + warp;  // the next task to stage
+  auto issue_next = [&]() {
+    issue_unit(pf_task, pf_kb, pf_ru);
+    ++pf_task;
+    pf_ru += kWarps;
+    if (pf_ru >= cta_first + cta_count) {
+      pf_ru = cta_first + warp;
+      ++pf_kb;
+    }
   };
   FB_MARK(12);
-  for (int t = 0; t < kStages && t < my_tasks; ++t) issue_task(t);  // weights never change: no need to wait
+  for (int t = 0; t < kStages && t < my_tasks; ++t) issue_next();  // weights never change: no need to wait
   FB_MARK(1);
 
   // Everything below reads activations and writes scratch / outputs of this stream.
@@ -312,11 +334,11 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   int pend_ru = -1;
   auto settle = [&]() {
     if (pend_ru < 0) return;
-    const W3Matrix& owner = p.mats[locate(pend_ru)];
-    const int lrow = (pend_ru - owner.ru_begin) * kUnitRows + lane;
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-      if ((int)(pend_old[m] & 63ull) == p.nSB - 1) {
+      if (((unsigned)pend_old[m] & 63u) == (unsigned)(p.nSB - 1)) {  // rare: one contribution in nSB
+        const W3Matrix& owner = p.mats[locate(pend_ru)];
+        const int lrow = (pend_ru - owner.ru_begin) * kUnitRows + lane;
         const unsigned long long total = pend_old[m] + pend_add[m];
         float value = __ll2float_rn((long long)total >> 12) * 1.4901161193847656e-08f;  // 2^-26
         if ((total >> 6) & 63ull) value = __int_as_float(0x7fc00000);
@@ -405,6 +427,9 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     FB_MARK(3);
 
     // ---- this warp's units ----
+    int cur_j = 0, cur_begin = 0, cur_end = -1, cur_O = 0;
+    const unsigned short* cur_scales = nullptr;
+    const uint8_t* cur_zeros = nullptr;
     const int gA = 2 * kb, gB = 2 * kb + 1;
     const bool hasB = gB < p.G;
     for (int i = 0; i < my_count; ++i) {
@@ -412,21 +437,36 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       const bool mine = true;
       const int ru = cta_first + i * kWarps + warp;
       const int row = ru * kUnitRows + lane;  // in the concatenated row space
-      const W3Matrix& mat = p.mats[locate(ru)];
-      const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
+      if (ru < cur_begin || ru >= cur_end) {  // entering another matrix of the launch: rare
+        cur_j = locate(ru);
+        cur_begin = p.mats[cur_j].ru_begin;
+        cur_end = cur_j + 1 < p.n_mats ? p.mats[cur_j + 1].ru_begin : p.nRU;
+        cur_O = p.mats[cur_j].O;
+        cur_scales = p.mats[cur_j].scales;
+        cur_zeros = p.mats[cur_j].zeros;
+      }
+      const W3Matrix& mat = p.mats[cur_j];
+      const int lrow = (ru - cur_begin) * kUnitRows + lane;
       // scales and zero points straight from global memory (one coalesced 64-byte run per group):
       // requested now, needed only after the lookups
       unsigned short sbitsA = 0, sbitsB = 0;
       unsigned char zA = 4, zB = 4;
       if (!dead) {
-        sbitsA = __ldg(mat.scales + (size_t)gA * mat.O + lrow);
-        if (hasB) sbitsB = __ldg(mat.scales + (size_t)gB * mat.O + lrow);
-        if (mat.zeros) {
-          zA = __ldg(mat.zeros + (size_t)gA * mat.O + lrow);
-          if (hasB) zB = __ldg(mat.zeros + (size_t)gB * mat.O + lrow);
+        const int at = gA * cur_O + lrow;  // G * O < 2^24
+        sbitsA = __ldg(cur_scales + at);
+        if (hasB) sbitsB = __ldg(cur_scales + at + cur_O);
+        if (cur_zeros) {
+          zA = __ldg(cur_zeros + at);
+          if (hasB) zB = __ldg(cur_zeros + at + cur_O);
         }
       }
       FB_WAVE_MARK(seq, 0);
+#if FB_W3_TRACE
+      if (lane == 0 && (warp == 0 || warp == 7) && seq < 8)
+        reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((FB_CTA * 2 + (warp == 7)) * 8 + seq) * 8 + 6] =
+            mbar_try_wait(smem_u32(&full_bars[warp * kStages + slot]), (uint32_t)((seq / kStages) & 1)) ? 1 : 0;
+      FB_WAVE_MARK(seq, 7);
+#endif
       bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[warp * kStages + slot]), (uint32_t)((seq / kStages) & 1));
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && !dead) {
@@ -501,10 +541,10 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       // all lanes are done with the staged bytes: the slot takes this warp's task kStages ahead
       __syncwarp();
       FB_WAVE_MARK(seq, 4);
-      if (!dead && seq + kStages < my_tasks) issue_task(seq + kStages);
+      if (!dead && pf_task < my_tasks && !(FB_W3_ABLATE & 4)) issue_next();
       FB_WAVE_MARK(seq, 5);
 
-      if (!dead && mine) {
+      if (!dead && mine && !(FB_W3_ABLATE & 2)) {
         const float sA = bits_to_float(sbitsA, p.scale_dtype);
         const float sB = bits_to_float(sbitsB, p.scale_dtype);
 #pragma unroll
@@ -513,7 +553,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           const float first = plane_sum(0, 0) + 2.f * plane_sum(0, 1) - 4.f * plane_sum(0, 2);
           const float second = plane_sum(1, 0) + 2.f * plane_sum(1, 1) - 4.f * plane_sum(1, 2);
           float dA = rh ? second : first, dB = rh ? first : second;
-          if (mat.zeros) {
+          if (cur_zeros) {
             dA += (4.f - (float)zA) * __shfl_sync(0xffffffffu, sx_m[m], 0);
             dB += (4.f - (float)zB) * __shfl_sync(0xffffffffu, sx_m[m], 16);
           }
@@ -600,7 +640,7 @@ int launch(const W3Params& p, const Plan& plan, int max_smem, bool pdl, cudaStre
     }
   }
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(plan.grid);
+  config.gridDim = dim3(plan.ctas_per_kb, plan.nSB);
   config.blockDim = dim3(kWarps * 32);
   config.dynamicSmemBytes = plan.smem;
   config.stream = stream;
@@ -767,6 +807,8 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   const Plan plan = make_plan(m, p.nKB, p.nRU, *info);
   p.ctas_per_kb = plan.ctas_per_kb;
   p.S = plan.S;
+  p.units_per_slice = p.nRU / plan.ctas_per_kb;
+  p.units_extra = p.nRU % plan.ctas_per_kb;
   p.nSB = plan.nSB;
   p.group_partials = group_partials ? 1 : 0;
   if (plan.smem > (size_t)info->max_smem_optin) return fail(FB_ELIMIT, "fb_w3_gemv: plan needs %zu bytes of shared memory", plan.smem);
