@@ -121,6 +121,20 @@ int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transform, const vo
                            void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream);
 
 /*
+ * Small-batch form on the tensor cores: y[M,O] = x[M,K] . W^T for M = 1..16, same layout and
+ * dtypes as fb_w3_gemv.  Every weight is dequantised once, T((code - zero) * scale) with T the
+ * activation dtype, into a shared-memory operand tile and applied to all M rows by tcgen05.mma
+ * (fp32 accumulation in tensor memory), so the time does not grow with M.  The K split is
+ * combined as in fb_w3_gemv (repeat-exact).  Own scratch (zero-filled once, 256-byte aligned),
+ * not to be shared with the other kernels.  The reference has no packed path for M > 1
+ * (csrc/w3_lut.cu:195); its dense fallback (w3_lut_deployment.py:343-359) is the oracle.
+ */
+size_t fb_w3_gemm_small_scratch_bytes(int m, int out_features, int in_features);
+int fb_w3_gemm_small(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales, int scale_dtype,
+                     const uint8_t* zeros, const int16_t* perm, void* out, int out_features, int in_features,
+                     void* scratch, size_t scratch_bytes, fb_stream_t stream);
+
+/*
  * out[o] = T( sum_s partials[s, o] ), rows summed in ascending order.
  * partials fp32 [splits, O]; out f16|bf16 [O].
  * Replaces the reference's finish (csrc/w3_lut.cu:275-296, kernel :142-150).

@@ -61,6 +61,12 @@ def library() -> ctypes.CDLL:
         lib.fb_w3_gemv_fused_input.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_float,
                                                ctypes.POINTER(W3Matrix), ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                                ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p]
+        lib.fb_w3_gemm_small_scratch_bytes.restype = ctypes.c_size_t
+        lib.fb_w3_gemm_small_scratch_bytes.argtypes = [ctypes.c_int] * 3
+        lib.fb_w3_gemm_small.restype = ctypes.c_int
+        lib.fb_w3_gemm_small.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                         ctypes.c_size_t, ctypes.c_void_p]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.fb_bb_gemv_scratch_bytes.restype = ctypes.c_size_t
@@ -317,3 +323,16 @@ def w3_gemv_fused_input(x, transform: int, operand, eps: float, matrices, n_matr
         check(library().fb_w3_gemv_fused_input(ptr(x), dtype_tag(x.dtype), transform, ptr(operand), float(eps), matrices, n_matrices,
                                                dtype_tag(scale_dtype), k, ptr(scratch), scratch.numel() * scratch.element_size(),
                                                0 if pdl else FB_W3_NO_PDL, stream_handle(x.device)))
+
+
+def w3_gemm_small(x, planes, scales, zeros, perm, out, *, scratch=None) -> None:
+    """Tensor-core form for ``x`` of 1..16 rows: x [M,K], planes [G,3,O,16], scales [G,O], out [M,O]."""
+    m, k = x.shape
+    o = planes.shape[2]
+    if scratch is None:
+        scratch = scratch_for(x.device, library().fb_w3_gemm_small_scratch_bytes(m, o, k), "w3mma")
+    with torch.cuda.device(x.device):
+        check(library().fb_w3_gemm_small(ptr(x), dtype_tag(x.dtype), m, ptr(planes), ptr(scales), dtype_tag(scales.dtype),
+                                         ptr(zeros) if zeros is not None else None, ptr(perm) if perm is not None else None,
+                                         ptr(out), o, k, ptr(scratch), scratch.numel() * scratch.element_size(),
+                                         stream_handle(x.device)))

@@ -284,6 +284,23 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   pdl_wait_prior_grid();
   FB_MARK(9);
 
+  // Raw 16-bit activations of one lane's table (8 values) and of the fused transform's operand;
+  // the next K block's are fetched while the current one is being computed.
+  const bool fast_x = M == 1 && !p.perm;
+  auto fetch_x = [&](int kb_, uint4& raw, uint4& op) {
+    const int g = 2 * kb_ + (lane >> 4);
+    raw = make_uint4(0u, 0u, 0u, 0u);
+    op = raw;
+    if (g < p.G) {
+      const int kbase = g * 128 + (lane & 15) * 8;
+      raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + kbase);
+      if (p.prologue != 0) op = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.prologue_arg) + kbase);
+    }
+  };
+  // requested before the RMS reduction below, so that the two round trips overlap
+  uint4 raw_next = make_uint4(0u, 0u, 0u, 0u), op_next = raw_next;
+  if (fast_x) fetch_x(kb_begin, raw_next, op_next);
+
   // Optional fused input transform.  For RMSNorm every CTA reduces the whole activation row
   // itself (K 16-bit values: a few KB out of L2), which costs far less than a separate launch.
   float inv_rms = 1.f;
@@ -311,19 +328,6 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   }
   auto round16 = [&](float v) { return p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v)); };
 
-  // Raw 16-bit activations of one lane's table (8 values) and of the fused transform's operand;
-  // the next K block's are fetched while the current one is being computed.
-  const bool fast_x = M == 1 && !p.perm;
-  auto fetch_x = [&](int kb_, uint4& raw, uint4& op) {
-    const int g = 2 * kb_ + (lane >> 4);
-    raw = make_uint4(0u, 0u, 0u, 0u);
-    op = raw;
-    if (g < p.G) {
-      const int kbase = g * 128 + (lane & 15) * 8;
-      raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + kbase);
-      if (p.prologue != 0) op = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.prologue_arg) + kbase);
-    }
-  };
   // Split-K combine.  A contribution is ONE 64-bit atomic add: the partial sum in fixed point
   // (units of 2^-26) in bits 12..63, an arrival count in bits 0..5, a count of non-finite or
   // out-of-range partials in bits 6..11.  Integer addition is associative, so the result does
@@ -348,8 +352,6 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     }
     pend_ru = -1;
   };
-  uint4 raw_next = make_uint4(0u, 0u, 0u, 0u), op_next = raw_next;
-  if (fast_x) fetch_x(kb_begin, raw_next, op_next);
 
   for (int s = 0; s < nS; ++s) {
     const int kb = kb_begin + s;

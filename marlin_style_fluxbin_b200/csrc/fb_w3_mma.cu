@@ -1,0 +1,387 @@
+// W3 (GPTQ 3-bit, group 128, planar layout) small-batch GEMM for B200 (sm_100a):
+//   y[M,O] = x[M,K] . W^T,  M = 1..16, on the fifth-generation tensor cores (tcgen05 + TMEM).
+//
+// Where the M = 1 kernel (fb_w3_gemv.cu) replaces multiplications by table lookups, whose cost
+// grows with every extra activation row, this kernel dequantises each weight ONCE into a
+// shared-memory operand tile and lets one tcgen05.mma apply it to all rows of the batch:
+//   * a CTA owns 128 output rows and a contiguous range of K groups (split-K over CTAs);
+//   * the three bit planes of (group, 128 rows) arrive by one tiled TMA copy (6 KB);
+//   * 256 threads turn them into a 128 x 128 tile of 16-bit weights T((code - zero) * scale),
+//     written straight in the K-major "core matrix" order that the MMA's shared-memory descriptor
+//     walks (8 rows x 16 bytes per core matrix, no swizzle): one 16-byte store per 8 weights;
+//   * the activations of the group (M rows padded to N = 16) are stored the same way;
+//   * one thread issues 8 x tcgen05.mma (128 x 16 x 16 each), accumulating in 16 TMEM columns
+//     over all groups of the CTA; tiles are double-buffered, so the next group is dequantised
+//     while the tensor core works;
+//   * the 128 x 16 fp32 result is read back with tcgen05.ld and either written (one split) or
+//     combined across splits with the 64-bit fixed-point atomic of the M = 1 kernel.
+// Every wait on an mbarrier is bounded; on expiry the CTA records a status, frees its TMEM
+// columns and leaves.
+//
+// The weights still cross HBM exactly once, so the bound is the same as for M = 1; the reference
+// has no packed path for M > 1 at all (csrc/w3_lut.cu:195 rejects it) and falls back to a dense
+// matmul of the restored weight (w3_lut_deployment.py:343-359), which is the oracle here.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "fb_common.cuh"
+
+namespace {
+
+using namespace fb;
+
+constexpr int kTileRows = 128;
+constexpr int kN = 16;            // activation rows presented to the MMA (M padded)
+constexpr int kThreads = 256;
+constexpr int kATile = kTileRows * 128 * 2;  // 32 KB: 128 rows x 128 k, 16-bit
+constexpr int kBTile = kN * 128 * 2;         // 4 KB
+constexpr int kPlaneTile = 3 * kTileRows * 16;  // 6 KB: three planes of 128 rows
+constexpr int kMaxSplits = 16;
+constexpr int kTmemCols = 32;
+constexpr size_t kCombineOffset = 16384;
+
+struct MmaParams {
+  alignas(64) CUtensorMap plane_map;  // planes as uint32 [G*3][O/32][128], box 3 x 4 x 128
+  const void* x;
+  const unsigned short* scales;
+  const uint8_t* zeros;
+  const int16_t* perm;
+  void* out;
+  unsigned long long* combine;
+  unsigned* status;
+  int M, O, K, G;
+  int groups_per_split, splits;
+  int act_dtype, scale_dtype;
+};
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes;
+// `lbo` = byte distance between core matrices adjacent in K, `sbo` = between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((address >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) | ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) |
+         (1ull << 46);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_constant__ MmaParams p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* const a_tiles = smem;                           // 2 x 32 KB
+  unsigned char* const b_tiles = smem + 2 * kATile;              // 2 x 4 KB
+  unsigned char* const planes_s = b_tiles + 2 * kBTile;          // 2 x 6 KB
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(planes_s + 2 * kPlaneTile);  // plane_full[2], mma_done[2], all_done
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int g_begin = split * p.groups_per_split, g_end = min(p.G, g_begin + p.groups_per_split);
+  const int ng = g_end - g_begin;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (tid < 5) {
+    mbar_init(smem_u32(&bars[tid]), 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) {  // TMEM columns for the 128 x 16 fp32 accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto issue_planes = [&](int gi) {  // one elected thread: the three planes of group gi, 128 rows
+    const uint32_t bar = smem_u32(&bars[gi & 1]);
+    mbar_expect_tx(bar, (uint32_t)kPlaneTile);
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            smem_u32(planes_s + (size_t)(gi & 1) * kPlaneTile)),
+        "l"(&p.plane_map), "r"(0), "r"(tile * (kTileRows / 32)), "r"(3 * (g_begin + gi)), "r"(bar)
+        : "memory");
+  };
+  if (tid == 0) {  // weights never change: staged before the wait on the previous kernel
+    if (ng > 0) issue_planes(0);
+    if (ng > 1) issue_planes(1);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // instruction descriptor: D fp32, A and B in the activation dtype, both K-major, N = 16, M = 128
+  const uint32_t format = p.act_dtype == FB_BF16 ? 1u : 0u;
+  const uint32_t idesc = (1u << 4) | (format << 7) | (format << 10) | ((uint32_t)(kN >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
+
+  const int row_in_tile = tid & 127, khalf = tid >> 7;  // dequantisation: one row, 8 of its 16 chunks
+  const int row = tile * kTileRows + row_in_tile;
+  const int xn = tid >> 4, xc = tid & 15;  // activation tile: row of the batch, chunk of 8 inputs
+  bool dead = false;
+
+  for (int gi = 0; gi < ng; ++gi) {
+    const int g = g_begin + gi, buf = gi & 1;
+    // scale and zero point of (group, row); rows past O contribute zero weights
+    float scale = 0.f, zero = 4.f;
+    if (row < p.O) {
+      scale = bits_to_float(__ldg(p.scales + (size_t)g * p.O + row), p.scale_dtype);
+      if (p.zeros) zero = (float)__ldg(p.zeros + (size_t)g * p.O + row);
+    }
+    // this batch row's 8 activations of chunk xc (gathered through perm when given)
+    uint4 xraw = make_uint4(0u, 0u, 0u, 0u);
+    if (xn < p.M) {
+      const int kbase = g * 128 + xc * 8;
+      const unsigned short* xrow = reinterpret_cast<const unsigned short*>(p.x) + (size_t)xn * p.K;
+      if (p.perm) {
+        unsigned short v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = xrow[p.perm[kbase + j]];
+        xraw = make_uint4(v[0] | (uint32_t)v[1] << 16, v[2] | (uint32_t)v[3] << 16, v[4] | (uint32_t)v[5] << 16, v[6] | (uint32_t)v[7] << 16);
+      } else {
+        xraw = *reinterpret_cast<const uint4*>(xrow + kbase);
+      }
+    }
+    // the tiles of this buffer were last read by the MMAs issued two groups ago
+    bool ok = true;
+    if (gi >= 2) ok = mbar_wait_bounded(smem_u32(&bars[2 + buf]), (uint32_t)(((gi >> 1) - 1) & 1));
+    ok = ok && mbar_wait_bounded(smem_u32(&bars[buf]), (uint32_t)((gi >> 1) & 1));
+    if (__syncthreads_or(!ok)) {
+      dead = true;
+      break;
+    }
+    // ---- activation tile: core matrix (chunk, 8 batch rows) at chunk * 256 + (n / 8) * 128 ----
+    *reinterpret_cast<uint4*>(b_tiles + (size_t)buf * kBTile + xc * 256 + (xn >> 3) * 128 + (xn & 7) * 16) = xraw;
+    // ---- weight tile: core matrix (chunk, 8 rows) at chunk * 2048 + (row / 8) * 128 ----
+    {
+      const unsigned char* pl = planes_s + (size_t)buf * kPlaneTile + row_in_tile * 16 + khalf * 8;
+      const uint2 w0 = *reinterpret_cast<const uint2*>(pl), w1 = *reinterpret_cast<const uint2*>(pl + kTileRows * 16),
+                  w2 = *reinterpret_cast<const uint2*>(pl + 2 * kTileRows * 16);
+      const float bias = -(128.f + zero) * scale;  // value = (128 + code) * scale + bias, one fp32 rounding
+      unsigned char* const a_row = a_tiles + (size_t)buf * kATile + (row_in_tile >> 3) * 128 + (row_in_tile & 7) * 16;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t b0 = ((c < 4 ? w0.x : w0.y) >> (8 * (c & 3))) & 0xffu;
+        const uint32_t b1 = ((c < 4 ? w1.x : w1.y) >> (8 * (c & 3))) & 0xffu;
+        const uint32_t b2 = ((c < 4 ? w2.x : w2.y) >> (8 * (c & 3))) & 0xffu;  // stored inverted: code bit 2 = 1 - b2
+        // low half: the byte; high half: the byte shifted right by one; even bit positions only
+        const uint32_t e0 = (b0 * 0x8001u) & 0x00550055u, e1 = (b1 * 0x8001u) & 0x00550055u,
+                       e2 = ((b2 ^ 0xffu) * 0x8001u) & 0x00550055u;
+        const uint32_t low2 = e0 + 2u * e1, high = e2 << 2;
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          // codes of inputs 2i (low half) and 2i+1 (high half) as bf16 128 + code
+          const uint32_t pair = ((((low2 >> (2 * i)) & 0x00030003u) | ((high >> (2 * i)) & 0x00040004u))) | 0x43004300u;
+          const float lo = __uint_as_float(pair << 16), hi = __uint_as_float(pair & 0xffff0000u);
+          const float vlo = lo * scale + bias, vhi = hi * scale + bias;
+          if (p.act_dtype == FB_BF16) {
+            const __nv_bfloat162 both = __floats2bfloat162_rn(vlo, vhi);
+            packed[i] = *reinterpret_cast<const uint32_t*>(&both);
+          } else {
+            const __half2 both = __floats2half2_rn(vlo, vhi);
+            packed[i] = *reinterpret_cast<const uint32_t*>(&both);
+          }
+        }
+        *reinterpret_cast<uint4*>(a_row + (size_t)(khalf * 8 + c) * 2048) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+    }
+    // generic-proxy stores must be visible to the tensor core's (async proxy) reads
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_base = smem_u32(a_tiles + (size_t)buf * kATile), b_base = smem_u32(b_tiles + (size_t)buf * kBTile);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)  // K = 16 per instruction: two chunks
+        mma_f16(tmem_base, smem_desc(a_base + j * 2 * 2048, 2048, 128), smem_desc(b_base + j * 2 * 256, 256, 128), idesc,
+                (gi > 0 || j > 0) ? 1u : 0u);
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[2 + buf])) : "memory");
+      if (gi + 2 < ng) issue_planes(gi + 2);  // every thread has read this buffer's planes
+    }
+  }
+
+  // ---- all MMAs done: read the accumulator back ----
+  if (!dead) {
+    if (tid == 0) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[4])) : "memory");
+    const bool ok = ng == 0 || mbar_wait_bounded(smem_u32(&bars[4]), 0u);
+    if (__syncthreads_or(!ok)) dead = true;
+  }
+  if (dead) {
+    if (tid == 0) atomicExch(p.status, 3u);
+  } else if (warp < 4 && ng > 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t acc[16];
+    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]), "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7]), "=r"(acc[8]),
+          "=r"(acc[9]), "=r"(acc[10]), "=r"(acc[11]), "=r"(acc[12]), "=r"(acc[13]), "=r"(acc[14]), "=r"(acc[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    const int out_row = tile * kTileRows + warp * 32 + lane;  // TMEM lane = row of the tile
+    if (out_row < p.O) {
+#pragma unroll
+      for (int n = 0; n < kN; ++n) {
+        if (n >= p.M) break;
+        const float v = __uint_as_float(acc[n]);
+        if (p.splits == 1) {
+          store_act(p.out, p.act_dtype, n * p.O + out_row, v);
+        } else {
+          // same combine as the M = 1 kernel: fixed point in bits 12..63, arrivals in bits 0..5,
+          // non-finite / out-of-range contributions counted in bits 6..11
+          const bool fits = fabsf(v) < 2097152.f;
+          const unsigned long long add = fits ? ((unsigned long long)__float2ll_rn(v * 67108864.f) << 12) + 1ull : 65ull;
+          unsigned long long* word = p.combine + (size_t)n * p.O + out_row;
+          const unsigned long long old = atomicAdd(word, add);
+          if ((int)(old & 63ull) == p.splits - 1) {
+            const unsigned long long total = old + add;
+            float value = __ll2float_rn((long long)total >> 12) * 1.4901161193847656e-08f;
+            if ((total >> 6) & 63ull) value = __int_as_float(0x7fc00000);
+            store_act(p.out, p.act_dtype, n * p.O + out_row, value);
+            *word = 0ull;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+// Descriptor of the planes for the 128-row tiled copy, cached per (address, O, G).
+bool plane_map_128(const uint8_t* planes, int O, int G, CUtensorMap* out) {
+  static std::mutex lock;
+  static PFN_cuTensorMapEncodeTiled encode = nullptr;
+  struct Key {
+    const void* ptr;
+    int O, G;
+    bool operator==(const Key& other) const { return ptr == other.ptr && O == other.O && G == other.G; }
+  };
+  struct Hash {
+    size_t operator()(const Key& key) const { return std::hash<const void*>()(key.ptr) ^ ((size_t)key.O * 1315423911u) ^ ((size_t)key.G << 40); }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  std::lock_guard<std::mutex> guard(lock);
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+    if (err != cudaSuccess || status != cudaDriverEntryPointSuccess || !fn) {
+      cuda_fail(err, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+      return false;
+    }
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+  }
+  const Key key{planes, O, G};
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return true;
+  }
+  const cuuint64_t dims[3] = {128, (cuuint64_t)(O / 32), (cuuint64_t)G * 3};
+  const cuuint64_t strides[2] = {512, (cuuint64_t)O * 16};
+  const cuuint32_t box[3] = {128, kTileRows / 32, 3};
+  const cuuint32_t step[3] = {1, 1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(planes), dims, strides, box, step,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    fail(FB_ECUDA, "cuTensorMapEncodeTiled failed with code %d for planes [%d,3,%d,16]", (int)rc, G, O);
+    return false;
+  }
+  if (cache.size() >= 8192) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return true;
+}
+
+}  // namespace
+
+extern "C" size_t fb_w3_gemm_small_scratch_bytes(int m, int out_features, int in_features) {
+  if (m < 1 || m > kN || out_features < 32 || in_features < 128) return 0;
+  return kCombineOffset + (size_t)m * out_features * sizeof(unsigned long long);
+}
+
+extern "C" int fb_w3_gemm_small(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales, int scale_dtype,
+                                const uint8_t* zeros, const int16_t* perm, void* out, int out_features, int in_features,
+                                void* scratch, size_t scratch_bytes, fb_stream_t stream) {
+  const int O = out_features, K = in_features;
+  if (!x || !planes || !scales || !out) return fail(FB_EINVAL, "fb_w3_gemm_small: x, planes, scales and out must be non-null");
+  if ((act_dtype != FB_F16 && act_dtype != FB_BF16) || (scale_dtype != FB_F16 && scale_dtype != FB_BF16))
+    return fail(FB_EINVAL, "fb_w3_gemm_small: dtype tags must be FB_F16 or FB_BF16");
+  if (m < 1 || m > kN) return fail(FB_ELIMIT, "fb_w3_gemm_small: M=%d outside 1..%d", m, kN);
+  if (K < 128 || K % 128 || K / 128 > 255) return fail(FB_ELIMIT, "fb_w3_gemm_small: K=%d must be a multiple of 128 with at most 255 groups", K);
+  if (O < 32 || O > 65536 || O % 32) return fail(FB_ELIMIT, "fb_w3_gemm_small: O=%d must be a multiple of 32 in 32..65536", O);
+  if (!aligned(planes, 16) || !aligned(scales, 2) || !aligned(out, 2) || !aligned(perm, 2))
+    return fail(FB_EINVAL, "fb_w3_gemm_small: planes must be 16-byte aligned, 16-bit tensors 2-byte aligned");
+  if (!perm && !aligned(x, 16)) return fail(FB_EINVAL, "fb_w3_gemm_small: x must be 16-byte aligned");
+  const int G = K / 128;
+  const size_t x_bytes = (size_t)m * K * 2, out_bytes = (size_t)m * O * 2;
+  if (overlaps(out, out_bytes, x, x_bytes) || overlaps(out, out_bytes, planes, (size_t)G * 3 * O * 16) ||
+      overlaps(out, out_bytes, scales, (size_t)G * O * 2))
+    return fail(FB_EALIAS, "fb_w3_gemm_small: out overlaps an input");
+  const size_t need = fb_w3_gemm_small_scratch_bytes(m, O, K);
+  if (!scratch || scratch_bytes < need) return fail(FB_ESCRATCH, "fb_w3_gemm_small: scratch of %zu bytes needed, %zu given", need, scratch_bytes);
+  if (!aligned(scratch, 256)) return fail(FB_EINVAL, "fb_w3_gemm_small: scratch must be 256-byte aligned");
+  if (overlaps(scratch, need, out, out_bytes) || overlaps(scratch, need, x, x_bytes)) return fail(FB_EALIAS, "fb_w3_gemm_small: scratch overlaps x or out");
+
+  const DeviceInfo* info = device_info();
+  if (!info) return FB_ECUDA;
+  MmaParams p;
+  if (!plane_map_128(planes, O, G, &p.plane_map)) return FB_ECUDA;
+  p.x = x;
+  p.scales = static_cast<const unsigned short*>(scales);
+  p.zeros = zeros;
+  p.perm = perm;
+  p.out = out;
+  p.status = reinterpret_cast<unsigned*>(scratch);
+  p.combine = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(scratch) + kCombineOffset);
+  p.M = m;
+  p.O = O;
+  p.K = K;
+  p.G = G;
+  p.act_dtype = act_dtype;
+  p.scale_dtype = scale_dtype;
+  const int tiles = (O + kTileRows - 1) / kTileRows;
+  int splits = 2 * info->sm_count / tiles;
+  if (splits < 1) splits = 1;
+  if (splits > kMaxSplits) splits = kMaxSplits;
+  if (splits > G) splits = G;
+  p.groups_per_split = (G + splits - 1) / splits;
+  p.splits = (G + p.groups_per_split - 1) / p.groups_per_split;
+
+  const size_t smem = 2 * (size_t)kATile + 2 * kBTile + 2 * kPlaneTile + 64;
+  static std::mutex lock;
+  static bool ready[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    if (device >= 0 && device < 64 && !ready[device]) {
+      cudaError_t err = cudaFuncSetAttribute(w3_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(w3_mma_kernel)");
+      ready[device] = true;
+    }
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(tiles, p.splits);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl_allowed() ? 1 : 0;
+  cudaError_t err = cudaLaunchKernelEx(&config, w3_mma_kernel, p);
+  if (err != cudaSuccess) return cuda_fail(err, "w3_mma_kernel launch");
+  return FB_OK;
+}

@@ -223,15 +223,32 @@ def w3_lut_m1_out(x, layout, out, workspace, *, row_tile: int, groups_per_split:
     return out
 
 
-def w3_lut_gemv_out(x, layout, out, *, arithmetic: str = "structural"):
-    """Small-batch form (``x`` is ``[M,K]``, M = 1..4) of ``w3_lut_m1_out``; no reference counterpart."""
+def w3_lut_gemv_out(x, layout, out, *, arithmetic: str = "structural", kernel: str = "auto"):
+    """Small-batch form (``x`` is ``[M,K]``, M = 1..16) of ``w3_lut_m1_out``; no reference counterpart.
+
+    ``kernel``: ``"lut"`` is the table-lookup kernel (M <= 4, cost grows with M), ``"mma"`` the
+    tensor-core kernel (M <= 16, cost independent of M; weights are rounded to the activation
+    dtype, as the reference's dense fallback rounds them), ``"auto"`` picks ``"lut"`` up to M = 2.
+    """
     out_features, in_features = validate_planar_w3(layout, check_values=False)
     if x.ndim != 2 or x.shape[1] != in_features or tuple(out.shape) != (x.shape[0], out_features):
         raise ValueError("x/out shape mismatch")
     if out.dtype != x.dtype or out.device != x.device:
         raise ValueError("out must match x in dtype and device")
+    if kernel not in ("auto", "lut", "mma"):
+        raise ValueError("kernel must be auto, lut or mma")
+    rows = x.shape[0]
+    if kernel == "auto":
+        kernel = "lut" if rows <= 2 or arithmetic == "decoded_bf16" else "mma"
+    if rows < 1 or rows > (4 if kernel == "lut" else 16):
+        raise ValueError(f"the {kernel} kernel takes 1..{4 if kernel == 'lut' else 16} rows")
     planes, scales, zeros, perm = _layout_args(layout)
-    _native.w3_gemv(x, planes, scales, zeros, perm, out, decoded_bf16=arithmetic == "decoded_bf16")
+    if kernel == "mma":
+        if arithmetic != "structural":
+            raise ValueError("the tensor-core kernel has one arithmetic: weights rounded to the activation dtype")
+        _native.w3_gemm_small(x, planes, scales, zeros, perm, out)
+    else:
+        _native.w3_gemv(x, planes, scales, zeros, perm, out, decoded_bf16=arithmetic == "decoded_bf16")
     return out
 
 

@@ -165,12 +165,47 @@ def test_small_batch_rows(m):
     layout, x = make_case(2048, 1024, seed=11 + m, zeros=(m % 2 == 0), m=m)
     reference, _ = oracle_outputs(layout, x)
     out = torch.empty(m, 2048, device="cuda", dtype=torch.bfloat16)
-    w3_lut_gemv_out(x.cuda(), to_cuda(layout), out)
+    w3_lut_gemv_out(x.cuda(), to_cuda(layout), out, kernel="lut")
     for row in range(m):
         assert_parity(out[row:row + 1], reference[row:row + 1])
     single = torch.empty(1, 2048, device="cuda", dtype=torch.bfloat16)
-    w3_lut_gemv_out(x[:1].cuda(), to_cuda(layout), single)
+    w3_lut_gemv_out(x[:1].cuda(), to_cuda(layout), single, kernel="lut")
     assert torch.equal(single[0], out[0])  # a row's result does not depend on its neighbours
+
+
+@pytest.mark.parametrize("o,k,m,dtype,scale_dtype,zeros,perm", (
+    (2048, 1024, 16, torch.bfloat16, torch.float16, True, False),
+    (2048, 1024, 5, torch.float16, torch.float16, False, False),
+    (96, 384, 8, torch.bfloat16, torch.bfloat16, True, False),     # a partial 128-row tile, an odd group count
+    (160, 128, 3, torch.bfloat16, torch.float16, False, False),    # one group: no K split
+    (1024, 1024, 16, torch.float16, torch.bfloat16, True, True),   # desc_act gather
+    (4096, 4096, 16, torch.bfloat16, torch.float16, True, False),  # q_proj
+    (4096, 12288, 8, torch.bfloat16, torch.float16, True, False),  # down_proj
+))
+def test_tensor_core_small_batch(o, k, m, dtype, scale_dtype, zeros, perm):
+    """The tcgen05 form (M = 1..16) against dequantise-then-matmul, its oracle: the reference has no
+    packed path for M > 1.  Weights are rounded to the activation dtype before the product, as in
+    the reference's dense fallback, so the distance to the fp32 oracle is that of a 16-bit Linear."""
+    from marlin_style_fluxbin_b200.w3_lut_deployment import w3_lut_gemv_out
+
+    layout, x = make_case(o, k, seed=3 * m + o % 7, zeros=zeros, perm=perm, scale_dtype=scale_dtype, act_dtype=dtype, m=m)
+    reference, _ = oracle_outputs(layout, x)
+    lg, xg = to_cuda(layout), x.cuda()
+    out = torch.full((m, o), float("nan"), device="cuda", dtype=dtype)
+    w3_lut_gemv_out(xg, lg, out, kernel="mma")
+    torch.cuda.synchronize()
+    for row in range(m):
+        assert_parity(out[row:row + 1], reference[row:row + 1])
+    again = torch.full_like(out, float("nan"))
+    w3_lut_gemv_out(xg, lg, again, kernel="mma")
+    assert torch.equal(again, out)  # repeat-exact
+    single = torch.empty(1, o, device="cuda", dtype=dtype)
+    w3_lut_gemv_out(xg[:1].contiguous(), lg, single, kernel="mma")
+    assert torch.equal(single[0], out[0])  # a row's result does not depend on its neighbours
+    # close to the table-lookup kernel's answer for the same row (different roundings of the weights)
+    lut = torch.empty(1, o, device="cuda", dtype=dtype)
+    w3_lut_gemv_out(xg[:1].contiguous(), lg, lut, kernel="lut")
+    assert float((lut.float() - single.float()).abs().max()) <= 2e-2 * float(lut.float().abs().max())
 
 
 def test_two_call_form_and_native_argument_contract():
