@@ -125,28 +125,38 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
   const int xn = tid >> 4, xc = tid & 15;  // activation tile: row of the batch, chunk of 8 inputs
   bool dead = false;
 
-  for (int gi = 0; gi < ng; ++gi) {
-    const int g = g_begin + gi, buf = gi & 1;
-    // scale and zero point of (group, row); rows past O contribute zero weights
-    float scale = 0.f, zero = 4.f;
-    if (row < p.O) {
-      scale = bits_to_float(__ldg(p.scales + (size_t)g * p.O + row), p.scale_dtype);
-      if (p.zeros) zero = (float)__ldg(p.zeros + (size_t)g * p.O + row);
+  // Per-group operands that come straight from global memory (scale and zero point of this
+  // thread's row, eight activations of this thread's batch row) are requested one group ahead.
+  float scale_next = 0.f, zero_next = 4.f;
+  uint4 x_next = make_uint4(0u, 0u, 0u, 0u);
+  auto fetch_group = [&](int g) {
+    scale_next = 0.f;
+    zero_next = 4.f;
+    x_next = make_uint4(0u, 0u, 0u, 0u);
+    if (row < p.O) {  // rows past O contribute zero weights
+      scale_next = bits_to_float(__ldg(p.scales + (size_t)g * p.O + row), p.scale_dtype);
+      if (p.zeros) zero_next = (float)__ldg(p.zeros + (size_t)g * p.O + row);
     }
-    // this batch row's 8 activations of chunk xc (gathered through perm when given)
-    uint4 xraw = make_uint4(0u, 0u, 0u, 0u);
     if (xn < p.M) {
       const int kbase = g * 128 + xc * 8;
       const unsigned short* xrow = reinterpret_cast<const unsigned short*>(p.x) + (size_t)xn * p.K;
-      if (p.perm) {
+      if (p.perm) {  // gathered through the column order
         unsigned short v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = xrow[p.perm[kbase + j]];
-        xraw = make_uint4(v[0] | (uint32_t)v[1] << 16, v[2] | (uint32_t)v[3] << 16, v[4] | (uint32_t)v[5] << 16, v[6] | (uint32_t)v[7] << 16);
+        x_next = make_uint4(v[0] | (uint32_t)v[1] << 16, v[2] | (uint32_t)v[3] << 16, v[4] | (uint32_t)v[5] << 16, v[6] | (uint32_t)v[7] << 16);
       } else {
-        xraw = *reinterpret_cast<const uint4*>(xrow + kbase);
+        x_next = *reinterpret_cast<const uint4*>(xrow + kbase);
       }
     }
+  };
+  if (ng > 0) fetch_group(g_begin);
+
+  for (int gi = 0; gi < ng; ++gi) {
+    const int buf = gi & 1;
+    const float scale = scale_next, zero = zero_next;
+    const uint4 xraw = x_next;
+    if (gi + 1 < ng) fetch_group(g_begin + gi + 1);
     // the tiles of this buffer were last read by the MMAs issued two groups ago
     bool ok = true;
     if (gi >= 2) ok = mbar_wait_bounded(smem_u32(&bars[2 + buf]), (uint32_t)(((gi >> 1) - 1) & 1));
