@@ -158,7 +158,7 @@ def run_ours(args, rank, world, local_rank):
             # per-shape: the same protocol on 36 distinct weights of one shape
             per_shape = {}
             for name, o, k in SHAPES:
-                if name in ("v_proj", "up_proj", "o_proj"):
+                if args.headline_only or name in ("v_proj", "up_proj", "o_proj"):
                     continue
                 mods = [m for n, m in modules if n == name]
                 shape_graph = torch.cuda.CUDAGraph()
@@ -180,8 +180,9 @@ def run_ours(args, rank, world, local_rank):
 
             # the same seven Linears as the decode engine launches them: q/k/v and gate/up share a
             # launch, so a layer is four launches; and the M sweep of configs[1] on two shapes
-            fused = fused_layer_pass(torch, modules, x_dev, stream, begin, end) if world == 1 else None
-            sweep = m_sweep(torch, modules, device, stream, begin, end) if world == 1 else None
+            extras = world == 1 and not args.headline_only
+            fused = fused_layer_pass(torch, modules, x_dev, stream, begin, end) if extras else None
+            sweep = m_sweep(torch, modules, device, stream, begin, end) if extras else None
 
             for _ in range(3):
                 e2e_step()
@@ -270,6 +271,55 @@ def m_sweep(torch, modules, device, stream, begin, end):
             out[f"{o}x{k} M={rows}"] = entry
         del dense
     return out
+
+
+def bb_bytes(o: int, k: int, n_salient: int = 32) -> int:
+    """Algorithmic bytes of one two-base GEMV with matrix-wide scales (BASELINE.json configs[2])."""
+    return 2 * o * k // 8 + 4 * o + 4 * k + 2 * n_salient * o + 4 * n_salient + 2 * k + 2 * o
+
+
+def run_binary_basis(torch, device):
+    """configs[2]: the two-base binary-basis GEMV (1 bit per weight and base, fp16 row / column scales,
+    32 dense bf16 salient columns) on the seven shapes, 12 distinct weight sets per shape."""
+    from marlin_style_fluxbin_b200 import _native
+    from marlin_style_fluxbin_b200.binary_global import global_two_base_m1_out
+
+    gen = torch.Generator(device=device).manual_seed(20260917)
+    stream = torch.cuda.Stream(device)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    table, total_us, total_bytes = {}, 0.0, 0
+    with torch.inference_mode(), torch.cuda.stream(stream):
+        for name, o, k in SHAPES:
+            key = f"{o}x{k}"
+            if key in table:
+                total_us += table[key]["us"]
+                total_bytes += table[key]["bytes"]
+                continue
+            layouts = []
+            for _ in range(12):
+                layouts.append({
+                    "codes": torch.randint(0, 256, (k // 128, o, 2, 16), device=device, generator=gen, dtype=torch.uint8),
+                    "row_scales": (torch.randn(2, o, device=device, generator=gen) * 0.02).abs().half(),
+                    "column_scales": (torch.randn(2, k, device=device, generator=gen) * 0.02).abs().half(),
+                    "salient_indices": torch.randperm(k, device=device, generator=gen)[:32].sort().values.int(),
+                    "salient_values": (torch.randn(o, 32, device=device, generator=gen) * 0.05).bfloat16(),
+                })
+            x = torch.randn(1, k, device=device, generator=gen).bfloat16()
+            y = torch.empty(1, o, device=device, dtype=torch.bfloat16)
+            scratch = torch.zeros(_native.bb_scratch_bytes(o, k, True), dtype=torch.uint8, device=device)
+
+            def run():
+                for layout in layouts:
+                    _native.bb_global_gemv(x, layout["codes"], layout["row_scales"], layout["column_scales"],
+                                           layout["salient_indices"], layout["salient_values"], y, scratch=scratch)
+
+            global_two_base_m1_out(x, layouts[0], y)  # the public call, once, validates the layout
+            us = _graph_time(torch, run, stream, begin, end, len(layouts))
+            table[key] = {"us": round(us, 3), "bytes": bb_bytes(o, k), "gbs": round(bb_bytes(o, k) / us / 1e3, 1)}
+            total_us += us
+            total_bytes += bb_bytes(o, k)
+            del layouts
+    return table, total_us, total_bytes
 
 
 def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=("bf16", "w3"), repeats=5):
@@ -395,11 +445,13 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    parser.add_argument("--workload", default="gemv", choices=("gemv", "decode-8b", "tp-decode-32b"),
+    parser.add_argument("--workload", default="gemv", choices=("gemv", "decode-8b", "tp-decode-32b", "binary-basis"),
                         help="gemv (default): the seven Linear shapes plus the 8B decode; tp-decode-32b: tensor-parallel decode over --gpus ranks")
     parser.add_argument("--case", default=None, metavar="OxK",
                         help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
     parser.add_argument("--copies", type=int, default=8)
+    parser.add_argument("--headline-only", action="store_true",
+                        help="time only the headline step (no per-shape table, sweeps, decode or CPU leg): for profiler launch lists")
     args = parser.parse_args()
     if args.case:
         return small_case(args)
@@ -444,9 +496,20 @@ def main():
             torch.distributed.barrier()
             torch.distributed.destroy_process_group()
         return
+    if args.workload == "binary-basis":
+        torch.cuda.set_device(local_rank)
+        table, total_us, total_bytes = run_binary_basis(torch, torch.device("cuda", local_rank))
+        peak, peak_kind = measured_peak()
+        if rank == 0:
+            print(json.dumps({"metric": "two-base binary-basis GEMV HBM GB/s per Qwen3-8B shape (configs[2])", "unit": "GB/s",
+                              "value": round(total_bytes / total_us / 1e3, 1), "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
+                              "dtype": "f32", "us_per_layer": round(total_us, 2), "per_shape": table,
+                              "roofline": {"bound": "hbm", "achieved": round(total_bytes / total_us / 1e3, 1), "peak": peak, "unit": "GB/s",
+                                           "frac": round(total_bytes / total_us / 1e3 / peak, 4), "peak_kind": peak_kind, "traffic": None}}))
+        return
     result = run_ours(args, rank, world, local_rank)
     decode = None
-    if world == 1:
+    if world == 1 and not args.headline_only:
         torch.cuda.empty_cache()
         decode = run_decode(torch, "qwen3-8b", 512, 32, 0, 1, local_rank)
     if rank == 0:
@@ -460,7 +523,7 @@ def main():
             entry["pct_of_measured"] = round(100 * entry["gbs"] / peak, 1)
             # the same time against the byte count with zero points held as fp16, as the config words them
             entry["gbs_zeros_as_fp16"] = round(entry["gbs"] * (1 + (entry["bytes_zeros_as_fp16"] - entry["bytes"]) / entry["bytes"]), 1)
-        cpu = cpu_reference(3, 1) if world == 1 else None
+        cpu = cpu_reference(3, 1) if world == 1 and not args.headline_only else None
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(result["step_ms"], 4), "higher_is_better": True,

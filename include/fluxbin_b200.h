@@ -149,8 +149,11 @@ int fb_w3_finish(const float* partials, int splits, int out_features, void* out,
  *   sparse_codes uint8 [G,O,2,1] (planar) or [G,O,2] (interleaved)
  *   sparse_rows  f32 [G,O,2]      sparse_cols  f32 [G,8,2]      indices int16 [G,8]
  * y[o] = sum_g ( r0*d0 + r1*d1 + sr0*s0 + sr1*s1 ), d_b = sum_k sign_b*col_b*x over the group,
- * s_b the same over the group's 8 refined columns; fp32, groups summed in ascending order.
- * Any O in 1..65536; scratch as for fb_w3_gemv, sized by fb_bb_gemv_scratch_bytes(O, K, 0).
+ * s_b the same over the group's 8 refined columns; fp32 within a group; the groups (at most 255)
+ * are combined by 64-bit fixed-point integer adds (steps of 2^-26, order-independent, so
+ * repeat-exact; a group's term that is not finite or is 8192 or more in magnitude gives NaN).
+ * Any O in 1..65536; scratch zero-filled once and 256-byte aligned, not shared with other
+ * kernels, sized by fb_bb_gemv_scratch_bytes(O, K, 0).
  * Replaces the reference's m1_out of the v5 kernels (csrc/m1_v5.cu:132-195); all the
  * reference's kernel names map to this one entry point.
  */

@@ -6,8 +6,8 @@
 // sums of +/- x*col in ascending order) laid out entry-major so that the bank of a lookup is the
 // table number; lane = output row; lanes walk the 32 (base, chunk) pairs in a lane-rotated order
 // so that lookups and staged-word reads are bank-conflict free; a warp's rows are one contiguous
-// run of 32-byte code rows, staged by a single bulk copy; split-K over groups is reduced in the
-// kernel through tickets, in ascending group order.
+// run of 32-byte code rows, staged by a single bulk copy; the split over groups is combined in the
+// kernel by one 64-bit fixed-point atomic add per contribution (order-independent, repeat-exact).
 //
 // Two scale conventions:
 //  * group mode (the reference's hybrid g128-s8 payload, deployment.py:23-27, kernel
@@ -47,8 +47,7 @@ struct BBParams {
   const int32_t* sal_idx;
   const __nv_bfloat16* sal;
   void* out;
-  float* partials;
-  unsigned* tickets;
+  unsigned long long* combine;  // [O] split-K accumulators, zero between launches
   unsigned* status;
   int O, K, G, nRU;
   int act_dtype, interleaved, global_mode, n_sal;
@@ -104,6 +103,19 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   };
 
   const int rb = lane & 3, rw = (lane >> 2) & 3, rh = (lane >> 4) & 1;
+  // Lookups use 32-bit shared-window addresses: entry * 128 + table offset is ONE dp4a (a byte
+  // dot product whose only non-zero weight, 128, sits at the wanted byte of the staged word).
+  const uint32_t lut_u32 = smem_u32(lut);
+  uint32_t sel[4];
+#pragma unroll
+  for (int b = 0; b < 4; ++b) sel[b] = 128u << (8 * ((b + rb) & 3));
+  auto lookup = [&](uint32_t word, int b, uint32_t table) {
+    uint32_t address;
+    float value;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(address) : "r"(word), "r"(sel[b]), "r"(table));
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(value) : "r"(address));
+    return value;
+  };
   uint32_t chunk_parity = 0, slot_parity = 0;
   bool dead = false, first_pass = true;
   int g, my_first, my_count;
@@ -111,6 +123,26 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   if (my_count > 0) stage_units(g, my_first, min(S, my_count), 0, kMaxSlots);
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // Split over the groups: every contribution is ONE 64-bit atomic add carrying the scaled
+  // partial sum in fixed point (steps of 2^-26, bits 16..63), an arrival count (bits 0..7) and a
+  // count of partials that are not finite or too large for the format (bits 8..15).  Integer
+  // adds commute, so the result is independent of arrival order; whoever reads back the last
+  // count converts, writes the output and zeroes the word.  The answer is looked at one unit
+  // later, so its round trip hides behind the next unit's lookups.
+  unsigned long long pend_old = 0ull, pend_add = 0ull;
+  int pend_row = -1;
+  auto settle = [&]() {
+    if (pend_row < 0) return;
+    if (((unsigned)pend_old & 255u) == (unsigned)(p.G - 1)) {
+      const unsigned long long total = pend_old + pend_add;
+      float value = __ll2float_rn((long long)total >> 16) * 1.4901161193847656e-08f;  // 2^-26
+      if ((total >> 8) & 255ull) value = __int_as_float(0x7fc00000);
+      store_act(p.out, p.act_dtype, pend_row, value);
+      p.combine[pend_row] = 0ull;
+    }
+    pend_row = -1;
+  };
 
   for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
     if (!first_pass) {
@@ -131,14 +163,25 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
         const float cv = GLOBAL ? __half2float(p.gcol[(size_t)base * p.K + kk]) : p.cols[(size_t)kk * 2 + base];
         v8[j] = __fmul_rn(xv, cv);
       }
+      // entry(p) = sum_b (bit b of p ? +v_b : -v_b) = low-nibble part + high-nibble part.  Warp w
+      // owns the entries whose low nibble is 2w or 2w+1; the sixteen high-nibble parts come from
+      // a tree (one add each), so an entry costs one add and one store.
       unsigned char* const column = lut + lane * 4;
-#pragma unroll 4
-      for (int e = 0; e < 256 / kWarps; ++e) {
-        const int pp = warp * (256 / kWarps) + e;
-        float s = 0.f;
+      float hi[16];
+      hi[0] = ((-v8[4] - v8[5]) - v8[6]) - v8[7];
 #pragma unroll
-        for (int b = 0; b < 8; ++b) s += ((pp >> b) & 1) ? v8[b] : -v8[b];
-        *reinterpret_cast<float*>(column + (size_t)pp * 128) = s;
+      for (int h = 1; h < 16; ++h) {
+        const int top = h >= 8 ? 3 : (h >= 4 ? 2 : (h >= 2 ? 1 : 0));
+        hi[h] = hi[h & ~(1 << top)] + 2.f * v8[4 + top];
+      }
+#pragma unroll
+      for (int qq = 0; qq < 16 / kWarps; ++qq) {
+        const int q = warp * (16 / kWarps) + qq;
+        float lo = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) lo += ((q >> b) & 1) ? v8[b] : -v8[b];
+#pragma unroll
+        for (int h = 0; h < 16; ++h) *reinterpret_cast<float*>(column + (size_t)(h * 16 + q) * 128) = lo + hi[h];
       }
       if (!GLOBAL) {
         // two refinement tables over the group's 8 selected columns; warp w fills entries 32w..32w+31
@@ -166,6 +209,11 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
       const bool live = row < p.O;
       float2 rs = make_float2(0.f, 0.f), srs = make_float2(0.f, 0.f);
       unsigned sp = 0;
+      uint32_t g0bits = 0, g1bits = 0;
+      if (GLOBAL && live) {
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(g0bits) : "l"(p.grow + row));
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(g1bits) : "l"(p.grow + (size_t)p.O + row));
+      }
       if (!GLOBAL && live) {
         rs = *reinterpret_cast<const float2*>(p.rows + ((size_t)g * p.O + row) * 2);
         srs = *reinterpret_cast<const float2*>(p.srows + ((size_t)g * p.O + row) * 2);
@@ -189,6 +237,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
       float d0 = 0.f, d1 = 0.f;
       if (!dead) {
         const unsigned char* const buf = stage_base + slot * kUnitBytes + lane * 32;
+        const uint32_t buf_u32 = stage_u32 + (uint32_t)(slot * kUnitBytes + lane * 32);
         if (!INTERLEAVED) {
           // row = [base 0: 16 bytes][base 1: 16 bytes]; steps with jh = 0 serve base rh
           float acc[2] = {0.f, 0.f};
@@ -198,13 +247,10 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
 #pragma unroll
             for (int jw = 0; jw < 4; ++jw) {
               const int ws = (jw + rw) & 3;
-              const uint32_t w = *reinterpret_cast<const uint32_t*>(buf + h * 16 + ws * 4);
+              uint32_t w;
+              asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(buf_u32 + (uint32_t)(h * 16 + ws * 4)));
 #pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                const int byte = (b + rb) & 3;
-                const uint32_t entry = (w >> (8 * byte)) & 0xffu;
-                acc[jh] += *reinterpret_cast<const float*>(lut + entry * 128 + (64 * h + 16 * ws + 4 * byte));
-              }
+              for (int b = 0; b < 4; ++b) acc[jh] += lookup(w, b, lut_u32 + (uint32_t)(64 * h + 16 * ws + 4 * ((b + rb) & 3)));
             }
           }
           d0 = rh ? acc[1] : acc[0];
@@ -238,74 +284,41 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
       __syncwarp();
       if (!dead && i + S < my_count) stage_units(g, my_first + i + S, 1, slot, slot);
 
+      settle();  // the previous unit's answer has long arrived
       if (!dead && live) {
+        float value;
         if (GLOBAL) {
-          float* dst = p.partials + ((size_t)g * 2) * p.O + row;
-          dst[0] = d0;
-          dst[p.O] = d1;
+          asm volatile("" : "+r"(g0bits), "+r"(g1bits));  // first use: after the lookups
+          value = __fmaf_rn(__half2float(__ushort_as_half((unsigned short)g0bits)), d0, 0.f);
+          value = __fmaf_rn(__half2float(__ushort_as_half((unsigned short)g1bits)), d1, value);
+          // the dense residual columns are dealt round-robin over the groups' contributions
+          for (int sidx = g; sidx < p.n_sal; sidx += p.G)
+            value = __fmaf_rn(__bfloat162float(p.sal[(size_t)row * p.n_sal + sidx]), load_act(p.x, p.act_dtype, p.sal_idx[sidx]), value);
         } else {
           const uint32_t p0 = INTERLEAVED ? compact_even(sp) : (sp & 0xffu);
           const uint32_t p1 = INTERLEAVED ? compact_even(sp >> 1) : (sp >> 8);
-          float value = __fmaf_rn(rs.x, d0, 0.f);
+          value = __fmaf_rn(rs.x, d0, 0.f);
           value = __fmaf_rn(rs.y, d1, value);
           value = __fmaf_rn(srs.x, sparse_lut[p0], value);
           value = __fmaf_rn(srs.y, sparse_lut[256 + p1], value);
-          if (p.G == 1)
-            store_act(p.out, p.act_dtype, row, value);
-          else
-            p.partials[(size_t)g * p.O + row] = value;
+        }
+        if (p.G == 1) {
+          store_act(p.out, p.act_dtype, row, value);
+        } else {
+          const bool fits = fabsf(value) < 8192.f;  // 255 of them stay inside 48 bits
+          pend_add = fits ? ((unsigned long long)__float2ll_rn(value * 67108864.f) << 16) + 1ull : 257ull;
+          asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;" : "=l"(pend_old) : "l"(p.combine + row), "l"(pend_add) : "memory");
+          pend_row = row;
         }
       }
     }
     if (my_count > 0) chunk_parity ^= 1u;
   }
 
-  // ---- split-K hand-over (see fb_w3_gemv.cu): one ticket per 32-row unit, taken once per warp ----
-  if ((GLOBAL || p.G > 1) && !dead) {
-    __syncwarp();
-    for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
-      share(v, g, my_first, my_count);
-      for (int base = 0; base < my_count; base += 32) {
-        const int count = min(32, my_count - base);
-        const int my_ru = lane < count ? my_first + base + lane : -1;
-        unsigned prior = 0;
-        if (my_ru >= 0)
-          asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prior) : "l"(p.tickets + my_ru) : "memory");
-        __syncwarp();
-        unsigned todo = __ballot_sync(0xffffffffu, my_ru >= 0 && prior == (unsigned)p.G - 1u);
-        while (todo) {
-          const int j = __ffs(todo) - 1;
-          todo &= todo - 1;
-          const int row = (my_first + base + j) * kUnitRows + lane;
-          if (row < p.O) {
-            if (GLOBAL) {
-              float t0 = 0.f, t1 = 0.f;
-#pragma unroll 4
-              for (int g2 = 0; g2 < p.G; ++g2) {
-                t0 += __ldcg(p.partials + ((size_t)g2 * 2) * p.O + row);
-                t1 += __ldcg(p.partials + ((size_t)g2 * 2 + 1) * p.O + row);
-              }
-              float value = __fmaf_rn(__half2float(p.grow[row]), t0, 0.f);
-              value = __fmaf_rn(__half2float(p.grow[(size_t)p.O + row]), t1, value);
-              for (int s = 0; s < p.n_sal; ++s)
-                value = __fmaf_rn(__bfloat162float(p.sal[(size_t)row * p.n_sal + s]), load_act(p.x, p.act_dtype, p.sal_idx[s]), value);
-              store_act(p.out, p.act_dtype, row, value);
-            } else {
-              float total = 0.f;
-#pragma unroll 8
-              for (int g2 = 0; g2 < p.G; ++g2) total += __ldcg(p.partials + (size_t)g2 * p.O + row);
-              store_act(p.out, p.act_dtype, row, total);
-            }
-          }
-        }
-        if (my_ru >= 0 && prior == (unsigned)p.G - 1u) p.tickets[my_ru] = 0u;
-      }
-    }
-  }
+  settle();
 }
 
-constexpr size_t kTicketsOffset = 256;
-constexpr size_t kPartialsOffset = 16384;
+constexpr size_t kCombineOffset = 16384;  // after the status block: one 64-bit word per output row
 
 template <bool INTERLEAVED, bool GLOBAL>
 int launch(const BBParams& p, int grid, size_t smem, int max_smem, bool pdl, cudaStream_t stream) {
@@ -337,15 +350,14 @@ int launch(const BBParams& p, int grid, size_t smem, int max_smem, bool pdl, cud
 }
 
 int run(BBParams& p, void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream, const char* who) {
-  const size_t need = kPartialsOffset + (size_t)p.G * (p.global_mode ? 2 : 1) * p.O * sizeof(float);
+  const size_t need = kCombineOffset + (size_t)p.O * sizeof(unsigned long long);
   if (!scratch || scratch_bytes < need) return fail(FB_ESCRATCH, "%s: scratch of %zu bytes needed, %zu given", who, need, scratch_bytes);
   if (!aligned(scratch, 256)) return fail(FB_EINVAL, "%s: scratch must be 256-byte aligned", who);
   const DeviceInfo* info = device_info();
   if (!info) return FB_ECUDA;
   unsigned char* base = static_cast<unsigned char*>(scratch);
   p.status = reinterpret_cast<unsigned*>(base);
-  p.tickets = reinterpret_cast<unsigned*>(base + kTicketsOffset);
-  p.partials = reinterpret_cast<float*>(base + kPartialsOffset);
+  p.combine = reinterpret_cast<unsigned long long*>(base + kCombineOffset);
   p.nRU = (p.O + kUnitRows - 1) / kUnitRows;
   int c = kCtasPerSm * info->sm_count / p.G;
   if (c < 1) c = 1;
@@ -366,7 +378,7 @@ int run(BBParams& p, void* scratch, size_t scratch_bytes, unsigned flags, fb_str
 int check_common(const char* who, const void* x, int act_dtype, const uint8_t* codes, void* out, int O, int K) {
   if (!x || !codes || !out) return fail(FB_EINVAL, "%s: x, codes and out must be non-null", who);
   if (act_dtype != FB_F16 && act_dtype != FB_BF16) return fail(FB_EINVAL, "%s: activation dtype must be FB_F16 or FB_BF16", who);
-  if (K < 128 || K % 128 || K / 128 > 1024) return fail(FB_ELIMIT, "%s: K=%d must be a multiple of 128 with at most 1024 groups", who, K);
+  if (K < 128 || K % 128 || K / 128 > 255) return fail(FB_ELIMIT, "%s: K=%d must be a multiple of 128 with at most 255 groups", who, K);
   if (O < 1 || O > 65536) return fail(FB_ELIMIT, "%s: O=%d outside 1..65536", who, O);
   if (!aligned(codes, 16)) return fail(FB_EINVAL, "%s: codes must be 16-byte aligned", who);
   if (overlaps(out, (size_t)O * 2, x, (size_t)K * 2) || overlaps(out, (size_t)O * 2, codes, (size_t)(K / 128) * O * 32))
@@ -378,7 +390,8 @@ int check_common(const char* who, const void* x, int act_dtype, const uint8_t* c
 
 extern "C" size_t fb_bb_gemv_scratch_bytes(int out_features, int in_features, int global_scales) {
   if (out_features < 1 || in_features < 128) return 0;
-  return kPartialsOffset + (size_t)(in_features / 128) * (global_scales ? 2 : 1) * out_features * sizeof(float);
+  (void)global_scales;
+  return kCombineOffset + (size_t)out_features * sizeof(unsigned long long);
 }
 
 extern "C" int fb_bb_gemv(const void* x, int act_dtype, const uint8_t* codes, int planar, const float* rows,

@@ -451,15 +451,16 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       const int lrow = (ru - cur_begin) * kUnitRows + lane;
       // scales and zero points straight from global memory (one coalesced 64-byte run per group):
       // requested now, needed only after the lookups
-      unsigned short sbitsA = 0, sbitsB = 0;
-      unsigned char zA = 4, zB = 4;
+      // (volatile, so that the requests stay HERE and their first use stays after the lookups:
+      // left to itself the compiler may move the pair together and expose the round trip)
+      uint32_t sbitsA = 0, sbitsB = 0, zA = 4, zB = 4;
       if (!dead) {
         const int at = gA * cur_O + lrow;  // G * O < 2^24
-        sbitsA = __ldg(cur_scales + at);
-        if (hasB) sbitsB = __ldg(cur_scales + at + cur_O);
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sbitsA) : "l"(cur_scales + at));
+        if (hasB) asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sbitsB) : "l"(cur_scales + at + cur_O));
         if (cur_zeros) {
-          zA = __ldg(cur_zeros + at);
-          if (hasB) zB = __ldg(cur_zeros + at + cur_O);
+          asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(zA) : "l"(cur_zeros + at));
+          if (hasB) asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(zB) : "l"(cur_zeros + at + cur_O));
         }
       }
       FB_WAVE_MARK(seq, 0);
@@ -547,8 +548,9 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       FB_WAVE_MARK(seq, 5);
 
       if (!dead && mine && !(FB_W3_ABLATE & 2)) {
-        const float sA = bits_to_float(sbitsA, p.scale_dtype);
-        const float sB = bits_to_float(sbitsB, p.scale_dtype);
+        asm volatile("" : "+r"(sbitsA), "+r"(sbitsB), "+r"(zA), "+r"(zB));  // first use: after the lookups
+        const float sA = bits_to_float((unsigned short)sbitsA, p.scale_dtype);
+        const float sB = bits_to_float((unsigned short)sbitsB, p.scale_dtype);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
           auto plane_sum = [&](int jh, int pl) { return acc2[m][jh][pl][0] + acc2[m][jh][pl][1]; };

@@ -261,9 +261,13 @@ def test_global_two_base_kernel(o, k):
     saved = out.clone()
     binary_global.global_two_base_m1_out(x.cuda(), lg, out)
     assert torch.equal(saved, out)
+    # scaling by two is exact in every fp32 step; the combine over groups is in fixed point (steps
+    # of 2^-26), which can move a 16-bit rounding boundary in a rare row, by one ulp
     doubled = torch.empty_like(out)
     binary_global.global_two_base_m1_out((x * 2).cuda(), lg, doubled)
-    assert torch.equal(doubled.float(), out.float() * 2)
+    twice = out.float() * 2
+    assert float((doubled.float() != twice).float().mean()) <= 5e-3
+    assert float((doubled.float() - twice).abs().max()) <= float(twice.abs().max()) * 2.0 ** -7
 
 
 @pytest.mark.gpu
