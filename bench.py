@@ -30,7 +30,7 @@ SHAPES = (  # name, out_features, in_features (Qwen3-8B)
 )
 LAYERS = 36
 NOMINAL_HBM_GBS = 8000.0
-DRAM_TRAFFIC_RATIO = 20.106 / 20.087
+DRAM_TRAFFIC_RATIO = 20.203 / 20.087
 METRIC = "W3 GEMV HBM GB/s (% of 8 TB/s) per Qwen3-8B shape; batch-1 decode tokens/s"
 
 
@@ -537,7 +537,7 @@ def main():
                          "frac": round(per_gpu / peak, 4), "traffic": None, "peak_kind": peak_kind,
                          "kernel": "w3_gemv_kernel<1,false>", "bytes_per_launch_avg": result["step_bytes"] // (LAYERS * len(SHAPES))},
         }
-        # DRAM bytes per launch: ncu measured 20.106 MB for the 12288x4096 launch against 20.087 MB
+        # DRAM bytes per launch: ncu measured 20.203 MB for the 12288x4096 launch against 20.087 MB
         # algorithmic (profiles/w3_gemv_12288x4096_m1.md); traffic grows with the bytes a launch
         # streams, so the average launch of this mixed-shape step is scaled by the same ratio.
         line["roofline"]["traffic"] = int(DRAM_TRAFFIC_RATIO * line["roofline"]["bytes_per_launch_avg"])
