@@ -6,7 +6,7 @@
 // shared-memory operand tile and lets one tcgen05.mma apply it to all rows of the batch:
 //   * a CTA owns 128 output rows and a contiguous range of K groups (split-K over CTAs);
 //   * the three bit planes of (group, 128 rows) arrive by one tiled TMA copy (6 KB);
-//   * 256 threads turn them into a 128 x 128 tile of 16-bit weights T((code - zero) * scale),
+//   * 256 threads turn them into a 128 x 128 tile of 16-bit weights T((code - zero) * T(scale)),
 //     written straight in the K-major "core matrix" order that the MMA's shared-memory descriptor
 //     walks (8 rows x 16 bytes per core matrix, no swizzle): one 16-byte store per 8 weights;
 //   * the activations of the group (M rows padded to N = 16) are stored the same way;
@@ -75,6 +75,7 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64
       : "memory");
 }
 
+template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_constant__ MmaParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* const a_tiles = smem;                           // 2 x 32 KB
@@ -172,7 +173,22 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
       const unsigned char* pl = planes_s + (size_t)buf * kPlaneTile + row_in_tile * 16 + khalf * 8;
       const uint2 w0 = *reinterpret_cast<const uint2*>(pl), w1 = *reinterpret_cast<const uint2*>(pl + kTileRows * 16),
                   w2 = *reinterpret_cast<const uint2*>(pl + 2 * kTileRows * 16);
-      const float bias = -(128.f + zero) * scale;  // value = (128 + code) * scale + bias, one fp32 rounding
+      // weight = T((code - zero) * T(scale)) with packed 16-bit arithmetic: the pair of codes is
+      // built as the 16-bit floats (magic + code), magic = 128 (bf16) or 1024 (fp16), where small
+      // integers are exact; one packed subtract removes magic + zero exactly, one packed multiply
+      // applies the scale with a single rounding, as the reference's dense fallback rounds.
+      constexpr bool bf16 = BF16;
+      const uint32_t magic = bf16 ? 0x43004300u : 0x64006400u;
+      uint32_t offset2, scale2;
+      if (bf16) {
+        const __nv_bfloat162 o2 = __float2bfloat162_rn(128.f + zero), s2 = __float2bfloat162_rn(scale);
+        offset2 = *reinterpret_cast<const uint32_t*>(&o2);
+        scale2 = *reinterpret_cast<const uint32_t*>(&s2);
+      } else {
+        const __half2 o2 = __float2half2_rn(1024.f + zero), s2 = __float2half2_rn(scale);
+        offset2 = *reinterpret_cast<const uint32_t*>(&o2);
+        scale2 = *reinterpret_cast<const uint32_t*>(&s2);
+      }
       unsigned char* const a_row = a_tiles + (size_t)buf * kATile + (row_in_tile >> 3) * 128 + (row_in_tile & 7) * 16;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -186,16 +202,16 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          // codes of inputs 2i (low half) and 2i+1 (high half) as bf16 128 + code
-          const uint32_t pair = ((((low2 >> (2 * i)) & 0x00030003u) | ((high >> (2 * i)) & 0x00040004u))) | 0x43004300u;
-          const float lo = __uint_as_float(pair << 16), hi = __uint_as_float(pair & 0xffff0000u);
-          const float vlo = lo * scale + bias, vhi = hi * scale + bias;
-          if (p.act_dtype == FB_BF16) {
-            const __nv_bfloat162 both = __floats2bfloat162_rn(vlo, vhi);
-            packed[i] = *reinterpret_cast<const uint32_t*>(&both);
+          // codes of inputs 2i (low half) and 2i+1 (high half) as 16-bit floats magic + code
+          const uint32_t pair = ((((low2 >> (2 * i)) & 0x00030003u) | ((high >> (2 * i)) & 0x00040004u))) | magic;
+          if (bf16) {
+            const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pair), *reinterpret_cast<const __nv_bfloat162*>(&offset2)),
+                                             *reinterpret_cast<const __nv_bfloat162*>(&scale2));
+            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
           } else {
-            const __half2 both = __floats2half2_rn(vlo, vhi);
-            packed[i] = *reinterpret_cast<const uint32_t*>(&both);
+            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&offset2)),
+                                      *reinterpret_cast<const __half2*>(&scale2));
+            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
           }
         }
         *reinterpret_cast<uint4*>(a_row + (size_t)(khalf * 8 + c) * 2048) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -376,7 +392,8 @@ extern "C" int fb_w3_gemm_small(const void* x, int act_dtype, int m, const uint8
   {
     std::lock_guard<std::mutex> guard(lock);
     if (device >= 0 && device < 64 && !ready[device]) {
-      cudaError_t err = cudaFuncSetAttribute(w3_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t err = cudaFuncSetAttribute(w3_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err == cudaSuccess) err = cudaFuncSetAttribute(w3_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(w3_mma_kernel)");
       ready[device] = true;
     }
@@ -391,7 +408,7 @@ extern "C" int fb_w3_gemm_small(const void* x, int act_dtype, int m, const uint8
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = pdl_allowed() ? 1 : 0;
-  cudaError_t err = cudaLaunchKernelEx(&config, w3_mma_kernel, p);
+  cudaError_t err = act_dtype == FB_BF16 ? cudaLaunchKernelEx(&config, w3_mma_kernel<true>, p) : cudaLaunchKernelEx(&config, w3_mma_kernel<false>, p);
   if (err != cudaSuccess) return cuda_fail(err, "w3_mma_kernel launch");
   return FB_OK;
 }
