@@ -422,20 +422,23 @@ def small_case(args):
     small, self-ending program that profiler captures are taken on."""
     import torch
 
-    from marlin_style_fluxbin_b200.w3_lut_deployment import w3_lut_m1_out, workspace_shape
+    from marlin_style_fluxbin_b200.w3_lut_deployment import w3_lut_gemv_out, w3_lut_m1_out, workspace_shape
 
     o, k = (int(v) for v in args.case.lower().split("x"))
     device = torch.device("cuda", 0)
     gen = torch.Generator(device=device).manual_seed(1)
     layouts = [synthetic_layout(torch, o, k, device, gen) for _ in range(args.copies)]
-    x = torch.randn(1, k, device=device, generator=gen).bfloat16()
-    out = torch.empty(1, o, device=device, dtype=torch.bfloat16)
+    x = torch.randn(args.rows, k, device=device, generator=gen).bfloat16()
+    out = torch.empty(args.rows, o, device=device, dtype=torch.bfloat16)
     workspace = torch.empty(workspace_shape(o, k), device=device)
     for _ in range(2):
         for layout in layouts:
-            w3_lut_m1_out(x, layout, out, workspace, row_tile=256)
+            if args.rows == 1:
+                w3_lut_m1_out(x, layout, out, workspace, row_tile=256)
+            else:  # the tensor-core small-batch kernel
+                w3_lut_gemv_out(x, layout, out, kernel="mma")
     torch.cuda.synchronize()
-    print(json.dumps({"case": args.case, "copies": args.copies, "launches": 2 * args.copies,
+    print(json.dumps({"case": args.case, "rows": args.rows, "copies": args.copies, "launches": 2 * args.copies,
                       "bytes_per_launch": gemv_bytes(o, k), "checksum": float(out.float().abs().sum())}))
 
 
@@ -450,6 +453,7 @@ def main():
     parser.add_argument("--case", default=None, metavar="OxK",
                         help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
     parser.add_argument("--copies", type=int, default=8)
+    parser.add_argument("--rows", type=int, default=1, help="with --case: activation rows (above 1 runs the tensor-core kernel)")
     parser.add_argument("--headline-only", action="store_true",
                         help="time only the headline step (no per-shape table, sweeps, decode or CPU leg): for profiler launch lists")
     args = parser.parse_args()

@@ -128,15 +128,16 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
 
   // Per-group operands that come straight from global memory (scale and zero point of this
   // thread's row, eight activations of this thread's batch row) are requested one group ahead.
-  float scale_next = 0.f, zero_next = 4.f;
+  // (volatile requests: they must stay a whole group ahead of their first use)
+  uint32_t scale_bits_next = 0, zero_bits_next = 4;
   uint4 x_next = make_uint4(0u, 0u, 0u, 0u);
   auto fetch_group = [&](int g) {
-    scale_next = 0.f;
-    zero_next = 4.f;
+    scale_bits_next = 0;
+    zero_bits_next = 4;
     x_next = make_uint4(0u, 0u, 0u, 0u);
-    if (row < p.O) {  // rows past O contribute zero weights
-      scale_next = bits_to_float(__ldg(p.scales + (size_t)g * p.O + row), p.scale_dtype);
-      if (p.zeros) zero_next = (float)__ldg(p.zeros + (size_t)g * p.O + row);
+    if (row < p.O) {  // rows past O contribute zero weights (scale 0)
+      asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(scale_bits_next) : "l"(p.scales + (size_t)g * p.O + row));
+      if (p.zeros) asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(zero_bits_next) : "l"(p.zeros + (size_t)g * p.O + row));
     }
     if (xn < p.M) {
       const int kbase = g * 128 + xc * 8;
@@ -147,7 +148,9 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
         for (int j = 0; j < 8; ++j) v[j] = xrow[p.perm[kbase + j]];
         x_next = make_uint4(v[0] | (uint32_t)v[1] << 16, v[2] | (uint32_t)v[3] << 16, v[4] | (uint32_t)v[5] << 16, v[6] | (uint32_t)v[7] << 16);
       } else {
-        x_next = *reinterpret_cast<const uint4*>(xrow + kbase);
+        asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(x_next.x), "=r"(x_next.y), "=r"(x_next.z), "=r"(x_next.w)
+                     : "l"(xrow + kbase));
       }
     }
   };
@@ -155,7 +158,8 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
 
   for (int gi = 0; gi < ng; ++gi) {
     const int buf = gi & 1;
-    const float scale = scale_next, zero = zero_next;
+    const float scale = row < p.O ? bits_to_float((unsigned short)scale_bits_next, p.scale_dtype) : 0.f;
+    const float zero = (float)zero_bits_next;
     const uint4 xraw = x_next;
     if (gi + 1 < ng) fetch_group(g_begin + gi + 1);
     // the tiles of this buffer were last read by the MMAs issued two groups ago
@@ -252,25 +256,35 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     const int out_row = tile * kTileRows + warp * 32 + lane;  // TMEM lane = row of the tile
     if (out_row < p.O) {
+      if (p.splits == 1) {
 #pragma unroll
-      for (int n = 0; n < kN; ++n) {
-        if (n >= p.M) break;
-        const float v = __uint_as_float(acc[n]);
-        if (p.splits == 1) {
-          store_act(p.out, p.act_dtype, n * p.O + out_row, v);
-        } else {
-          // same combine as the M = 1 kernel: fixed point in bits 12..63, arrivals in bits 0..5,
-          // non-finite / out-of-range contributions counted in bits 6..11
+        for (int n = 0; n < kN; ++n)
+          if (n < p.M) store_act(p.out, p.act_dtype, n * p.O + out_row, __uint_as_float(acc[n]));
+      } else {
+        // same combine as the M = 1 kernel: fixed point in bits 12..63, arrivals in bits 0..5,
+        // non-finite / out-of-range contributions counted in bits 6..11.  All adds of a thread are
+        // issued before the first answer is looked at: one round trip, not one per batch row.
+        unsigned long long add[kN], old[kN];
+#pragma unroll
+        for (int n = 0; n < kN; ++n) {
+          const float v = __uint_as_float(acc[n]);
           const bool fits = fabsf(v) < 2097152.f;
-          const unsigned long long add = fits ? ((unsigned long long)__float2ll_rn(v * 67108864.f) << 12) + 1ull : 65ull;
-          unsigned long long* word = p.combine + (size_t)n * p.O + out_row;
-          const unsigned long long old = atomicAdd(word, add);
-          if ((int)(old & 63ull) == p.splits - 1) {
-            const unsigned long long total = old + add;
+          add[n] = fits ? ((unsigned long long)__float2ll_rn(v * 67108864.f) << 12) + 1ull : 65ull;
+          old[n] = 0ull;
+          if (n < p.M)
+            asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;"
+                         : "=l"(old[n])
+                         : "l"(p.combine + (size_t)n * p.O + out_row), "l"(add[n])
+                         : "memory");
+        }
+#pragma unroll
+        for (int n = 0; n < kN; ++n) {
+          if (n < p.M && (int)(old[n] & 63ull) == p.splits - 1) {
+            const unsigned long long total = old[n] + add[n];
             float value = __ll2float_rn((long long)total >> 12) * 1.4901161193847656e-08f;
             if ((total >> 6) & 63ull) value = __int_as_float(0x7fc00000);
             store_act(p.out, p.act_dtype, n * p.O + out_row, value);
-            *word = 0ull;
+            p.combine[(size_t)n * p.O + out_row] = 0ull;
           }
         }
       }
