@@ -373,9 +373,24 @@ def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=(
             margins = [float(b[i, reference[0][i]] - b[i, greedy[i]]) for i in differ]
             entry["disagreements"] = len(differ)
             entry["disagreements_outside_near_ties"] = sum(1 for v in margins if v > 4 * rms)
+        if arm == "w3":
+            tp_forced, tp_greedy, tp_logits = fed, greedy, logits
         out[arm] = entry
         del engine, graph
         torch.cuda.empty_cache()
+    if world > 1 and "w3" in out:
+        # the sharded engine against an unsharded engine with the same weights, on rank 0:
+        # the allreduce changes the summation order, nothing else
+        if rank == 0:
+            single = DecodeEngine(shape, device=device, max_positions=prompt + steps + 8, arm="w3", tp_rank=0, tp_size=1)
+            first_single = single.prefill(ids).argmax(-1)
+            _, greedy_single, logits_single = single.decode(first_single, prompt, min(steps, 8), forced=tp_forced[:min(steps, 8)])
+            a, b = tp_logits[:min(steps, 8)].double(), logits_single.double()
+            out["w3"]["tp_vs_single_logits_nrmse"] = round(float((a - b).square().mean().sqrt() / b.square().mean().sqrt()), 5)
+            out["w3"]["tp_vs_single_greedy_agreement"] = round(float((tp_greedy[:min(steps, 8)] == greedy_single).float().mean()), 4)
+            del single
+            torch.cuda.empty_cache()
+        torch.distributed.barrier()
     if "w3" in out and "bf16" in out:
         out["w3_over_bf16"] = round(out["w3"]["tokens_per_s"] / out["bf16"]["tokens_per_s"], 3)
     out["config"] = {"model": shape_name, "prompt_tokens": prompt, "decode_tokens": steps, "tensor_parallel": world,
