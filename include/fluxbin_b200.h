@@ -121,6 +121,35 @@ int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transform, const vo
                            void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream);
 
 /*
+ * Tensor-parallel form of a row-split Linear (o_proj, down_proj): one matrix, M = 1, optional
+ * fused input transform (0 = none) as in fb_w3_gemv_fused_input.  Instead of writing `out`
+ * (ignored; may be any non-null pointer), the final fp32 value of output row o is stored,
+ * together with a valid mark, as ONE 8-byte store {value, 1} to data[r][o] for every rank r
+ * (pointers into each rank's exchange buffer of 8-byte slots, peer-mapped over NVLink, this
+ * rank's own included).  fb_tp_reduce on each rank polls the slots and sums the ranks' rows:
+ * compute and exchange are one kernel, the transfer overlaps the rest of the GEMV, there is no
+ * fence, no counter and no collective library call between the two Linears.
+ * No counterpart in the reference (single GPU only, engine_interface.py:26-27).
+ */
+typedef struct fb_w3_push {
+  void* data[8];
+  int world;
+} fb_w3_push_t;
+int fb_w3_gemv_push(const void* x, int act_dtype, int transform, const void* operand, float eps,
+                    const fb_w3_matrix_t* matrix, int scale_dtype, int in_features, const fb_w3_push_t* push,
+                    void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream);
+
+/*
+ * out[i] = T(T(sum_r value(parts[r*n + i])) + residual[i]) for i < n: the receiving half of
+ * fb_w3_gemv_push.  `parts` is this rank's exchange buffer, [world, n] 8-byte slots, all zero
+ * before the first use; a thread waits until the slots of its element carry the mark, sums them
+ * in ascending rank order and zeroes them again.  The wait is bounded (about ten seconds; on
+ * expiry *status is set to 4 and the sum is of whatever arrived).  residual may be NULL.
+ */
+int fb_tp_reduce(void* parts, int world, const void* residual, void* out, int n, int dtype, unsigned* status,
+                 fb_stream_t stream);
+
+/*
  * Small-batch form on the tensor cores: y[M,O] = x[M,K] . W^T for M = 1..16, same layout and
  * dtypes as fb_w3_gemv.  Every weight is dequantised once, T((code - zero) * scale) with T the
  * activation dtype, into a shared-memory operand tile and applied to all M rows by tcgen05.mma

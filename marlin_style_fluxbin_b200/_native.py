@@ -29,6 +29,12 @@ class W3Matrix(ctypes.Structure):
                 ("out", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("out_features", ctypes.c_int)]
 
 
+class W3Push(ctypes.Structure):
+    """``fb_w3_push_t`` of the C header: per rank, where this rank's rows go and which counter to bump."""
+
+    _fields_ = [("data", ctypes.c_void_p * 8), ("world", ctypes.c_int)]
+
+
 class NativeError(RuntimeError):
     """A call into the CUDA library was rejected (message from ``fb_last_error``)."""
 
@@ -67,6 +73,13 @@ def library() -> ctypes.CDLL:
         lib.fb_w3_gemm_small.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                          ctypes.c_size_t, ctypes.c_void_p]
+        lib.fb_w3_gemv_push.restype = ctypes.c_int
+        lib.fb_w3_gemv_push.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_float,
+                                        ctypes.POINTER(W3Matrix), ctypes.c_int, ctypes.c_int, ctypes.POINTER(W3Push), ctypes.c_void_p,
+                                        ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p]
+        lib.fb_tp_reduce.restype = ctypes.c_int
+        lib.fb_tp_reduce.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                     ctypes.c_void_p, ctypes.c_void_p]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.fb_bb_gemv_scratch_bytes.restype = ctypes.c_size_t
@@ -336,3 +349,27 @@ def w3_gemm_small(x, planes, scales, zeros, perm, out, *, scratch=None) -> None:
                                          ptr(zeros) if zeros is not None else None, ptr(perm) if perm is not None else None,
                                          ptr(out), o, k, ptr(scratch), scratch.numel() * scratch.element_size(),
                                          stream_handle(x.device)))
+
+
+def w3_push_descriptor(data_ptrs) -> W3Push:
+    """``fb_w3_push_t`` from one slot-array pointer per rank (plain integers)."""
+    push = W3Push()
+    push.world = len(data_ptrs)
+    for r, data in enumerate(data_ptrs):
+        push.data[r] = data
+    return push
+
+
+def w3_gemv_push(x, transform: int, operand, eps: float, matrix, k: int, scale_dtype, push: W3Push, *, scratch, pdl=True) -> None:
+    """Row-split Linear of a tensor-parallel rank: results go to every rank's exchange buffer (see the header)."""
+    with torch.cuda.device(x.device):
+        check(library().fb_w3_gemv_push(ptr(x), dtype_tag(x.dtype), transform, ptr(operand), float(eps), matrix, dtype_tag(scale_dtype), k,
+                                        ctypes.byref(push), ptr(scratch), scratch.numel() * scratch.element_size(),
+                                        0 if pdl else FB_W3_NO_PDL, stream_handle(x.device)))
+
+
+def tp_reduce(parts_ptr: int, world: int, residual, out, status_ptr: int) -> None:
+    """Receiving half of the push: polls every rank's slots, sums their rows, adds the residual."""
+    with torch.cuda.device(out.device):
+        check(library().fb_tp_reduce(ctypes.c_void_p(parts_ptr), world, ptr(residual), ptr(out), out.numel(), dtype_tag(out.dtype),
+                                     ctypes.c_void_p(status_ptr), stream_handle(out.device)))

@@ -290,6 +290,41 @@ __global__ void silu_mul_kernel(const unsigned short* __restrict__ gate, const u
   out[i] = to_bits(s * bits_to_float(up[i], dtype), dtype);
 }
 
+// Receiving half of the tensor-parallel push: every rank's GEMV stores (fp32 value, mark = 1)
+// pairs, one 8-byte store each, into this rank's exchange buffer [world][n].  A thread polls the
+// `world` slots of its element until all carry the mark (bounded), sums the values in ascending
+// rank order (the same on every rank), and clears the slots for the next use: no fence, no
+// counter, no collective call.  A rank cannot write a slot again before it has received this
+// rank's NEXT contribution, which this rank sends only after this kernel: the clear is safe.
+__global__ void tp_reduce_kernel(uint2* parts, int world, const unsigned short* __restrict__ residual, unsigned short* __restrict__ out,
+                                 int n, int dtype, unsigned* status) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned long long start = global_timer_ns();
+  float total = 0.f;
+  bool expired = false;
+  for (int r = 0; r < world; ++r) {
+    uint2* slot = parts + (size_t)r * n + i;
+    uint2 got;
+    for (;;) {
+      asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(got.x), "=r"(got.y) : "l"(slot) : "memory");
+      if (got.y == 1u) break;
+      if (global_timer_ns() - start > 10000000000ull) {  // ten seconds: ranks may be skewed by host work
+        expired = true;
+        break;
+      }
+    }
+    total += __uint_as_float(got.x);
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %1};" ::"l"(slot), "r"(0u) : "memory");
+  }
+  if (expired) atomicExch(status, 4u);
+  float value = round_to(total, dtype);
+  if (residual) value += bits_to_float(residual[i], dtype);
+  out[i] = to_bits(value, dtype);
+}
+
 template <class Kernel, class... Args>
 int launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const char* what, Args... args) {
   cudaLaunchConfig_t config = {};
@@ -380,4 +415,14 @@ extern "C" int fb_silu_mul(const void* gate, const void* up, void* out, int n, i
   if (n < 1) return fail(FB_ELIMIT, "fb_silu_mul: n must be positive");
   return launch_pdl(silu_mul_kernel, dim3((n + 255) / 256), dim3(256), static_cast<cudaStream_t>(stream), "silu_mul launch",
                     u16(gate), u16(up), u16(out), n, dtype);
+}
+
+extern "C" int fb_tp_reduce(void* parts, int world, const void* residual, void* out, int n, int dtype, unsigned* status,
+                            fb_stream_t stream) {
+  if (!parts || !out || !status) return fail(FB_EINVAL, "fb_tp_reduce: null pointer");
+  if (!aligned(parts, 8)) return fail(FB_EINVAL, "fb_tp_reduce: the exchange buffer must be 8-byte aligned");
+  if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_tp_reduce: dtype must be FB_F16 or FB_BF16");
+  if (world < 1 || world > 8 || n < 1) return fail(FB_ELIMIT, "fb_tp_reduce: world 1..8 and n >= 1");
+  return launch_pdl(tp_reduce_kernel, dim3((n + 127) / 128), dim3(128), static_cast<cudaStream_t>(stream), "tp_reduce launch",
+                    static_cast<uint2*>(parts), world, u16(residual), u16(out), n, dtype, status);
 }

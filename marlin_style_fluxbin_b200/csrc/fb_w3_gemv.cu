@@ -107,6 +107,12 @@ struct W3Params {
   const void* prologue_arg;  // RMSNorm weight [K] (kind 1) or the `up` vector [K] (kind 2)
   int prologue;              // 0 none, 1 RMSNorm of x, 2 x = silu(x) * up  (M = 1, identity order)
   float eps;
+  // Tensor-parallel push (M = 1, one matrix): instead of writing `out`, the final fp32 value of a
+  // row goes, together with a valid mark in the same 8-byte store, to slot `row` of a buffer on
+  // every rank (peer pointers over NVLink, this rank's own buffer included).  No fence and no
+  // counter: the receiver polls each slot for its mark.
+  uint2* push_data[8];
+  int push_world;  // 0 = no push
   float* partials;  // [nSB, M, O]
   unsigned long long* combine;  // [M, O] split-K accumulators, zero between launches
   unsigned* status;
@@ -206,6 +212,12 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   // Final value of one output element: rounded to the 16-bit dtype, then the optional residual
   // is added and the sum rounded again (what separate Linear and add kernels produce).
   auto emit = [&](const W3Matrix& mat, int m, int lrow, float value) {
+    if (p.push_world > 0) {  // one 8-byte store (value, mark) into every rank's exchange buffer
+      const uint2 slot = make_uint2(__float_as_uint(value), 1u);
+      for (int r = 0; r < p.push_world; ++r)
+        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p.push_data[r] + lrow), "r"(slot.x), "r"(slot.y) : "memory");
+      return;
+    }
     if (mat.residual) {
       const float y = p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(value)) : __half2float(__float2half_rn(value));
       value = y + load_act(mat.residual, p.act_dtype, m * mat.O + lrow);
@@ -730,8 +742,16 @@ bool plane_map(const uint8_t* planes, int O, int G, CUtensorMap* out) {
 
 int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices, int scale_dtype,
               const int16_t* perm, int in_features, void* scratch, size_t scratch_bytes, unsigned flags,
-              fb_stream_t stream, int prologue, const void* prologue_arg, float eps) {
+              fb_stream_t stream, int prologue, const void* prologue_arg, float eps, const fb_w3_push_t* push = nullptr) {
   const int K = in_features;
+  if (push) {
+    if (m != 1 || n_matrices != 1 || (flags & FB_W3_GROUP_PARTIALS) || matrices[0].residual)
+      return fail(FB_EINVAL, "fb_w3_gemv_push: one matrix, M = 1, no residual and no group partials");
+    if (push->world < 1 || push->world > 8) return fail(FB_ELIMIT, "fb_w3_gemv_push: world=%d outside 1..8", push->world);
+    for (int r = 0; r < push->world; ++r)
+      if (!push->data[r] || !aligned(push->data[r], 8))
+        return fail(FB_EINVAL, "fb_w3_gemv_push: exchange pointer of rank %d missing or not 8-byte aligned", r);
+  }
   if (prologue < 0 || prologue > 2) return fail(FB_EINVAL, "fb_w3_gemv: unknown input transform %d", prologue);
   if (prologue != 0 && (m != 1 || perm || !prologue_arg || !aligned(prologue_arg, 2)))
     return fail(FB_EINVAL, "fb_w3_gemv: a fused input transform needs M = 1, identity column order and its operand");
@@ -755,6 +775,8 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   p.prologue = prologue;
   p.prologue_arg = prologue_arg;
   p.eps = eps;
+  p.push_world = push ? push->world : 0;
+  for (int r = 0; r < 8; ++r) p.push_data[r] = push && r < push->world ? static_cast<uint2*>(push->data[r]) : nullptr;
   p.n_mats = n_matrices;
   long long total = 0;
   for (int j = 0; j < kMaxMatrices; ++j) {
@@ -847,6 +869,16 @@ extern "C" int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transfor
     return fail(FB_EINVAL, "fb_w3_gemv_fused_input: transform must be FB_W3_INPUT_RMSNORM or FB_W3_INPUT_SILU_MUL");
   return run_multi(x, act_dtype, 1, matrices, n_matrices, scale_dtype, nullptr, in_features, scratch, scratch_bytes, flags, stream,
                    transform, operand, eps);
+}
+
+extern "C" int fb_w3_gemv_push(const void* x, int act_dtype, int transform, const void* operand, float eps,
+                               const fb_w3_matrix_t* matrix, int scale_dtype, int in_features, const fb_w3_push_t* push,
+                               void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
+  if (!push || !matrix) return fail(FB_EINVAL, "fb_w3_gemv_push: matrix and push descriptor must be non-null");
+  if (transform != 0 && transform != FB_W3_INPUT_RMSNORM && transform != FB_W3_INPUT_SILU_MUL)
+    return fail(FB_EINVAL, "fb_w3_gemv_push: unknown input transform %d", transform);
+  return run_multi(x, act_dtype, 1, matrix, 1, scale_dtype, nullptr, in_features, scratch, scratch_bytes, flags, stream, transform,
+                   operand, eps, push);
 }
 
 extern "C" int fb_w3_gemv(const void* x, int act_dtype, int m, const uint8_t* planes, const void* scales,

@@ -78,7 +78,8 @@ def shard_groups(layout, rank, size):
 
 
 class _Layer:
-    __slots__ = ("q", "k", "v", "o", "gate", "up", "down", "ln1", "ln2", "q_norm", "k_norm", "dense", "qkv_list", "gu_list", "o_list", "down_list")
+    __slots__ = ("q", "k", "v", "o", "gate", "up", "down", "ln1", "ln2", "q_norm", "k_norm", "dense", "qkv_list", "gu_list", "o_list", "down_list",
+                 "o_push", "down_push")
 
 
 class DecodeEngine:
@@ -86,7 +87,7 @@ class DecodeEngine:
 
     def __init__(self, shape: ModelShape, *, device, max_positions: int, arm: str = "w3", seed: int = 20260916,
                  tp_rank: int = 0, tp_size: int = 1, group=None, dtype=torch.bfloat16, fuse_inputs: bool = True,
-                 fuse_attention: bool = True):
+                 fuse_attention: bool = True, tp_push: bool | None = None):
         if arm not in ("w3", "bf16"):
             raise ValueError("arm must be w3 or bf16")
         if shape.q_heads % tp_size or shape.kv_heads % tp_size or (shape.hidden // 128) % tp_size or (shape.intermediate // 128) % tp_size:
@@ -98,6 +99,10 @@ class DecodeEngine:
         self.fuse_inputs = fuse_inputs
         # q/k-norm, RoPE and the cache write run inside the attention launch (both arms)
         self.fuse_attention = fuse_attention
+        # tensor parallel, packed arm: the row-split GEMVs push their rows straight into every
+        # rank's exchange buffer (peer stores over NVLink) and a small kernel sums them, instead
+        # of an NCCL allreduce between the two Linears.  Off: NCCL allreduce.
+        self.tp_push = (tp_size > 1 and arm == "w3") if tp_push is None else (tp_push and tp_size > 1 and arm == "w3")
         s, p = shape, tp_size
         self.q_heads, self.kv_heads = s.q_heads // p, s.kv_heads // p
         self.inter = s.intermediate // p
@@ -142,6 +147,8 @@ class DecodeEngine:
         self.attn_scratch = torch.zeros(_native.attn_scratch_bytes(self.q_heads), dtype=torch.uint8, device=self.device)
         if arm == "w3":
             self._build_matrix_lists()
+        if self.tp_push:
+            self._build_exchange()
 
     # ------------------------------------------------------------------ weights
     def _dense(self, layer):
@@ -161,6 +168,31 @@ class DecodeEngine:
         need = max(_native.w3_scratch_bytes(1, 2 * self.inter, self.shape.hidden),
                    _native.w3_scratch_bytes(1, self.shape.hidden, self.inter))
         self.scratch = torch.zeros(need, dtype=torch.uint8, device=self.device)
+
+    def _build_exchange(self):
+        """Symmetric exchange buffer (one per rank, peer-mapped): for each of the two reduction
+        sites of a layer, 8-byte (value, mark) slots [world, hidden]."""
+        import torch.distributed._symmetric_memory as symm
+
+        hidden, world = self.shape.hidden, self.tp_size
+        header = 64  # 8-byte slots: a status word first, then [site][rank][hidden] (value, mark) pairs
+        self._xchg = symm.empty(2 * (header + 2 * world * hidden), dtype=torch.float32, device=self.device)
+        self._xchg.zero_()
+        group = self.group if self.group is not None else torch.distributed.group.WORLD
+        handle = symm.rendezvous(self._xchg, group.group_name)
+        bases = [int(ptr) for ptr in handle.buffer_ptrs]
+        torch.cuda.synchronize(self.device)
+        torch.distributed.barrier(group=self.group)
+        mine = bases[self.tp_rank]
+        self._sites = []
+        for site in range(2):
+            data = 8 * (header + site * world * hidden)
+            push = _native.w3_push_descriptor([base + data + 8 * self.tp_rank * hidden for base in bases])
+            self._sites.append({"push": push, "parts": mine + data, "status": mine})
+        for layer in self.layers:  # no residual in the GEMV: the reduce kernel adds it on every rank
+            entry = lambda lay, out: (lay["planes"], lay["scales"], lay["zeros"], out, None)  # noqa: E731
+            layer.o_push = _native.w3_matrix_list([entry(layer.o, self.h_next)])
+            layer.down_push = _native.w3_matrix_list([entry(layer.down, self.h)])
 
     # ------------------------------------------------------------------ collectives
     def _allreduce(self, tensor):
@@ -244,14 +276,19 @@ class DecodeEngine:
                 nat.qknorm_rope_cache(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.q_rot,
                                       self.k_cache[index], self.v_cache[index], position, s.eps)
                 nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale, self.attn_scratch)
-            if w3:
+            if self.tp_push:
+                site = self._sites[0]
+                nat.w3_gemv_push(self.attn, 0, None, 0.0, layer.o_push, self.attn.shape[-1], f16, site["push"], scratch=self.scratch)
+                nat.tp_reduce(site["parts"], self.tp_size, self.h, self.h_next, site["status"])
+            elif w3:
                 nat.w3_gemv_multi(self.attn, layer.o_list, 1, s.hidden, f16, None, scratch=self.scratch)
             else:
                 torch.mm(self.attn, layer.dense["o"].t(), out=self.h_next)
                 if self.tp_rank == 0:
                     self.h_next.add_(self.h)
                     launches += 1
-            self._allreduce(self.h_next)
+            if not self.tp_push:
+                self._allreduce(self.h_next)
             if not fuse:
                 nat.rmsnorm(self.h_next, layer.ln2, self.xn, s.eps)
             if fuse:
@@ -266,7 +303,15 @@ class DecodeEngine:
                 launches += 2
             if not fuse:
                 nat.silu_mul(self.gate, self.up, self.act)
-            if fuse:
+            if self.tp_push:
+                site = self._sites[1]
+                if fuse:
+                    nat.w3_gemv_push(self.gate, nat.W3_INPUT_SILU_MUL, self.up, 0.0, layer.down_push, self.inter, f16, site["push"],
+                                     scratch=self.scratch)
+                else:
+                    nat.w3_gemv_push(self.act, 0, None, 0.0, layer.down_push, self.inter, f16, site["push"], scratch=self.scratch)
+                nat.tp_reduce(site["parts"], self.tp_size, self.h_next, self.h, site["status"])
+            elif fuse:
                 nat.w3_gemv_fused_input(self.gate, nat.W3_INPUT_SILU_MUL, self.up, 0.0, layer.down_list, 1, s.hidden, f16,
                                         scratch=self.scratch)
             elif w3:
@@ -276,7 +321,8 @@ class DecodeEngine:
                 if self.tp_rank == 0:
                     self.h.add_(self.h_next)
                     launches += 1
-            self._allreduce(self.h)
+            if not self.tp_push:
+                self._allreduce(self.h)
             launches += (6 if fuse else 9) - (1 if self.fuse_attention else 0) + (2 if self.tp_size > 1 else 0)
         nat.rmsnorm(self.h, self.final_norm, self.xn, s.eps)
         torch.mm(self.xn, self.lm_head.t(), out=self.logits)
