@@ -391,3 +391,46 @@ def test_split_k_combine_flags_non_finite_partials_and_resets():
         again = torch.empty_like(good)
         _native.w3_gemv(x_host.cuda(), lg["planes"], lg["scales"], None, None, again, scratch=scratch)
         assert torch.equal(again, good)
+
+
+def test_push_epilogue_and_polling_reduce_on_one_device():
+    """The tensor-parallel exchange protocol with both 'ranks' on one device: each rank's GEMV
+    over its half of K stores (value, mark) pairs into both exchange buffers; the reduce kernel
+    of each rank then finds every mark set (the stores completed earlier on the stream, so nothing
+    waits on a later launch), sums in rank order, adds the residual and clears the slots."""
+    from marlin_style_fluxbin_b200 import _native
+
+    o, k, world = 512, 2048, 2
+    layout, x_host = make_case(o, k, seed=91, zeros=True)
+    lg, x = to_cuda(layout), x_host.cuda()
+    residual = torch.randn(1, o, generator=torch.Generator().manual_seed(4)).bfloat16().cuda()
+    groups = k // 128
+    buffers = [torch.zeros(world * o, 2, dtype=torch.int32, device="cuda") for _ in range(world)]  # 8-byte slots
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    scratch = torch.zeros(_native.w3_scratch_bytes(1, o, k), dtype=torch.uint8, device="cuda")
+    dummy = torch.empty(1, o, device="cuda", dtype=torch.bfloat16)
+    partial_reference = []
+    for rank in range(world):
+        lo, hi = rank * groups // world, (rank + 1) * groups // world
+        shard = {"planes": lg["planes"][lo:hi].contiguous(), "scales": lg["scales"][lo:hi].contiguous(), "zeros": lg["zeros"][lo:hi].contiguous()}
+        x_shard = x[:, lo * 128:hi * 128].contiguous()
+        matrix = _native.w3_matrix_list([(shard["planes"], shard["scales"], shard["zeros"], dummy, None)])
+        push = _native.w3_push_descriptor([buf.data_ptr() + 8 * rank * o for buf in buffers])
+        _native.w3_gemv_push(x_shard, 0, None, 0.0, matrix, (hi - lo) * 128, torch.float16, push, scratch=scratch)
+        own = torch.empty(1, o, device="cuda", dtype=torch.bfloat16)
+        _native.w3_gemv(x_shard, shard["planes"], shard["scales"], shard["zeros"], None, own, scratch=scratch)
+        partial_reference.append(own)
+    outs = []
+    for rank in range(world):
+        out = torch.full((1, o), float("nan"), device="cuda", dtype=torch.bfloat16)
+        _native.tp_reduce(buffers[rank].data_ptr(), world, residual, out, status.data_ptr())
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert torch.equal(outs[0], outs[1])  # every rank computes the same sum in the same order
+    assert all(int(buf.abs().sum()) == 0 for buf in buffers)  # slots cleared for the next use
+    reference, _ = oracle_outputs(layout, x_host)
+    assert_parity((outs[0].float() - residual.float()).bfloat16(), reference, tol=2e-2)
+    # against the two-kernel form with 16-bit partial results: the push keeps fp32 partials
+    two_step = ((partial_reference[0].float() + partial_reference[1].float()).bfloat16().float() + residual.float()).bfloat16()
+    assert float((outs[0].float() - two_step.float()).abs().max()) <= 2.0 ** -6 * float(two_step.float().abs().max())
