@@ -1,4 +1,4 @@
-"""Batch-1 Qwen3 decode engine on the packed W3 kernels: nine launches per layer, one CUDA graph.
+"""Batch-1 Qwen3 decode engine on the packed W3 kernels: five launches per layer, one CUDA graph.
 
 The reference drives an unmodified HF ``Qwen3ForCausalLM`` whose Linears were swapped
 (``static_decode.py:15-138``); that drop-in route is kept in ``static_decode.py`` here.  This
@@ -9,8 +9,9 @@ dependent launch and captured, for a whole continuation, in one CUDA graph.
 
 The same engine runs a BF16 arm (dense dequantised weights through cuBLAS, identical glue
 kernels), which is the same-box baseline the packed path is compared with, and shards itself
-tensor-parallel: q/k/v/gate/up by output rows, o/down by input groups, one NCCL sum-allreduce
-after each of the two row-split GEMVs of a layer.
+tensor-parallel: q/k/v/gate/up by output rows, o/down by input groups; after each of the two
+row-split GEMVs of a layer the packed arm pushes its rows into every rank's exchange buffer from
+the GEMV epilogue (``tp_push``), the BF16 arm runs an NCCL sum-allreduce.
 """
 from __future__ import annotations
 
