@@ -322,7 +322,7 @@ def run_binary_basis(torch, device):
     return table, total_us, total_bytes
 
 
-def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=("bf16", "w3"), repeats=5):
+def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=("bf16", "w3"), repeats=5, tp_push=None):
     """Full-model batch-1 decode (BASELINE.json configs[3] / [4]): random-init Qwen3 shape, all Linears
     W3 g128, LM head bf16; prefill `prompt` random ids, then `steps` tokens from ONE CUDA graph.  The
     BF16 arm runs the same engine with dense dequantised weights through cuBLAS.  Tensor parallel
@@ -335,7 +335,7 @@ def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=(
     out, forced, reference = {}, None, None
     for arm in arms:
         engine = DecodeEngine(shape, device=device, max_positions=prompt + steps + 8, arm=arm,
-                              tp_rank=rank, tp_size=world)
+                              tp_rank=rank, tp_size=world, tp_push=tp_push)
         first = engine.prefill(ids).argmax(-1)
         fed, greedy, logits = engine.decode(first, prompt, steps, forced=forced)
         engine.prefill(ids)
@@ -393,7 +393,8 @@ def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=(
         torch.distributed.barrier()
     if "w3" in out and "bf16" in out:
         out["w3_over_bf16"] = round(out["w3"]["tokens_per_s"] / out["bf16"]["tokens_per_s"], 3)
-    out["config"] = {"model": shape_name, "prompt_tokens": prompt, "decode_tokens": steps, "tensor_parallel": world,
+    exchange = "none" if world == 1 else ("nccl allreduce" if tp_push is False else "pushed from the GEMV epilogue into peer buffers (packed arm)")
+    out["config"] = {"model": shape_name, "prompt_tokens": prompt, "decode_tokens": steps, "tensor_parallel": world, "exchange": exchange,
                      "graph": "whole continuation, teacher-forced from the bf16 arm's greedy tokens"}
     return out
 
@@ -467,6 +468,8 @@ def main():
                         help="gemv (default): the seven Linear shapes plus the 8B decode; tp-decode-32b: tensor-parallel decode over --gpus ranks")
     parser.add_argument("--case", default=None, metavar="OxK",
                         help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
+    parser.add_argument("--tp-exchange", default="push", choices=("push", "nccl"),
+                        help="tp-decode-32b: exchange after the row-split GEMVs (fused push, or NCCL allreduce)")
     parser.add_argument("--copies", type=int, default=8)
     parser.add_argument("--rows", type=int, default=1, help="with --case: activation rows (above 1 runs the tensor-core kernel)")
     parser.add_argument("--headline-only", action="store_true",
@@ -506,7 +509,8 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if args.workload == "tp-decode-32b":
         torch.cuda.set_device(local_rank)
-        decode = run_decode(torch, "qwen3-32b", 1024, 64, rank, world, local_rank, arms=("w3",) if world > 1 else ("bf16", "w3"))
+        decode = run_decode(torch, "qwen3-32b", 1024, 64, rank, world, local_rank, arms=("w3",) if world > 1 else ("bf16", "w3"),
+                            tp_push=False if args.tp_exchange == "nccl" else None)
         if rank == 0:
             print(json.dumps({"metric": "batch-1 decode tokens/s, Qwen3-32B-shaped W3 g128, tensor parallel", "unit": "tokens/s",
                               "value": decode["w3"]["tokens_per_s"], "n_gpus": world, "higher_is_better": True, "scaling": "strong",
