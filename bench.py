@@ -468,6 +468,9 @@ def main():
                         help="gemv (default): the seven Linear shapes plus the 8B decode; tp-decode-32b: tensor-parallel decode over --gpus ranks")
     parser.add_argument("--case", default=None, metavar="OxK",
                         help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
+    parser.add_argument("--prompt-tokens", type=int, default=512, help="decode-8b: prompt length")
+    parser.add_argument("--decode-tokens", type=int, default=32, help="decode-8b: tokens decoded in the graph")
+    parser.add_argument("--packed-arm-only", action="store_true", help="decode-8b: skip the BF16 arm (for profiler launch lists)")
     parser.add_argument("--tp-exchange", default="push", choices=("push", "nccl"),
                         help="tp-decode-32b: exchange after the row-split GEMVs (fused push, or NCCL allreduce)")
     parser.add_argument("--copies", type=int, default=8)
@@ -518,6 +521,15 @@ def main():
         if world > 1:
             torch.distributed.barrier()
             torch.distributed.destroy_process_group()
+        return
+    if args.workload == "decode-8b":
+        torch.cuda.set_device(local_rank)
+        decode = run_decode(torch, "qwen3-8b", args.prompt_tokens, args.decode_tokens, 0, 1, local_rank,
+                            arms=("w3",) if args.packed_arm_only else ("bf16", "w3"))
+        if rank == 0:
+            print(json.dumps({"metric": "batch-1 decode tokens/s, Qwen3-8B random init, W3 g128 (configs[3])", "unit": "tokens/s",
+                              "value": decode["w3"]["tokens_per_s"], "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
+                              "dtype": "f32", "decode": decode}))
         return
     if args.workload == "binary-basis":
         torch.cuda.set_device(local_rank)
