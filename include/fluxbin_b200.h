@@ -52,7 +52,8 @@ typedef void* fb_stream_t; /* a cudaStream_t */
 /* Message describing the last rejected call made by this thread ("" if none). */
 const char* fb_last_error(void);
 
-/* Library / device facts: key "version", "sm_count", "max_smem", "w3_max_m".
+/* Library / device facts: key "version", "sm_count", "max_smem", "w3_max_m", "w3_mma_max_m",
+ * "w3_max_splits", "w3_ctas_per_sm", "w3_smem_bytes", "tp_max_world".
  *  Returns the value, or FB_EINVAL for an unknown key. */
 int64_t fb_query(const char* key);
 

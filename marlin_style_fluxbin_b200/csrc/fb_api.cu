@@ -58,7 +58,12 @@ extern "C" const char* fb_last_error(void) { return fb::g_error; }
 extern "C" int64_t fb_query(const char* key) {
   if (!key) return fb::fail(FB_EINVAL, "fb_query: null key");
   if (!strcmp(key, "version")) return 1;
-  if (!strcmp(key, "w3_max_m")) return 4;
+  if (!strcmp(key, "w3_max_m")) return 4;            // table-lookup kernel
+  if (!strcmp(key, "w3_mma_max_m")) return 16;       // tensor-core kernel
+  if (!strcmp(key, "w3_max_splits")) return 16;      // contributions combined per output
+  if (!strcmp(key, "w3_ctas_per_sm")) return 2;
+  if (!strcmp(key, "w3_smem_bytes")) return 32768 + 8 * 3 * 3072 + 8 * 3 * 8;  // M = 1: tables + per-warp rings + barriers
+  if (!strcmp(key, "tp_max_world")) return 8;
   if (!strcmp(key, "sm_count") || !strcmp(key, "max_smem")) {
     const fb::DeviceInfo* info = fb::device_info();
     if (!info) return FB_ECUDA;
