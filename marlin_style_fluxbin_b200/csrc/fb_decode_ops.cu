@@ -6,6 +6,8 @@
 // The reference leaves these steps to stock HF modules (static_decode.py:43-76); after the Linears
 // shrink by 5x they dominate the step, so each becomes one launch here.  All are launched with
 // programmatic dependent launch and let the next kernel start its prologue at once.
+#include <mutex>
+
 #include "fb_common.cuh"
 
 namespace {
@@ -113,7 +115,7 @@ __device__ __forceinline__ void norm_rope_head(const unsigned short* src, const 
 // FUSED: q arrives raw; the kernel norms and rotates q and the new k itself (every CTA of a head
 // repeats that small piece of work), takes the new token's k / v from shared memory instead of
 // the cache, and one CTA per k/v head writes them into the cache for the steps to come.
-template <bool FUSED>
+template <bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsigned short* __restrict__ q,
                                                                       unsigned short* __restrict__ k_cache,
                                                                       unsigned short* __restrict__ v_cache,
@@ -210,7 +212,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
   for (int i = 0; i < 4; ++i) sm_acc[warp][lane * 4 + i] = acc[i];
   __syncthreads();
+  // CLUSTER: the CTAs of one head form a thread-block cluster; every CTA stores its (output, max,
+  // sum) into the first CTA's shared memory and one cluster barrier hands them over, instead of
+  // a global scratch slot, a fence, a ticket and a round of loads.
+  __shared__ __align__(16) float cl_part[CLUSTER ? kAttnMaxSplits : 1][kAttnSlot];
   float* slot = scratch + ((size_t)head * kAttnMaxSplits + split) * kAttnSlot;
+  float my_m = -INFINITY, my_l = 0.f;
+  float4 part[kAttnMaxSplits];
   if (warp == 0) {
     float gm = -INFINITY;
 #pragma unroll
@@ -223,7 +231,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[i] += sm_acc[w][lane * 4 + i] * f;
     }
-    if (splits == 1) {  // nothing to merge: no scratch round trip
+    if (!CLUSTER && splits == 1) {  // nothing to merge: no scratch round trip
       const float inv1 = 1.f / total;
       uint2 direct;
       direct.x = (uint32_t)to_bits(o[0] * inv1, dtype) | ((uint32_t)to_bits(o[1] * inv1, dtype) << 16);
@@ -231,32 +239,53 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
       *reinterpret_cast<uint2*>(out + (size_t)head * D + lane * 4) = direct;
       return;
     }
+    if (CLUSTER) {
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&cl_part[split][0])), "r"(0));
+      asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + lane * 16), "f"(o[0]), "f"(o[1]), "f"(o[2]), "f"(o[3]) : "memory");
+      if (lane == 0) {
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 512), "f"(gm) : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 516), "f"(total) : "memory");
+      }
+    } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) slot[lane * 4 + i] = o[i];
-    if (lane == 0) {
-      slot[128] = gm;
-      slot[129] = total;
+      for (int i = 0; i < 4; ++i) slot[lane * 4 + i] = o[i];
+      if (lane == 0) {
+        slot[128] = gm;
+        slot[129] = total;
+      }
+      __threadfence();
+      __syncwarp();
+      unsigned prior = 0;
+      if (lane == 0) prior = atomicAdd(&tickets[head], 1u);
+      prior = __shfl_sync(0xffffffffu, prior, 0);
+      if (prior != (unsigned)splits - 1u) return;
+      __threadfence();
     }
-    __threadfence();
-    __syncwarp();
-    unsigned prior = 0;
-    if (lane == 0) prior = atomicAdd(&tickets[head], 1u);
-    prior = __shfl_sync(0xffffffffu, prior, 0);
-    if (prior != (unsigned)splits - 1u) return;
-    __threadfence();
-  } else {
+  } else if (!CLUSTER) {
     return;
   }
-  // Merge of the splits by one warp with every load in flight at once: lane sp fetches the
-  // (max, sum) of split sp, the rescaling factors come from shuffles, and each lane fetches its
-  // four output dims of all splits before the first use.  Sums run in ascending split order.
-  const float* base_slot = scratch + (size_t)head * kAttnMaxSplits * kAttnSlot;
-  const float my_m = lane < splits ? __ldcg(base_slot + lane * kAttnSlot + 128) : -INFINITY;
-  const float my_l = lane < splits ? __ldcg(base_slot + lane * kAttnSlot + 129) : 0.f;
-  float4 part[kAttnMaxSplits];
+  if (CLUSTER) {
+    // every thread of every CTA of the cluster arrives: release the stores above, acquire the others'
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (split != 0 || warp != 0) return;
+    my_m = lane < splits ? cl_part[lane][128] : -INFINITY;
+    my_l = lane < splits ? cl_part[lane][129] : 0.f;
 #pragma unroll
-  for (int sp = 0; sp < kAttnMaxSplits; ++sp)
-    part[sp] = sp < splits ? __ldcg(reinterpret_cast<const float4*>(base_slot + sp * kAttnSlot + lane * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = 0; sp < kAttnMaxSplits; ++sp)
+      part[sp] = sp < splits ? *reinterpret_cast<const float4*>(&cl_part[sp][lane * 4]) : make_float4(0.f, 0.f, 0.f, 0.f);
+  } else {
+    // Merge of the splits by one warp with every load in flight at once: lane sp fetches the
+    // (max, sum) of split sp, the rescaling factors come from shuffles, and each lane fetches its
+    // four output dims of all splits before the first use.  Sums run in ascending split order.
+    const float* base_slot = scratch + (size_t)head * kAttnMaxSplits * kAttnSlot;
+    my_m = lane < splits ? __ldcg(base_slot + lane * kAttnSlot + 128) : -INFINITY;
+    my_l = lane < splits ? __ldcg(base_slot + lane * kAttnSlot + 129) : 0.f;
+#pragma unroll
+    for (int sp = 0; sp < kAttnMaxSplits; ++sp)
+      part[sp] = sp < splits ? __ldcg(reinterpret_cast<const float4*>(base_slot + sp * kAttnSlot + lane * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   float gm = my_m;
 #pragma unroll
   for (int d = 16; d >= 1; d >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, d));
@@ -276,7 +305,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
   packed.x = (uint32_t)to_bits(o[0] * inv, dtype) | ((uint32_t)to_bits(o[1] * inv, dtype) << 16);
   packed.y = (uint32_t)to_bits(o[2] * inv, dtype) | ((uint32_t)to_bits(o[3] * inv, dtype) << 16);
   *reinterpret_cast<uint2*>(out + (size_t)head * D + lane * 4) = packed;
-  if (lane == 0) tickets[head] = 0u;
+  if (!CLUSTER && lane == 0) tickets[head] = 0u;
 }
 
 __global__ void silu_mul_kernel(const unsigned short* __restrict__ gate, const unsigned short* __restrict__ up,
@@ -341,6 +370,42 @@ int launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const 
   return FB_OK;
 }
 
+// Attention launch: with more than one split the CTAs of a head (grid.y of them) form one
+// thread-block cluster, which merges the splits in distributed shared memory.  Clusters of more
+// than 8 CTAs need the non-portable size attribute, set once per kernel and device.
+template <class Kernel, class... Args>
+int launch_attention(Kernel kernel, Kernel cluster_kernel, dim3 grid, cudaStream_t stream, const char* what, Args... args) {
+  if (grid.y == 1) return launch_pdl(kernel, grid, dim3(kAttnWarps * 32), stream, what, args...);
+  static std::mutex lock;
+  static bool ready[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    if (device >= 0 && device < 64 && !ready[device]) {
+      cudaError_t err = cudaFuncSetAttribute(cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(non-portable cluster size)");
+      ready[device] = true;
+    }
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(kAttnWarps * 32);
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = grid.y;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl_allowed() ? 2 : 1;
+  cudaError_t err = cudaLaunchKernelEx(&config, cluster_kernel, args...);
+  if (err != cudaSuccess) return cuda_fail(err, what);
+  return FB_OK;
+}
+
 inline const unsigned short* u16(const void* p) { return static_cast<const unsigned short*>(p); }
 inline unsigned short* u16(void* p) { return static_cast<unsigned short*>(p); }
 
@@ -380,7 +445,7 @@ extern "C" int fb_attn_decode(const void* q, const void* k_cache, const void* v_
   if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
   float* partial = static_cast<float*>(scratch);
   unsigned* tickets = reinterpret_cast<unsigned*>(partial + (size_t)q_heads * kAttnMaxSplits * kAttnSlot);
-  return launch_pdl(attn_decode_kernel<false>, dim3(q_heads, splits), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode launch",
+  return launch_attention(attn_decode_kernel<false, false>, attn_decode_kernel<false, true>, dim3(q_heads, splits), static_cast<cudaStream_t>(stream), "attn_decode launch",
                     u16(q), const_cast<unsigned short*>(u16(k_cache)), const_cast<unsigned short*>(u16(v_cache)), u16(out), partial, tickets,
                     q_heads, kv_heads, length, max_positions, scale, dtype, NewToken{});
 }
@@ -404,7 +469,7 @@ extern "C" int fb_attn_decode_fused(const void* q, const void* k, const void* v,
   float* partial = static_cast<float*>(scratch);
   unsigned* tickets = reinterpret_cast<unsigned*>(partial + (size_t)q_heads * kAttnMaxSplits * kAttnSlot);
   const NewToken nt = {u16(q), u16(k), u16(v), u16(q_weight), u16(k_weight), u16(cosv), u16(sinv), eps};
-  return launch_pdl(attn_decode_kernel<true>, dim3(q_heads, splits), dim3(kAttnWarps * 32), static_cast<cudaStream_t>(stream), "attn_decode_fused launch",
+  return launch_attention(attn_decode_kernel<true, false>, attn_decode_kernel<true, true>, dim3(q_heads, splits), static_cast<cudaStream_t>(stream), "attn_decode_fused launch",
                     static_cast<const unsigned short*>(nullptr), u16(k_cache), u16(v_cache), u16(out), partial, tickets, q_heads, kv_heads, length,
                     max_positions, scale, dtype, nt);
 }
