@@ -65,13 +65,15 @@ __global__ void qknorm_rope_cache_kernel(const unsigned short* __restrict__ q, c
 }
 
 // Single-query attention, split over the cached positions: grid (query heads, splits); a CTA
-// of 8 warps takes one contiguous chunk of positions, each warp four positions at a time (all
-// eight loads issued before any use) with an online softmax; the CTA's (max, sum, output) goes to
-// a scratch slot and the last CTA of a head (ticket) merges the splits in ascending order.
+// of 8 warps takes one contiguous chunk of positions, each warp ten positions at a time (all
+// their loads issued before any use) with an online softmax.  The CTAs of a head form a
+// thread-block cluster: each stores its (max, sum, output) into the first CTA's shared memory,
+// one cluster barrier later that CTA merges the splits in ascending order.  (The variant
+// without clusters keeps the scratch slots and the ticket; it runs when there is one split.)
 // head_dim 128: a lane holds four consecutive dims.
 constexpr int kAttnWarps = 8;
 constexpr int kAttnMaxSplits = 16;
-constexpr int kAttnBatch = 8;
+constexpr int kAttnBatch = 10;  // positions per warp with all their loads in flight: 80 per CTA and round
 constexpr int kAttnSlot = 132;  // 128 outputs + max + sum, padded
 
 __device__ __forceinline__ void unpack4(uint2 raw, int dtype, float* f) {
@@ -370,22 +372,39 @@ int launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const 
   return FB_OK;
 }
 
+// Up to 80 positions per CTA (one round of loads), the split count a power of two and at most 8:
+// the CTAs of a head form a thread-block cluster, and clusters beyond the portable size of 8
+// measured slower than the longer walk they would save.
+inline int attention_splits(int length) {
+  int splits = 1;
+  while (splits < 8 && splits * 80 < length) splits *= 2;
+  return splits;
+}
+
 // Attention launch: with more than one split the CTAs of a head (grid.y of them) form one
 // thread-block cluster, which merges the splits in distributed shared memory.  Clusters of more
 // than 8 CTAs need the non-portable size attribute, set once per kernel and device.
 template <class Kernel, class... Args>
 int launch_attention(Kernel kernel, Kernel cluster_kernel, dim3 grid, cudaStream_t stream, const char* what, Args... args) {
   if (grid.y == 1) return launch_pdl(kernel, grid, dim3(kAttnWarps * 32), stream, what, args...);
-  static std::mutex lock;
-  static bool ready[64] = {};
-  int device = 0;
-  cudaGetDevice(&device);
-  {
+  if (grid.y > 8) {  // per kernel and device; the two kernels share this function's instantiation
+    static std::mutex lock;
+    static const void* done[64][4] = {};
+    int device = 0;
+    cudaGetDevice(&device);
     std::lock_guard<std::mutex> guard(lock);
-    if (device >= 0 && device < 64 && !ready[device]) {
+    bool ready = false;
+    if (device >= 0 && device < 64)
+      for (const void* seen : done[device]) ready = ready || seen == reinterpret_cast<const void*>(cluster_kernel);
+    if (!ready) {
       cudaError_t err = cudaFuncSetAttribute(cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
       if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(non-portable cluster size)");
-      ready[device] = true;
+      if (device >= 0 && device < 64)
+        for (const void*& seen : done[device])
+          if (!seen) {
+            seen = reinterpret_cast<const void*>(cluster_kernel);
+            break;
+          }
     }
   }
   cudaLaunchConfig_t config = {};
@@ -441,8 +460,7 @@ extern "C" int fb_attn_decode(const void* q, const void* k_cache, const void* v_
   if (!aligned(q, 8) || !aligned(k_cache, 8) || !aligned(v_cache, 8) || !aligned(out, 8)) return fail(FB_EINVAL, "fb_attn_decode: tensors must be 8-byte aligned");
   const size_t need = fb_attn_decode_scratch_bytes(q_heads);
   if (!scratch || scratch_bytes < need || !aligned(scratch, 16)) return fail(FB_ESCRATCH, "fb_attn_decode: 16-byte aligned scratch of %zu bytes needed", need);
-  int splits = (length + 63) / 64;  // about 64 positions per CTA
-  if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
+  const int splits = attention_splits(length);
   float* partial = static_cast<float*>(scratch);
   unsigned* tickets = reinterpret_cast<unsigned*>(partial + (size_t)q_heads * kAttnMaxSplits * kAttnSlot);
   return launch_attention(attn_decode_kernel<false, false>, attn_decode_kernel<false, true>, dim3(q_heads, splits), static_cast<cudaStream_t>(stream), "attn_decode launch",
@@ -464,8 +482,7 @@ extern "C" int fb_attn_decode_fused(const void* q, const void* k, const void* v,
   const size_t need = fb_attn_decode_scratch_bytes(q_heads);
   if (!scratch || scratch_bytes < need || !aligned(scratch, 16)) return fail(FB_ESCRATCH, "fb_attn_decode_fused: 16-byte aligned scratch of %zu bytes needed", need);
   const int length = position + 1;
-  int splits = (length + 63) / 64;
-  if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
+  const int splits = attention_splits(length);
   float* partial = static_cast<float*>(scratch);
   unsigned* tickets = reinterpret_cast<unsigned*>(partial + (size_t)q_heads * kAttnMaxSplits * kAttnSlot);
   const NewToken nt = {u16(q), u16(k), u16(v), u16(q_weight), u16(k_weight), u16(cosv), u16(sinv), eps};
