@@ -232,8 +232,10 @@ int fb_rope_qk(const void* q, const void* k, const void* cosv, const void* sinv,
  *   and k (weights [D]), rotary embedding with cos/sin [D], rotated q to q_out, rotated k and v
  *   into k_cache / v_cache [kv_heads, max_positions, D] at `position`.
  * fb_attn_decode: softmax(q k^T * scale) v over cache positions 0..length-1, grouped-query heads,
- *   D = 128; out [q_heads, D].  Positions are split over CTAs; `scratch` (fb_attn_decode_scratch_bytes,
- *   zero-filled once, 16-byte aligned) holds the per-split partial results and one ticket per head.
+ *   D = 128; out [q_heads, D].  Positions are split over 1, 2, 4 or 8 CTAs per head, which form a
+ *   thread-block cluster and merge their partial results through distributed shared memory;
+ *   `scratch` (fb_attn_decode_scratch_bytes, zero-filled once, 16-byte aligned) is kept for the
+ *   variant without clusters (partial results and one ticket per head).
  * fb_silu_mul: out[i] = T(silu(gate[i])) * up[i].
  */
 int fb_qknorm_rope_cache(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,

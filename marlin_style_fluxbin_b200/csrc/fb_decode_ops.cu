@@ -136,6 +136,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
   const int chunk = (length + splits - 1) / splits;
   const int p0 = split * chunk, p1 = min(length, p0 + chunk);
   const int newest = length - 1;  // FUSED: the token being decoded, not in the cache yet
+  // a CTA's shared memory may be written by the others of its cluster only once it is running:
+  // every thread arrives here and waits just before the exchange, far from the critical path
+  if (CLUSTER) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   __shared__ __align__(8) unsigned short sm_new[3][D];  // rotated q, rotated k, v of the new token
   // A warp takes kAttnBatch positions at a time with all their loads in flight; the first batch
   // is requested before the q/k prologue so that the two round trips overlap.
@@ -218,6 +221,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
   // sum) into the first CTA's shared memory and one cluster barrier hands them over, instead of
   // a global scratch slot, a fence, a ticket and a round of loads.
   __shared__ __align__(16) float cl_part[CLUSTER ? kAttnMaxSplits : 1][kAttnSlot];
+  if (CLUSTER) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // all CTAs of the head have started
   float* slot = scratch + ((size_t)head * kAttnMaxSplits + split) * kAttnSlot;
   float my_m = -INFINITY, my_l = 0.f;
   float4 part[kAttnMaxSplits];
