@@ -152,17 +152,31 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
     }
     first_pass = false;
 
+    float sal_x = 0.f;
     // ---- 32 signed tables: lane = table (base = lane/16, chunk = lane%16), warp = 32 entries ----
     {
       const int base = lane >> 4, chunk = lane & 15;
       float v8[8];
+      {
+        // eight activations (and, with matrix-wide scales, eight fp16 column scales) in one 16-byte load each
+        const int k0 = g * 128 + chunk * 8;
+        const uint4 xr = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + k0);
+        const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w};
+        uint32_t cw[4] = {0u, 0u, 0u, 0u};
+        if (GLOBAL) {
+          const uint4 cr = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.gcol) + (size_t)base * p.K + k0);
+          cw[0] = cr.x, cw[1] = cr.y, cw[2] = cr.z, cw[3] = cr.w;
+        }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int kk = g * 128 + chunk * 8 + j;
-        const float xv = load_act(p.x, p.act_dtype, kk);
-        const float cv = GLOBAL ? __half2float(p.gcol[(size_t)base * p.K + kk]) : p.cols[(size_t)kk * 2 + base];
-        v8[j] = __fmul_rn(xv, cv);
+        for (int j = 0; j < 8; ++j) {
+          const float xv = bits_to_float((unsigned short)((xw[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+          const float cv = GLOBAL ? __half2float(__ushort_as_half((unsigned short)((cw[j >> 1] >> (16 * (j & 1))) & 0xffffu)))
+                                  : p.cols[(size_t)(k0 + j) * 2 + base];
+          v8[j] = __fmul_rn(xv, cv);
+        }
       }
+      // the salient input this group's contribution carries (matrix-wide scales): fetched once per group
+      if (GLOBAL && g < p.n_sal) sal_x = load_act(p.x, p.act_dtype, p.sal_idx[g]);
       // entry(p) = sum_b (bit b of p ? +v_b : -v_b) = low-nibble part + high-nibble part.  Warp w
       // owns the entries whose low nibble is 2w or 2w+1; the sixteen high-nibble parts come from
       // a tree (one add each), so an entry costs one add and one store.
@@ -210,6 +224,8 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
       float2 rs = make_float2(0.f, 0.f), srs = make_float2(0.f, 0.f);
       unsigned sp = 0;
       uint32_t g0bits = 0, g1bits = 0;
+      uint32_t sal_bits = 0;
+      if (GLOBAL && live && g < p.n_sal) asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sal_bits) : "l"(p.sal + (size_t)row * p.n_sal + g));
       if (GLOBAL && live) {
         asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(g0bits) : "l"(p.grow + row));
         asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(g1bits) : "l"(p.grow + (size_t)p.O + row));
@@ -292,7 +308,11 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
           value = __fmaf_rn(__half2float(__ushort_as_half((unsigned short)g0bits)), d0, 0.f);
           value = __fmaf_rn(__half2float(__ushort_as_half((unsigned short)g1bits)), d1, value);
           // the dense residual columns are dealt round-robin over the groups' contributions
-          for (int sidx = g; sidx < p.n_sal; sidx += p.G)
+          if (g < p.n_sal) {
+            asm volatile("" : "+r"(sal_bits));
+            value = __fmaf_rn(__uint_as_float(sal_bits << 16), sal_x, value);
+          }
+          for (int sidx = g + p.G; sidx < p.n_sal; sidx += p.G)  // more salient columns than groups: rare
             value = __fmaf_rn(__bfloat162float(p.sal[(size_t)row * p.n_sal + sidx]), load_act(p.x, p.act_dtype, p.sal_idx[sidx]), value);
         } else {
           const uint32_t p0 = INTERLEAVED ? compact_even(sp) : (sp & 0xffu);
