@@ -79,6 +79,10 @@ constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
 constexpr int kWarps = 8;
 constexpr int kCtasPerSm = 2;
 constexpr int kStages = 3;  // units staged ahead per warp (each warp owns a private ring)
+#ifndef FB_W3_EARLY_STAGES
+#define FB_W3_EARLY_STAGES 1
+#endif
+constexpr int kEarlyStages = FB_W3_EARLY_STAGES;  // of them, staged before the wait on the previous kernel
 constexpr int kMaxM = 4;
 constexpr int kMaxSplits = 16;  // partial sums per output (one arrival count of 6 bits, 52-bit fixed-point sum)
 
@@ -289,7 +293,10 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     }
   };
   FB_MARK(12);
-  for (int t = 0; t < kStages && t < my_tasks; ++t) issue_next();  // weights never change: no need to wait
+  // Weights never change, so staging needs no wait.  Only kEarlyStages units per warp go out before
+  // the wait on the previous kernel: the whole grid's requests are served in order, and the small
+  // activation loads that follow the wait must not queue behind 20 MB of weights.
+  for (int t = 0; t < kEarlyStages && t < my_tasks; ++t) issue_next();
   FB_MARK(1);
 
   // Everything below reads activations and writes scratch / outputs of this stream.
@@ -338,6 +345,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     inv_rms = rsqrtf(ss / (float)p.K + p.eps);
     __syncthreads();
   }
+  for (int t = kEarlyStages; t < kStages && t < my_tasks; ++t) issue_next();  // the rest of the ring, behind the activation loads
   auto round16 = [&](float v) { return p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v)); };
 
   // Split-K combine.  A contribution is ONE 64-bit atomic add: the partial sum in fixed point
