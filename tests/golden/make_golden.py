@@ -2,7 +2,7 @@
 Python code (its packing, layout, dequantisation and reference-math functions) on small
 seeded inputs.  Needs the reference tree; run it where that tree is mounted:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
 
 The fixtures are what pins the CPU oracle (and, through it, the CUDA kernels) to the
 reference's results.  Inputs follow the reference's own test recipes
@@ -15,7 +15,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) != 2:
+    sys.exit("usage: make_golden.py /path/to/reference")
+REFERENCE = Path(sys.argv[1])
 sys.path.insert(0, str(REFERENCE / "src"))
 sys.path.insert(0, str(REFERENCE / "tests"))
 
