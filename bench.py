@@ -419,6 +419,8 @@ def cpu_reference(steps: int, warmup: int):
 
     from oracle import oracle as orc
 
+    # all the host cores this process may use (torchrun exports OMP_NUM_THREADS=1 to its ranks)
+    orc.set_num_threads(len(os.sched_getaffinity(0)))
     rng = np.random.default_rng(20260916)
     layer = []
     t_dequant = 0.0

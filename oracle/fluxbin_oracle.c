@@ -83,6 +83,15 @@ int fbo_num_threads(void) {
 #endif
 }
 
+/* Thread count of the parallel loops (a launcher may have exported OMP_NUM_THREADS=1). */
+void fbo_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 void fbo_convert_to_f32(const uint16_t* src, int dtype, int64_t n, float* dst) {
   for (int64_t i = 0; i < n; ++i) dst[i] = half_to_f32(src[i], dtype);
 }

@@ -84,6 +84,11 @@ def num_threads() -> int:
     return int(lib().fbo_num_threads())
 
 
+def set_num_threads(count: int) -> None:
+    """Threads of the oracle's parallel loops; overrides an OMP_NUM_THREADS a launcher exported."""
+    lib().fbo_set_num_threads(ctypes.c_int(int(count)))
+
+
 # ----------------------------------------------------------------- GPTQ words
 def gptq_unpack_rows(qweight: np.ndarray) -> np.ndarray:
     words = _c(qweight, np.int32)
