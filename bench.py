@@ -581,8 +581,8 @@ def main():
             "pct_of_8TBps": round(100 * per_gpu / NOMINAL_HBM_GBS, 1),
             "linear_tokens_per_s": round(world * 1e3 / result["step_ms"], 1),
             "per_shape": result["per_shape"], "fused_launches": result["fused"], "m_sweep": result["m_sweep"], "clocks": result["clocks"],
-            "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": result["h2d"], "d2h_bytes_per_step": result["d2h"]},
-            "gpu_launches": result["launches"],
+            "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": result["h2d"] * world, "d2h_bytes_per_step": result["d2h"] * world},
+            "gpu_launches": result["launches"] * world,  # whole job: every rank launches the same graph
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(per_gpu / peak, 4), "traffic": None, "peak_kind": peak_kind,
                          "kernel": "w3_gemv_kernel<1,false>", "bytes_per_launch_avg": result["step_bytes"] // (LAYERS * len(SHAPES))},
