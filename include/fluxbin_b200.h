@@ -37,7 +37,12 @@ extern "C" {
 #define FB_W3_DECODED_BF16 1u /* add the +/-3 weight-rounding correction: the result then
                                  follows the dequantised 16-bit weight rather than
                                  scale * integer-dot (reference: "decoded_bf16" arithmetic,
-                                 csrc/w3_lut.cu:105-122).  Needs zero point 4 (zeros == NULL). */
+                                 csrc/w3_lut.cu:105-122).  The dequantised weight is
+                                 scale * (code - zero) rounded once in the scale's dtype.  Exact
+                                 for zero points 3 and 4 (zeros == NULL is 4), where +/-3 are the
+                                 only inexact products; other zero points get that correction
+                                 only.  Zero points are then read before the lookups, which
+                                 costs some speed. */
 
 #define FB_W3_NO_PDL 2u /* launch without programmatic dependent launch (by default the
                           kernel's prologue may overlap the previous kernel in the stream;
@@ -144,11 +149,13 @@ int fb_w3_gemv_push(const void* x, int act_dtype, int transform, const void* ope
  * out[i] = T(T(sum_r value(parts[r*n + i])) + residual[i]) for i < n: the receiving half of
  * fb_w3_gemv_push.  `parts` is this rank's exchange buffer, [world, n] 8-byte slots, all zero
  * before the first use; a thread waits until the slots of its element carry the mark, sums them
- * in ascending rank order and zeroes them again.  The wait is bounded (about ten seconds; on
- * expiry *status is set to 4 and the sum is of whatever arrived).  residual may be NULL.
+ * in ascending rank order and zeroes them again.  The wait is bounded by wait_ns nanoseconds
+ * (0 = the default of ten seconds, at most 60 s); on expiry *status is set to 4, the sum is of
+ * whatever arrived and the slots are zeroed all the same.  The host reads *status after
+ * synchronising; a non-zero value means the outputs of that step are invalid.  residual may be NULL.
  */
 int fb_tp_reduce(void* parts, int world, const void* residual, void* out, int n, int dtype, unsigned* status,
-                 fb_stream_t stream);
+                 uint64_t wait_ns, fb_stream_t stream);
 
 /*
  * Small-batch form on the tensor cores: y[M,O] = x[M,K] . W^T for M = 1..16, same layout and

@@ -79,7 +79,7 @@ def library() -> ctypes.CDLL:
                                         ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p]
         lib.fb_tp_reduce.restype = ctypes.c_int
         lib.fb_tp_reduce.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
-                                     ctypes.c_void_p, ctypes.c_void_p]
+                                     ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]
         lib.fb_w3_finish.restype = ctypes.c_int
         lib.fb_w3_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.fb_bb_gemv_scratch_bytes.restype = ctypes.c_size_t
@@ -368,8 +368,11 @@ def w3_gemv_push(x, transform: int, operand, eps: float, matrix, k: int, scale_d
                                         0 if pdl else FB_W3_NO_PDL, stream_handle(x.device)))
 
 
-def tp_reduce(parts_ptr: int, world: int, residual, out, status_ptr: int) -> None:
-    """Receiving half of the push: polls every rank's slots, sums their rows, adds the residual."""
+def tp_reduce(parts_ptr: int, world: int, residual, out, status_ptr: int, wait_ns: int = 0) -> None:
+    """Receiving half of the push: polls every rank's slots, sums their rows, adds the residual.
+
+    ``wait_ns`` bounds the poll (0 = the library default of ten seconds); on expiry the status word
+    becomes 4 and the kernel returns."""
     with torch.cuda.device(out.device):
         check(library().fb_tp_reduce(ctypes.c_void_p(parts_ptr), world, ptr(residual), ptr(out), out.numel(), dtype_tag(out.dtype),
-                                     ctypes.c_void_p(status_ptr), stream_handle(out.device)))
+                                     ctypes.c_void_p(status_ptr), int(wait_ns), stream_handle(out.device)))

@@ -3,7 +3,10 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <cudaTypedefs.h>
+
 #include <mutex>
+#include <unordered_map>
 
 #include "fb_common.cuh"
 
@@ -51,6 +54,55 @@ const DeviceInfo* device_info() {
   return &table[device];
 }
 
+bool plane_tensor_map(const uint8_t* planes, int O, int G, int box_units, int box_runs, CUtensorMap* out) {
+  static std::mutex lock;
+  static PFN_cuTensorMapEncodeTiled encode = nullptr;
+  struct Key {
+    const void* ptr;
+    int O, G, box;
+    bool operator==(const Key& other) const { return ptr == other.ptr && O == other.O && G == other.G && box == other.box; }
+  };
+  struct Hash {
+    size_t operator()(const Key& key) const {
+      return std::hash<const void*>()(key.ptr) ^ ((size_t)key.O * 1315423911u) ^ ((size_t)key.G << 40) ^ ((size_t)key.box << 52);
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  std::lock_guard<std::mutex> guard(lock);
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+    if (err != cudaSuccess || status != cudaDriverEntryPointSuccess || !fn) {
+      cuda_fail(err, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+      return false;
+    }
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+  }
+  const Key key{planes, O, G, box_units * 256 + box_runs};
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return true;
+  }
+  const cuuint64_t dims[3] = {128, (cuuint64_t)(O / 32), (cuuint64_t)G * 3};
+  const cuuint64_t strides[2] = {512, (cuuint64_t)O * 16};  // bytes, dims 1 and 2
+  const cuuint32_t box[3] = {128, (cuuint32_t)box_units, (cuuint32_t)box_runs};
+  const cuuint32_t step[3] = {1, 1, 1};
+  CUtensorMap map;
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(planes), dims, strides, box, step,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    fail(FB_ECUDA, "cuTensorMapEncodeTiled failed with code %d for planes [%d,3,%d,16]", (int)rc, G, O);
+    return false;
+  }
+  if (cache.size() >= 8192) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return true;
+}
+
 }  // namespace fb
 
 extern "C" const char* fb_last_error(void) { return fb::g_error; }
@@ -61,8 +113,8 @@ extern "C" int64_t fb_query(const char* key) {
   if (!strcmp(key, "w3_max_m")) return 4;            // table-lookup kernel
   if (!strcmp(key, "w3_mma_max_m")) return 16;       // tensor-core kernel
   if (!strcmp(key, "w3_max_splits")) return 16;      // contributions combined per output
-  if (!strcmp(key, "w3_ctas_per_sm")) return 2;
-  if (!strcmp(key, "w3_smem_bytes")) return 32768 + 8 * 3 * 3072 + 8 * 3 * 8;  // M = 1: tables + per-warp rings + barriers
+  if (!strcmp(key, "w3_ctas_per_sm")) return 1;
+  if (!strcmp(key, "w3_smem_bytes")) return 2 * 32768 + 16 * 3 * 3072 + 16 * 3 * 8;  // M = 1: two table sets + per-warp rings + barriers
   if (!strcmp(key, "tp_max_world")) return 8;
   if (!strcmp(key, "sm_count") || !strcmp(key, "max_smem")) {
     const fb::DeviceInfo* info = fb::device_info();

@@ -2,6 +2,7 @@
 // conversion, and thin wrappers over the PTX used for bulk asynchronous copies
 // (cp.async.bulk + mbarrier).  Every device-side wait is bounded.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -27,6 +28,31 @@ const DeviceInfo* device_info();
 // environment variable FB_NO_PDL (read once); used to tell launch-overlap effects apart.
 bool pdl_allowed();
 
+// Tiled-copy descriptor of a W3 planes tensor [G,3,O,16] seen as uint32 [G*3][O/32][128] (a
+// 512-byte run per 32 rows, plane and group); one box is `box_runs` (group, plane) runs of
+// `box_units` 32-row units.  Encoding is pure host work; descriptors are cached per
+// (address, O, G, box).  Returns false after recording the error.
+bool plane_tensor_map(const uint8_t* planes, int O, int G, int box_units, int box_runs, CUtensorMap* out);
+
+// Launch with the programmatic-dependent-launch attribute (unless switched off): the kernel's
+// prologue may overlap the tail of the previous kernel in the stream.
+template <class Kernel, class... Args>
+int launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const char* what, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl_allowed() ? 1 : 0;
+  cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
+  if (err != cudaSuccess) return cuda_fail(err, what);
+  return FB_OK;
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline bool overlaps(const void* a, size_t na, const void* b, size_t nb) {
   auto pa = reinterpret_cast<uintptr_t>(a), pb = reinterpret_cast<uintptr_t>(b);
@@ -43,6 +69,12 @@ __device__ __forceinline__ float load_act(const void* base, int dtype, int index
 __device__ __forceinline__ float bits_to_float(unsigned short bits, int dtype) {
   if (dtype == FB_BF16) return __uint_as_float(static_cast<unsigned>(bits) << 16);
   return __half2float(__ushort_as_half(bits));
+}
+
+// v rounded to the 16-bit dtype and widened again
+__device__ __forceinline__ float round_to(float v, int dtype) {
+  if (dtype == FB_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  return __half2float(__float2half_rn(v));
 }
 
 __device__ __forceinline__ void store_act(void* base, int dtype, int index, float value) {

@@ -14,9 +14,6 @@ namespace {
 
 using namespace fb;
 
-__device__ __forceinline__ float round_to(float v, int dtype) {
-  return dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
-}
 __device__ __forceinline__ unsigned short to_bits(float v, int dtype) {
   return dtype == FB_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
 }
@@ -325,14 +322,17 @@ __global__ void silu_mul_kernel(const unsigned short* __restrict__ gate, const u
   out[i] = to_bits(s * bits_to_float(up[i], dtype), dtype);
 }
 
-// Receiving half of the tensor-parallel push: every rank's GEMV stores (fp32 value, mark = 1)
-// pairs, one 8-byte store each, into this rank's exchange buffer [world][n].  A thread polls the
-// `world` slots of its element until all carry the mark (bounded), sums the values in ascending
-// rank order (the same on every rank), and clears the slots for the next use: no fence, no
-// counter, no collective call.  A rank cannot write a slot again before it has received this
-// rank's NEXT contribution, which this rank sends only after this kernel: the clear is safe.
-__global__ void tp_reduce_kernel(uint2* parts, int world, const unsigned short* __restrict__ residual, unsigned short* __restrict__ out,
-                                 int n, int dtype, unsigned* status) {
+// Receiving half of the tensor-parallel push: every rank's GEMV stores {fp32 value, mark = 1} as
+// ONE 64-bit store into this rank's exchange buffer [world][n] (a scalar 8-byte access is
+// single-copy atomic, so the mark never becomes visible without its value).  A thread polls the
+// `world` slots of its element until all carry the mark (bounded by `wait_ns`), sums the values
+// in ascending rank order (the same on every rank), and clears the slots for the next use: no
+// fence, no counter, no collective call.  A rank cannot write a slot again before it has received
+// this rank's NEXT contribution, which this rank sends only after this kernel: the clear is safe.
+// On expiry the status word is set to 4; the slots are cleared all the same, so the buffer is
+// clean for the next use once the late stores (if any) have been dealt with by the host.
+__global__ void tp_reduce_kernel(unsigned long long* parts, int world, const unsigned short* __restrict__ residual,
+                                 unsigned short* __restrict__ out, int n, int dtype, unsigned* status, unsigned long long wait_ns) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -341,39 +341,23 @@ __global__ void tp_reduce_kernel(uint2* parts, int world, const unsigned short* 
   float total = 0.f;
   bool expired = false;
   for (int r = 0; r < world; ++r) {
-    uint2* slot = parts + (size_t)r * n + i;
-    uint2 got;
+    unsigned long long* slot = parts + (size_t)r * n + i;
+    unsigned long long got;
     for (;;) {
-      asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(got.x), "=r"(got.y) : "l"(slot) : "memory");
-      if (got.y == 1u) break;
-      if (global_timer_ns() - start > 10000000000ull) {  // ten seconds: ranks may be skewed by host work
+      asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(got) : "l"(slot) : "memory");
+      if ((unsigned)(got >> 32) == 1u) break;
+      if (expired || global_timer_ns() - start > wait_ns) {
         expired = true;
         break;
       }
     }
-    total += __uint_as_float(got.x);
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %1};" ::"l"(slot), "r"(0u) : "memory");
+    total += __uint_as_float((unsigned)got);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(slot), "l"(0ull) : "memory");
   }
   if (expired) atomicExch(status, 4u);
   float value = round_to(total, dtype);
   if (residual) value += bits_to_float(residual[i], dtype);
   out[i] = to_bits(value, dtype);
-}
-
-template <class Kernel, class... Args>
-int launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const char* what, Args... args) {
-  cudaLaunchConfig_t config = {};
-  config.gridDim = grid;
-  config.blockDim = block;
-  config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = attr;
-  config.numAttrs = pdl_allowed() ? 1 : 0;
-  cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
-  if (err != cudaSuccess) return cuda_fail(err, what);
-  return FB_OK;
 }
 
 // Up to 80 positions per CTA (one round of loads), the split count a power of two and at most 8:
@@ -390,7 +374,7 @@ inline int attention_splits(int length) {
 // than 8 CTAs need the non-portable size attribute, set once per kernel and device.
 template <class Kernel, class... Args>
 int launch_attention(Kernel kernel, Kernel cluster_kernel, dim3 grid, cudaStream_t stream, const char* what, Args... args) {
-  if (grid.y == 1) return launch_pdl(kernel, grid, dim3(kAttnWarps * 32), stream, what, args...);
+  if (grid.y == 1) return launch_pdl(kernel, grid, dim3(kAttnWarps * 32), 0, stream, what, args...);
   if (grid.y > 8) {  // per kernel and device; the two kernels share this function's instantiation
     static std::mutex lock;
     static const void* done[64][4] = {};
@@ -443,7 +427,7 @@ extern "C" int fb_qknorm_rope_cache(const void* q, const void* k, const void* v,
   if (q_heads < 1 || kv_heads < 1 || head_dim < 2 || head_dim % 2 || head_dim > 1024) return fail(FB_ELIMIT, "fb_qknorm_rope_cache: head geometry outside bounds");
   if (position < 0 || position >= max_positions) return fail(FB_ELIMIT, "fb_qknorm_rope_cache: position %d outside the cache of %d", position, max_positions);
   const int heads = q_heads + 2 * kv_heads;
-  return launch_pdl(qknorm_rope_cache_kernel, dim3((heads + 3) / 4), dim3(128), static_cast<cudaStream_t>(stream), "qknorm_rope_cache launch",
+  return launch_pdl(qknorm_rope_cache_kernel, dim3((heads + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream), "qknorm_rope_cache launch",
                     u16(q), u16(k), u16(v), u16(q_weight), u16(k_weight), u16(cosv), u16(sinv), u16(q_out), u16(k_cache), u16(v_cache),
                     q_heads, kv_heads, head_dim, position, max_positions, eps, dtype);
 }
@@ -499,16 +483,18 @@ extern "C" int fb_silu_mul(const void* gate, const void* up, void* out, int n, i
   if (!gate || !up || !out) return fail(FB_EINVAL, "fb_silu_mul: null pointer");
   if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_silu_mul: dtype must be FB_F16 or FB_BF16");
   if (n < 1) return fail(FB_ELIMIT, "fb_silu_mul: n must be positive");
-  return launch_pdl(silu_mul_kernel, dim3((n + 255) / 256), dim3(256), static_cast<cudaStream_t>(stream), "silu_mul launch",
+  return launch_pdl(silu_mul_kernel, dim3((n + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), "silu_mul launch",
                     u16(gate), u16(up), u16(out), n, dtype);
 }
 
 extern "C" int fb_tp_reduce(void* parts, int world, const void* residual, void* out, int n, int dtype, unsigned* status,
-                            fb_stream_t stream) {
+                            uint64_t wait_ns, fb_stream_t stream) {
   if (!parts || !out || !status) return fail(FB_EINVAL, "fb_tp_reduce: null pointer");
   if (!aligned(parts, 8)) return fail(FB_EINVAL, "fb_tp_reduce: the exchange buffer must be 8-byte aligned");
   if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_tp_reduce: dtype must be FB_F16 or FB_BF16");
   if (world < 1 || world > 8 || n < 1) return fail(FB_ELIMIT, "fb_tp_reduce: world 1..8 and n >= 1");
-  return launch_pdl(tp_reduce_kernel, dim3((n + 127) / 128), dim3(128), static_cast<cudaStream_t>(stream), "tp_reduce launch",
-                    static_cast<uint2*>(parts), world, u16(residual), u16(out), n, dtype, status);
+  if (wait_ns > 60000000000ull) return fail(FB_ELIMIT, "fb_tp_reduce: wait limit above 60 s");
+  const unsigned long long limit = wait_ns ? wait_ns : 10000000000ull;  // default ten seconds: ranks may be skewed by host work
+  return launch_pdl(tp_reduce_kernel, dim3((n + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), "tp_reduce launch",
+                    static_cast<unsigned long long*>(parts), world, u16(residual), u16(out), n, dtype, status, limit);
 }

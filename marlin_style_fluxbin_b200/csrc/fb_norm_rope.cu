@@ -12,10 +12,6 @@ namespace {
 
 using namespace fb;
 
-__device__ __forceinline__ float round_to(float v, int dtype) {
-  return dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
-}
-
 // One warp per row when LANES == 32, one 256-thread CTA per row otherwise.
 template <int LANES>
 __global__ void rmsnorm_kernel(const unsigned short* __restrict__ x, const unsigned short* __restrict__ weight,
@@ -72,22 +68,6 @@ __global__ void rope_kernel(const unsigned short* __restrict__ q, const unsigned
   dst[i + half] = dtype == FB_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y1)) : __half_as_ushort(__float2half_rn(y1));
 }
 
-template <class Kernel, class... Args>
-int launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const char* what, Args... args) {
-  cudaLaunchConfig_t config = {};
-  config.gridDim = grid;
-  config.blockDim = block;
-  config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = attr;
-  config.numAttrs = pdl_allowed() ? 1 : 0;
-  cudaError_t err = cudaLaunchKernelEx(&config, kernel, args...);
-  if (err != cudaSuccess) return cuda_fail(err, what);
-  return FB_OK;
-}
-
 }  // namespace
 
 extern "C" int fb_rmsnorm(const void* x, const void* weight, void* out, int rows, int dim, float eps, int dtype,
@@ -102,10 +82,10 @@ extern "C" int fb_rmsnorm(const void* x, const void* weight, void* out, int rows
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dim <= 512) {
     const int rows_per_block = 4;
-    return launch_pdl(rmsnorm_kernel<32>, dim3((rows + rows_per_block - 1) / rows_per_block), dim3(32 * rows_per_block), s,
+    return launch_pdl(rmsnorm_kernel<32>, dim3((rows + rows_per_block - 1) / rows_per_block), dim3(32 * rows_per_block), 0, s,
                       "rmsnorm_kernel launch", xs, ws, os, rows, dim, eps, dtype);
   }
-  return launch_pdl(rmsnorm_kernel<256>, dim3(rows), dim3(256), s, "rmsnorm_kernel launch", xs, ws, os, rows, dim, eps, dtype);
+  return launch_pdl(rmsnorm_kernel<256>, dim3(rows), dim3(256), 0, s, "rmsnorm_kernel launch", xs, ws, os, rows, dim, eps, dtype);
 }
 
 extern "C" int fb_rope_qk(const void* q, const void* k, const void* cosv, const void* sinv, void* q_out, void* k_out,
@@ -115,7 +95,7 @@ extern "C" int fb_rope_qk(const void* q, const void* k, const void* cosv, const 
   if (q_heads < 0 || k_heads < 0 || q_heads + k_heads < 1 || q_heads + k_heads > 65536 || head_dim < 2 || head_dim % 2 || head_dim > 1024)
     return fail(FB_ELIMIT, "fb_rope_qk: heads=%d+%d head_dim=%d outside bounds", q_heads, k_heads, head_dim);
   const int work = (q_heads + k_heads) * (head_dim / 2);
-  return launch_pdl(rope_kernel, dim3((work + 127) / 128), dim3(128), static_cast<cudaStream_t>(stream), "rope_kernel launch",
+  return launch_pdl(rope_kernel, dim3((work + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), "rope_kernel launch",
                     static_cast<const unsigned short*>(q), static_cast<const unsigned short*>(k),
                     static_cast<const unsigned short*>(cosv), static_cast<const unsigned short*>(sinv),
                     static_cast<unsigned short*>(q_out), static_cast<unsigned short*>(k_out), q_heads, k_heads, head_dim, dtype);

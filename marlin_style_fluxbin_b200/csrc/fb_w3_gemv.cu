@@ -13,16 +13,21 @@
 //    construction, whatever the weights are.  The same rotation makes the reads of the
 //    staged weight words conflict free.
 //  * The three bit planes of a unit (6 runs of 512 bytes: group half x plane) are staged into
-//    shared memory with bulk asynchronous copies (cp.async.bulk + mbarrier), six lanes issuing
-//    one run each in the same instruction.  Every warp owns a private ring of three staged
-//    units and refills a slot as soon as it has read it, so warps never wait for one another
-//    between table builds; scales and zero points come straight from global memory, requested
-//    before the lookups and used after them.
-//  * Two CTAs per SM: each K block is served by floor(2 SMs / K blocks) CTAs that split its rows.
-//  * Launched with programmatic dependent launch: a kernel's prologue and first weight
-//    copies overlap the tail of the previous kernel in the stream; everything that
-//    reads activations or touches scratch comes after griddepcontrol.wait.  A CTA stays
-//    near 104 KB of shared memory (M = 1) so that two can be resident on an SM.
+//    shared memory by ONE tiled bulk copy (cp.async.bulk.tensor + mbarrier).  Every warp owns a
+//    private ring of staged units and refills a slot as soon as it has read it, so warps never
+//    wait for one another between table builds; scales and zero points come straight from
+//    global memory, requested before the lookups and used after them.
+//  * One CTA of 16 warps per SM (the whole register file): each K super-block is served by
+//    floor(SMs / super-blocks) CTAs that split its rows, so the 32 KB of tables of a K block are
+//    built once per SM and shared by 16 warps.
+//  * A CTA that walks several K blocks (K > 4096) keeps two table sets (M = 1): the tables of
+//    the next K block are built while the current block's lookups run, one barrier per block.
+//    A warp whose rows are a single unit carries its sum across the K blocks in registers.
+//  * Two lookups are added with one packed fp32x2 add (an even-step and an odd-step partial sum
+//    per plane share a 64-bit register pair), which halves the adds of the main loop.
+//  * Launched with programmatic dependent launch: barrier set-up and the first weight copies
+//    come before griddepcontrol.wait; everything that reads activations or touches scratch
+//    comes after it.
 //  * Split-K is combined inside the kernel with ONE 64-bit atomic add per contribution: the
 //    partial sum in fixed point (2^-26 units) plus an arrival count in the low bits.  Integer
 //    addition is associative, so the result is independent of arrival order (deterministic,
@@ -33,39 +38,11 @@
 // dot = a0 + 2*a1 - 4*a2 over the stored planes (plane 2 inverted), times the group
 // scale, fp32 accumulation; tables hold ascending-order subset sums as in
 // csrc/lut8_unsigned.cuh:12-27.  Extension over the reference: fp16 or bf16 scales and
-// an optional per-(group,row) zero point, y += scale*(4-zero)*sum(x_group).
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
+// an optional per-(group,row) zero point, y += scale*(4-zero)*sum(x_group); the rounding
+// correction of the dequantised-weight arithmetic (csrc/w3_lut.cu:105-122) is extended to zero
+// points 3 and 4, the two for which +/-3 are the only inexact products.
 #include <mutex>
-#include <unordered_map>
-
-#ifndef FB_W3_TRACE
-#define FB_W3_TRACE 0
-#endif
-#if FB_W3_TRACE
-#define FB_CTA (blockIdx.y * gridDim.x + blockIdx.x)
-#define FB_MARK(i)                                                                                   \
-  do {                                                                                               \
-    if (threadIdx.x == 0 && FB_CTA == 0) reinterpret_cast<long long*>(p.status)[8 + (i)] = clock64(); \
-    if (threadIdx.x == 0 && ((i) == 0 || (i) == 8))                                                  \
-      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.status) + (3 << 20))[FB_CTA * 2 + ((i) == 8)] = fb::global_timer_ns(); \
-    if (threadIdx.x == 0 && (i) == 0) { unsigned smid_; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));  \
-      reinterpret_cast<unsigned*>(reinterpret_cast<char*>(p.status) + (3 << 20) + 65536)[FB_CTA] = smid_; } \
-  } while (0)
-#define FB_WAVE_MARK(w, which)                                                                         \
-  do {                                                                                               \
-    if (lane == 0 && (warp == 0 || warp == 7) && (w) < 8)                                            \
-      reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((FB_CTA * 2 + (warp == 7)) * 8 + (w)) * 8 + (which)] = clock64(); \
-  } while (0)
-#else
-#define FB_MARK(i) \
-  do {             \
-  } while (0)
-#define FB_WAVE_MARK(w, which) \
-  do {                         \
-  } while (0)
-#endif
+#include <type_traits>
 
 #include "fb_common.cuh"
 
@@ -74,18 +51,11 @@ namespace {
 using namespace fb;
 
 constexpr int kUnitRows = 32;
-constexpr int kPlaneTile = kUnitRows * 16;  // 512 B: one plane of one group for a unit
+constexpr int kPlaneTile = kUnitRows * 16;      // 512 B: one plane of one group for a unit
 constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
-constexpr int kWarps = 8;
-constexpr int kCtasPerSm = 2;
-constexpr int kStages = 3;  // units staged ahead per warp (each warp owns a private ring)
-#ifndef FB_W3_EARLY_STAGES
-#define FB_W3_EARLY_STAGES 1
-#endif
-constexpr int kEarlyStages = FB_W3_EARLY_STAGES;  // of them, staged before the wait on the previous kernel
+constexpr int kWarps = 16;
 constexpr int kMaxM = 4;
 constexpr int kMaxSplits = 16;  // partial sums per output (one arrival count of 6 bits, 52-bit fixed-point sum)
-
 constexpr int kMaxMatrices = 4;
 
 // One weight matrix of a launch.  Several matrices that share x and K (q/k/v, gate/up) are
@@ -115,7 +85,7 @@ struct W3Params {
   // row goes, together with a valid mark in the same 8-byte store, to slot `row` of a buffer on
   // every rank (peer pointers over NVLink, this rank's own buffer included).  No fence and no
   // counter: the receiver polls each slot for its mark.
-  uint2* push_data[8];
+  unsigned long long* push_data[8];
   int push_world;  // 0 = no push
   float* partials;  // [nSB, M, O]
   unsigned long long* combine;  // [M, O] split-K accumulators, zero between launches
@@ -123,60 +93,81 @@ struct W3Params {
   int O, K, G, nKB, nRU;
   int act_dtype, scale_dtype;
   int S, nSB;          // K blocks per super-block (one CTA walks them in turn), super-blocks
-  int ctas_per_kb;     // row slices per super-block
   int units_per_slice, units_extra;  // nRU / slices and nRU % slices
   int group_partials;  // write scale-multiplied per-group sums instead of reducing
 };
 
-// Table geometry: entry p of table t for activation row m lives at byte
+// Shared-memory geometry.  Entry p of table t for activation row m lives at byte
 //   p * kStride + m * 128 + t * 4,   kStride = 128 * (M rounded up to a power of two),
 // so with M = 1 the 32 tables of a K block take 32 KB and the bank of a lookup is the table
-// number.  A lookup address is a rotate of the staged weight word (which brings the weight
-// byte to the entry field) and one logic op that masks it and merges the lane's table offset.
+// number.  M = 1 keeps two table sets (the next K block's are built during this block's
+// lookups); the ring holds three staged units per warp, two when the tables take 128 KB.
 template <int M>
-struct LutGeom {
+struct Geom {
   static constexpr int kStrideLog = 7 + (M == 1 ? 0 : (M == 2 ? 1 : 2));
   static constexpr int kStride = 1 << kStrideLog;
-  static constexpr int kBytes = 256 << kStrideLog;
+  static constexpr int kLutBytes = 256 << kStrideLog;
+  static constexpr int kLutSets = M == 1 ? 2 : 1;
+  static constexpr int kStages = M <= 2 ? 3 : 2;
+  static constexpr int kRingOffset = kLutSets * kLutBytes;
+  static constexpr int kBarOffset = kRingOffset + kWarps * kStages * kUnitBytes;
+  static constexpr int kSmemBytes = kBarOffset + kWarps * kStages * 8;
 };
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Two fp32 values in one 64-bit register pair, added lane-wise by one instruction.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// Shared-memory load at a 32-bit address plus a compile-time offset (folded into the instruction).
+template <int OFFSET>
+__device__ __forceinline__ float lds_at(uint32_t address) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(address), "n"(OFFSET));
+  return v;
+}
+__device__ __forceinline__ float sum2(uint64_t v) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+  return lo + hi;
+}
+
 template <int M, bool CORRECT>
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const __grid_constant__ W3Params p) {
+__global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_constant__ W3Params p) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  using Geom = LutGeom<M>;
+  using G_ = Geom<M>;
+  constexpr int kStages = G_::kStages;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* const lut = smem;
   // Every warp owns a private ring of kStages staged units, [stage][group half * 3 + plane][32 rows
   // x 16 B], and one mbarrier per stage: warps never wait for one another between table builds.
-  unsigned char* const ring = smem + Geom::kBytes;
-  uint64_t* const full_bars = reinterpret_cast<uint64_t*>(smem + Geom::kBytes + (size_t)kWarps * kStages * kUnitBytes);
+  unsigned char* const ring = smem + G_::kRingOffset;
+  uint64_t* const full_bars = reinterpret_cast<uint64_t*>(smem + G_::kBarOffset);
 
-  FB_MARK(0);
-  // The next kernel in the stream may start its own prologue (weight prefetch) now; it
-  // orders itself after this grid with its own wait before touching activations or scratch.
+  // The next kernel in the stream may be scheduled as soon as this grid's CTAs leave; it orders
+  // itself after this grid with its own wait before touching activations or scratch.
   pdl_launch_dependents();
-  FB_MARK(10);
-
 
   if (threadIdx.x < kWarps * kStages) {
     mbar_init(smem_u32(&full_bars[threadIdx.x]), 1);  // the issuing lane's expect_tx
     mbar_init_fence();
   }
   __syncthreads();
-  FB_MARK(11);
 
-  // Work of CTA v: super-block v / c (K blocks sb*S ..), the row units [first, first + count) of slice v % c.
-  // The grid is (row slices, super-blocks); the first nRU % c slices take one unit more.  No
-  // division on the device: the quotient and remainder come with the parameters.
-  auto share = [&](int& sb, int& first, int& count) {
-    sb = (int)blockIdx.y;
-    const int slice = (int)blockIdx.x;
-    first = slice * p.units_per_slice + min(slice, p.units_extra);
-    count = p.units_per_slice + (slice < p.units_extra ? 1 : 0);
-  };
+  // Work of this CTA: super-block blockIdx.y (K blocks sb*S ..), the row units [first, first + count)
+  // of slice blockIdx.x.  The first nRU % slices slices take one unit more.
+  const int sb = (int)blockIdx.y;
+  const int cta_first = (int)blockIdx.x * p.units_per_slice + min((int)blockIdx.x, p.units_extra);
+  const int cta_count = p.units_per_slice + ((int)blockIdx.x < p.units_extra ? 1 : 0);
   // Matrix that owns 32-row unit `ru` of the concatenated row space.
   auto locate = [&](int ru) {
     int j = 0;
@@ -184,15 +175,13 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     return j;
   };
   bool dead = false;
-  // Stage this warp's task t (its t-th unit, counted over the K blocks the CTA walks) into ring
-  // slot t % kStages: lane 0 announces the bytes, then lanes 0..5 each copy one 512-byte
-  // (group half, plane) run in the same instruction.  The slot is free: the warp itself finished
-  // reading it (all lanes pass the __syncwarp before this is called).
-  auto issue_unit = [&](int t, int kb_, int ru) {
-    const int slot = t % kStages;
+  // Stage unit (kb_, ru) into ring slot `slot`: one tiled copy brings all six runs (lane 0 announces
+  // the bytes and issues it).  The slot is free: the warp itself finished reading it (all lanes
+  // pass a __syncwarp before this is called).
+  auto issue_unit = [&](int slot, int kb_, int ru) {
     const int ngroups = min(2, p.G - 2 * kb_);
     const uint32_t bar = smem_u32(&full_bars[warp * kStages + slot]);
-    if (ngroups == 2) {  // one tiled copy brings all six runs
+    if (ngroups == 2) {
       if (lane == 0) {
         const int j = locate(ru);
         mbar_expect_tx(bar, (uint32_t)kUnitBytes);
@@ -205,9 +194,9 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       return;
     }
     // a single trailing group: three plain runs
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(3 * ngroups * kPlaneTile));
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(3 * kPlaneTile));
     __syncwarp();
-    if (lane < 3 * ngroups) {
+    if (lane < 3) {
       const W3Matrix& mat = p.mats[locate(ru)];
       const uint8_t* src = mat.planes + (((size_t)(2 * kb_) * 3 + lane) * mat.O + (size_t)(ru - mat.ru_begin) * kUnitRows) * 16;
       bulk_g2s(smem_u32(ring + ((size_t)(warp * kStages + slot) * 6 + lane) * kPlaneTile), src, (uint32_t)kPlaneTile, bar);
@@ -216,35 +205,23 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   // Final value of one output element: rounded to the 16-bit dtype, then the optional residual
   // is added and the sum rounded again (what separate Linear and add kernels produce).
   auto emit = [&](const W3Matrix& mat, int m, int lrow, float value) {
-    if (p.push_world > 0) {  // one 8-byte store (value, mark) into every rank's exchange buffer
-      const uint2 slot = make_uint2(__float_as_uint(value), 1u);
+    if (p.push_world > 0) {  // one 8-byte store {value, mark = 1} into every rank's exchange buffer
+      const unsigned long long slot = (1ull << 32) | (unsigned long long)__float_as_uint(value);
       for (int r = 0; r < p.push_world; ++r)
-        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p.push_data[r] + lrow), "r"(slot.x), "r"(slot.y) : "memory");
+        asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p.push_data[r] + lrow), "l"(slot) : "memory");
       return;
     }
-    if (mat.residual) {
-      const float y = p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(value)) : __half2float(__float2half_rn(value));
-      value = y + load_act(mat.residual, p.act_dtype, m * mat.O + lrow);
-    }
+    if (mat.residual) value = round_to(value, p.act_dtype) + load_act(mat.residual, p.act_dtype, m * mat.O + lrow);
     store_act(mat.out, p.act_dtype, m * mat.O + lrow, value);
   };
 
   // Lane rotation (byte, half, word): at every step the 32 lanes hit 32 different tables.
   const int rb = lane & 3, rh = (lane >> 2) & 1, rw = (lane >> 3) & 3;
   // Per-lane constants of the rotated walk, all as 32-bit shared-memory addresses / offsets so
-  // that the hot loop does no 64-bit pointer arithmetic.  A lookup is: byte-permute (weight byte
-  // to the low byte), one integer multiply-add (entry * stride + table address, on the FMA
-  // pipe, which keeps the half-rate integer ALU pipe nearly idle), the shared-memory load, one add.
+  // that the hot loop does no 64-bit pointer arithmetic.  A lookup is: one 4-way byte dot product
+  // (entry * stride + table address), the shared-memory load, and half a packed add.
   const uint32_t lut_u32 = smem_u32(lut), ring_u32 = smem_u32(ring);
   uint32_t sel[4], xl[2][4][4], woff[2][4];
-  uint32_t xa[2], xb[4], xc[4];
-  xa[0] = lut_u32 + 64u * rh;
-  xa[1] = lut_u32 + 64u * (rh ^ 1);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    xb[j] = 16u * ((j + rw) & 3);
-    xc[j] = 4u * ((j + rb) & 3);
-  }
 #pragma unroll
   for (int b = 0; b < 4; ++b) sel[b] = 128u << (8 * ((b + rb) & 3));  // weight 128 at byte (b+rb)%4
 #pragma unroll
@@ -253,55 +230,45 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     for (int jw = 0; jw < 4; ++jw) {
       woff[jh][jw] = (uint32_t)(((jh ^ rh) * 3) * kPlaneTile + ((jw + rw) & 3) * 4);
 #pragma unroll
-      for (int b = 0; b < 4; ++b) xl[jh][jw][b] = xa[jh] + xb[jw] + xc[b];  // one three-input add each
+      for (int b = 0; b < 4; ++b) xl[jh][jw][b] = lut_u32 + 64u * (jh ^ rh) + 16u * ((jw + rw) & 3) + 4u * ((b + rb) & 3);
     }
   // entry * stride + table address in ONE instruction: a 4-way byte dot product whose only
   // non-zero weight (the stride, 128 for M = 1) sits at the wanted byte of the staged word
   auto lookup_address = [&](uint32_t word, int b, uint32_t table) {
     uint32_t address;
-    if (Geom::kStride <= 128) {
+    if (G_::kStride <= 128) {
       asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(address) : "r"(word), "r"(sel[b]), "r"(table));
     } else {  // the stride does not fit a byte weight: dot product with weight 128, then scale
       uint32_t entry128;
       asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(entry128) : "r"(word), "r"(sel[b]), "r"(0u));
-      address = entry128 * (Geom::kStride / 128) + table;
+      address = entry128 * (G_::kStride / 128) + table;
     }
     return address;
   };
-  auto lds_f32 = [](uint32_t address) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(address));
-    return v;
-  };
-  auto table_of = [&](int m) { return lut + m * 128; };
 
   // This CTA walks the K blocks kb_begin .. kb_begin + nS - 1 over the same rows.  Warp w takes
-  // the units cta_first + w, + kWarps, ...; its tasks are numbered t = K block * my_count + unit.
-  int sb, cta_first, cta_count;
-  share(sb, cta_first, cta_count);
+  // the units cta_first + w, + kWarps, ...; its tasks are numbered K block * my_count + unit.
   const int kb_begin = sb * p.S, nS = min(p.S, p.nKB - kb_begin);
   const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
   const int my_tasks = nS * my_count;
-  int pf_task = 0, pf_kb = kb_begin, pf_ru = cta_first + warp;  // the next task to stage
+  int pf_task = 0, pf_slot = 0, pf_kb = kb_begin, pf_ru = cta_first + warp;  // the next task to stage
   auto issue_next = [&]() {
-    issue_unit(pf_task, pf_kb, pf_ru);
+    issue_unit(pf_slot, pf_kb, pf_ru);
     ++pf_task;
+    pf_slot = pf_slot + 1 == kStages ? 0 : pf_slot + 1;
     pf_ru += kWarps;
     if (pf_ru >= cta_first + cta_count) {
       pf_ru = cta_first + warp;
       ++pf_kb;
     }
   };
-  FB_MARK(12);
-  // Weights never change, so staging needs no wait.  Only kEarlyStages units per warp go out before
-  // the wait on the previous kernel: the whole grid's requests are served in order, and the small
+  // Weights never change, so staging needs no wait.  Only one unit per warp goes out before the
+  // wait on the previous kernel: the whole grid's requests are served in order, and the small
   // activation loads that follow the wait must not queue behind 20 MB of weights.
-  for (int t = 0; t < kEarlyStages && t < my_tasks; ++t) issue_next();
-  FB_MARK(1);
+  if (my_tasks > 0) issue_next();
 
   // Everything below reads activations and writes scratch / outputs of this stream.
   pdl_wait_prior_grid();
-  FB_MARK(9);
 
   // Raw 16-bit activations of one lane's table (8 values) and of the fused transform's operand;
   // the next K block's are fetched while the current one is being computed.
@@ -345,8 +312,79 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     inv_rms = rsqrtf(ss / (float)p.K + p.eps);
     __syncthreads();
   }
-  for (int t = kEarlyStages; t < kStages && t < my_tasks; ++t) issue_next();  // the rest of the ring, behind the activation loads
-  auto round16 = [&](float v) { return p.act_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v)); };
+  for (int t = 1; t < kStages && t < my_tasks; ++t) issue_next();  // the rest of the ring, behind the activation loads
+
+  // ---- build the 32 tables of K block kb_ into table set `set`: lane = table; warp w owns the
+  // entries whose low nibble is w, so that the walk over the high nibble unrolls with constant
+  // offsets.  sx[m][jh]: the sum of the activations of the group this lane walks in half jh. ----
+  auto build = [&](int kb_, int set, float (&sx)[M][2]) {
+    const int g = 2 * kb_ + (lane >> 4);
+    const int kbase = g * 128 + (lane & 15) * 8;
+    unsigned char* const tables = lut + (size_t)set * G_::kLutBytes;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float v8[8];
+      if (fast_x) {
+        const uint32_t words[4] = {raw_next.x, raw_next.y, raw_next.z, raw_next.w};
+        const uint32_t owords[4] = {op_next.x, op_next.y, op_next.z, op_next.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+          if (p.prologue != 0) {
+            // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
+            // SwiGLU rounds silu(gate) before the product
+            const float other = bits_to_float((unsigned short)((owords[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+            v8[j] = p.prologue == 1 ? round_to(other * round_to(v8[j] * inv_rms, p.act_dtype), p.act_dtype)
+                                    : round_to(round_to(v8[j] / (1.f + __expf(-v8[j])), p.act_dtype) * other, p.act_dtype);
+          }
+        }
+        if (kb_ + 1 < kb_begin + nS) fetch_x(kb_ + 1, raw_next, op_next);
+      } else if (g < p.G) {
+        if (p.perm) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v8[j] = load_act(p.x, p.act_dtype, m * p.K + p.perm[kbase + j]);
+        } else {
+          const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + (size_t)m * p.K + kbase);
+          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v8[j] = 0.f;
+      }
+      // Every entry is the ascending-order subset sum of its activations (as the reference's
+      // tables are): first the low nibble's, then one add per step of the high nibble's tree.
+      unsigned char* const column = tables + m * 128 + lane * 4;
+#pragma unroll
+      for (int qq = 0; qq < 16 / kWarps; ++qq) {
+        const int q = warp * (16 / kWarps) + qq;
+        float hi[16];
+        hi[0] = 0.f;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if ((q >> b) & 1) hi[0] += v8[b];
+#pragma unroll
+        for (int h = 1; h < 16; ++h) {
+          const int top = h >= 8 ? 3 : (h >= 4 ? 2 : (h >= 2 ? 1 : 0));
+          hi[h] = hi[h & ~(1 << top)] + v8[4 + top];
+        }
+        unsigned char* const at = column + (size_t)q * G_::kStride;
+#pragma unroll
+        for (int h = 0; h < 16; ++h) *reinterpret_cast<float*>(at + (size_t)h * 16 * G_::kStride) = hi[h];
+      }
+      float total = 0.f;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) total += v8[b];
+#pragma unroll
+      for (int d = 8; d >= 1; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
+      // lanes 0..15 hold the first group's sum, lanes 16..31 the second's; half jh of this lane's
+      // walk is group (jh ^ rh)
+      sx[m][0] = __shfl_sync(0xffffffffu, total, 16 * rh);
+      sx[m][1] = __shfl_sync(0xffffffffu, total, 16 * (rh ^ 1));
+    }
+  };
 
   // Split-K combine.  A contribution is ONE 64-bit atomic add: the partial sum in fixed point
   // (units of 2^-26) in bits 12..63, an arrival count in bits 0..5, a count of non-finite or
@@ -372,91 +410,38 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
     }
     pend_ru = -1;
   };
+  auto contribute = [&](int m, int ru, int row, float v) {
+    if (m == 0) settle();  // the previous unit's answers have long arrived
+    const bool fits = fabsf(v) < 2097152.f;  // 2^21: sixteen of them stay inside 52 bits
+    pend_add[m] = fits ? ((unsigned long long)__float2ll_rn(v * 67108864.f) << 12) + 1ull : 65ull;
+    asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;"
+                 : "=l"(pend_old[m])
+                 : "l"(p.combine + (size_t)m * p.O + row), "l"(pend_add[m])
+                 : "memory");
+    pend_ru = ru;
+  };
 
-  for (int s = 0; s < nS; ++s) {
+  // A warp with a single unit carries its sum over the K blocks of the super-block in registers;
+  // with more units the running sums of a super-block go through the L2-resident partials.
+  const bool in_registers = my_count == 1;
+  float carried[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) carried[m] = 0.f;
+  int c_slot = 0;
+  uint32_t c_phase = 0;
+  float sx_cur[M][2], sx_nxt[M][2];
+
+  // ---- the units of this warp for K block kb = kb_begin + s, tables in set SET ----
+  auto run_block = [&](auto set_tag, int s) {
+    constexpr int kSetOffset = decltype(set_tag)::value * G_::kLutBytes;
     const int kb = kb_begin + s;
-    if (s > 0) __syncthreads();  // everyone has finished reading the previous tables
-
-    // ---- build the 32 tables of this K block: lane = table; warp w owns the entries whose low
-    // nibble is 2w or 2w+1, so that the walk over the high nibble unrolls with constant offsets ----
-    float sx_m[M];  // lanes 0..15: sum of group A's activations, lanes 16..31: group B's
-    {
-      const int g = 2 * kb + (lane >> 4);
-      const int kbase = g * 128 + (lane & 15) * 8;
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float v8[8];
-        if (fast_x) {
-          const uint32_t words[4] = {raw_next.x, raw_next.y, raw_next.z, raw_next.w};
-          const uint32_t owords[4] = {op_next.x, op_next.y, op_next.z, op_next.w};
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
-            if (p.prologue != 0) {
-              // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
-              // SwiGLU rounds silu(gate) before the product
-              const float other = bits_to_float((unsigned short)((owords[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
-              v8[j] = p.prologue == 1 ? round16(other * round16(v8[j] * inv_rms))
-                                      : round16(round16(v8[j] / (1.f + __expf(-v8[j]))) * other);
-            }
-          }
-          if (s + 1 < nS) fetch_x(kb + 1, raw_next, op_next);
-        } else if (g < p.G) {
-          if (p.perm) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v8[j] = load_act(p.x, p.act_dtype, m * p.K + p.perm[kbase + j]);
-          } else {
-            const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + (size_t)m * p.K + kbase);
-            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v8[j] = 0.f;
-        }
-        // Every entry is the ascending-order subset sum of its activations (as the reference's
-        // tables are): first the low nibble's, then one add per step of the high nibble's tree.
-        unsigned char* const column = table_of(m) + lane * 4;
-#pragma unroll
-        for (int qq = 0; qq < 16 / kWarps; ++qq) {
-          const int q = warp * (16 / kWarps) + qq;
-          float hi[16];
-          hi[0] = 0.f;
-#pragma unroll
-          for (int b = 0; b < 4; ++b)
-            if ((q >> b) & 1) hi[0] += v8[b];
-#pragma unroll
-          for (int h = 1; h < 16; ++h) {
-            const int top = h >= 8 ? 3 : (h >= 4 ? 2 : (h >= 2 ? 1 : 0));
-            hi[h] = hi[h & ~(1 << top)] + v8[4 + top];
-          }
-          unsigned char* const at = column + (size_t)q * Geom::kStride;
-#pragma unroll
-          for (int h = 0; h < 16; ++h) *reinterpret_cast<float*>(at + (size_t)h * 16 * Geom::kStride) = hi[h];
-        }
-        float total = 0.f;
-#pragma unroll
-        for (int b = 0; b < 8; ++b) total += v8[b];
-#pragma unroll
-        for (int d = 8; d >= 1; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
-        sx_m[m] = total;
-      }
-    }
-    FB_MARK(2);
-    __syncthreads();
-    FB_MARK(3);
-
-    // ---- this warp's units ----
     int cur_j = 0, cur_begin = 0, cur_end = -1, cur_O = 0;
     const unsigned short* cur_scales = nullptr;
     const uint8_t* cur_zeros = nullptr;
-    const int gA = 2 * kb, gB = 2 * kb + 1;
-    const bool hasB = gB < p.G;
+    // half jh of this lane's walk covers group 2*kb + (jh ^ rh); an odd G leaves the last one empty
+    const int g_of[2] = {2 * kb + rh, 2 * kb + (rh ^ 1)};
+    const bool has[2] = {g_of[0] < p.G, g_of[1] < p.G};
     for (int i = 0; i < my_count; ++i) {
-      const int seq = s * my_count + i, slot = seq % kStages;
-      const bool mine = true;
       const int ru = cta_first + i * kWarps + warp;
       const int row = ru * kUnitRows + lane;  // in the concatenated row space
       if (ru < cur_begin || ru >= cur_end) {  // entering another matrix of the launch: rare
@@ -473,24 +458,17 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       // requested now, needed only after the lookups
       // (volatile, so that the requests stay HERE and their first use stays after the lookups:
       // left to itself the compiler may move the pair together and expose the round trip)
-      uint32_t sbitsA = 0, sbitsB = 0, zA = 4, zB = 4;
+      uint32_t sbits[2] = {0u, 0u}, zp[2] = {4u, 4u};
       if (!dead) {
-        const int at = gA * cur_O + lrow;  // G * O < 2^24
-        asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sbitsA) : "l"(cur_scales + at));
-        if (hasB) asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sbitsB) : "l"(cur_scales + at + cur_O));
-        if (cur_zeros) {
-          asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(zA) : "l"(cur_zeros + at));
-          if (hasB) asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(zB) : "l"(cur_zeros + at + cur_O));
-        }
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh)
+          if (has[jh]) {
+            const int at = g_of[jh] * cur_O + lrow;  // G * O < 2^24
+            asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sbits[jh]) : "l"(cur_scales + at));
+            if (cur_zeros) asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(zp[jh]) : "l"(cur_zeros + at));
+          }
       }
-      FB_WAVE_MARK(seq, 0);
-#if FB_W3_TRACE
-      if (lane == 0 && (warp == 0 || warp == 7) && seq < 8)
-        reinterpret_cast<long long*>(reinterpret_cast<char*>(p.status) + (2 << 20))[((FB_CTA * 2 + (warp == 7)) * 8 + seq) * 8 + 6] =
-            mbar_try_wait(smem_u32(&full_bars[warp * kStages + slot]), (uint32_t)((seq / kStages) & 1)) ? 1 : 0;
-      FB_WAVE_MARK(seq, 7);
-#endif
-      bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[warp * kStages + slot]), (uint32_t)((seq / kStages) & 1));
+      bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[warp * kStages + c_slot]), c_phase);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok && !dead) {
         dead = true;
@@ -500,12 +478,10 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
       float prev[M];
 #pragma unroll
       for (int m = 0; m < M; ++m)
-        prev[m] = (s > 0 && mine && !dead && p.nKB > 1 && !p.group_partials) ? __ldcg(&p.partials[((size_t)sb * M + m) * p.O + row]) : 0.f;
-      FB_MARK(4);
-      FB_WAVE_MARK(seq, 1);
+        prev[m] = (s > 0 && !in_registers && !dead && !p.group_partials) ? __ldcg(&p.partials[((size_t)sb * M + m) * p.O + row]) : 0.f;
 
-      // per activation row, group half and plane: two partial sums (even / odd byte steps)
-      float acc2[M][2][3][2];
+      // per activation row, group half and plane: an (even byte step, odd byte step) pair of sums
+      uint64_t acc[M][2][3];
       float corr[M][2];
 #pragma unroll
       for (int m = 0; m < M; ++m)
@@ -513,14 +489,18 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
         for (int jh = 0; jh < 2; ++jh) {
           corr[m][jh] = 0.f;
 #pragma unroll
-          for (int pl = 0; pl < 3; ++pl) acc2[m][jh][pl][0] = acc2[m][jh][pl][1] = 0.f;
+          for (int pl = 0; pl < 3; ++pl) acc[m][jh][pl] = 0ull;
         }
 
-#ifndef FB_W3_ABLATE
-#define FB_W3_ABLATE 0
-#endif
-      if (!dead && mine && !(FB_W3_ABLATE & 1)) {
-        const uint32_t wbase = ring_u32 + (uint32_t)((warp * kStages + slot) * kUnitBytes + lane * 16);
+      if (!dead) {
+        // the rounding correction needs the zero points during the lookups (code - zero = +/-3 is
+        // code 7 / 1 at zero point 4 and code 6 / 0 at zero point 3)
+        uint32_t flip[2] = {0u, 0u};
+        if (CORRECT) {
+          flip[0] = zp[0] == 3u ? 0xffffffffu : 0u;
+          flip[1] = zp[1] == 3u ? 0xffffffffu : 0u;
+        }
+        const uint32_t wbase = ring_u32 + (uint32_t)((warp * kStages + c_slot) * kUnitBytes + lane * 16);
         // staged words are fetched one (half, word) step ahead of their use: six live registers
         auto fetch = [&](int jh, int jw, uint32_t (&dst)[3]) {
           const uint32_t wa = wbase + woff[jh][jw];
@@ -536,135 +516,170 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
           if (step + 1 < 8) fetch((step + 1) >> 2, (step + 1) & 3, nxt);
           uint32_t plus3 = 0, minus3 = 0;
           if (CORRECT) {
-            plus3 = cur[0] & cur[1] & ~cur[2];   // code 7 (stored high plane is inverted)
-            minus3 = cur[0] & ~cur[1] & cur[2];  // code 1
+            const uint32_t low = cur[0] ^ flip[jh];
+            plus3 = low & cur[1] & ~cur[2];   // code - zero = +3 (the stored high plane is inverted)
+            minus3 = low & ~cur[1] & cur[2];  // code - zero = -3
           }
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
+          for (int bp = 0; bp < 2; ++bp) {  // byte steps 2bp (even) and 2bp + 1 (odd) make one packed add
 #pragma unroll
             for (int pl = 0; pl < 3; ++pl) {
-              const uint32_t a = lookup_address(cur[pl], b, xl[jh][jw][b]);
+              const uint32_t a0 = lookup_address(cur[pl], 2 * bp, xl[jh][jw][2 * bp]);
+              const uint32_t a1 = lookup_address(cur[pl], 2 * bp + 1, xl[jh][jw][2 * bp + 1]);
 #pragma unroll
-              for (int m = 0; m < M; ++m) acc2[m][jh][pl][b & 1] += lds_f32(a + m * 128);
+              for (int m = 0; m < M; ++m) {
+                // activation row m sits m * 128 bytes further (M > 1 has a single table set)
+                const float v0 = M == 1 ? lds_at<kSetOffset>(a0) : lds_at<0>(a0 + (uint32_t)(m * 128));
+                const float v1 = M == 1 ? lds_at<kSetOffset>(a1) : lds_at<0>(a1 + (uint32_t)(m * 128));
+                acc[m][jh][pl] = add2(acc[m][jh][pl], pack2(v0, v1));
+              }
             }
             if (CORRECT) {
-              const uint32_t ap = lookup_address(plus3, b, xl[jh][jw][b]);
-              const uint32_t am = lookup_address(minus3, b, xl[jh][jw][b]);
 #pragma unroll
-              for (int m = 0; m < M; ++m) corr[m][jh] += lds_f32(ap + m * 128) - lds_f32(am + m * 128);
+              for (int b = 2 * bp; b < 2 * bp + 2; ++b) {
+                const uint32_t ap = lookup_address(plus3, b, xl[jh][jw][b]);
+                const uint32_t am = lookup_address(minus3, b, xl[jh][jw][b]);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                  const float vp = M == 1 ? lds_at<kSetOffset>(ap) : lds_at<0>(ap + (uint32_t)(m * 128));
+                  const float vm = M == 1 ? lds_at<kSetOffset>(am) : lds_at<0>(am + (uint32_t)(m * 128));
+                  corr[m][jh] += vp - vm;
+                }
+              }
             }
           }
 #pragma unroll
           for (int pl = 0; pl < 3; ++pl) cur[pl] = nxt[pl];
         }
       }
-      FB_MARK(5);
-      FB_WAVE_MARK(seq, 2);
 
       // all lanes are done with the staged bytes: the slot takes this warp's task kStages ahead
       __syncwarp();
-      FB_WAVE_MARK(seq, 4);
-      if (!dead && pf_task < my_tasks && !(FB_W3_ABLATE & 4)) issue_next();
-      FB_WAVE_MARK(seq, 5);
+      if (!dead && pf_task < my_tasks) issue_next();
+      if (++c_slot == kStages) {
+        c_slot = 0;
+        c_phase ^= 1u;
+      }
 
-      if (!dead && mine && !(FB_W3_ABLATE & 2)) {
-        asm volatile("" : "+r"(sbitsA), "+r"(sbitsB), "+r"(zA), "+r"(zB));  // first use: after the lookups
-        const float sA = bits_to_float((unsigned short)sbitsA, p.scale_dtype);
-        const float sB = bits_to_float((unsigned short)sbitsB, p.scale_dtype);
+      if (!dead) {
+        asm volatile("" : "+r"(sbits[0]), "+r"(sbits[1]), "+r"(zp[0]), "+r"(zp[1]));  // first use: after the lookups
+        const float sc[2] = {bits_to_float((unsigned short)sbits[0], p.scale_dtype), bits_to_float((unsigned short)sbits[1], p.scale_dtype)};
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          auto plane_sum = [&](int jh, int pl) { return acc2[m][jh][pl][0] + acc2[m][jh][pl][1]; };
-          const float first = plane_sum(0, 0) + 2.f * plane_sum(0, 1) - 4.f * plane_sum(0, 2);
-          const float second = plane_sum(1, 0) + 2.f * plane_sum(1, 1) - 4.f * plane_sum(1, 2);
-          float dA = rh ? second : first, dB = rh ? first : second;
-          if (cur_zeros) {
-            dA += (4.f - (float)zA) * __shfl_sync(0xffffffffu, sx_m[m], 0);
-            dB += (4.f - (float)zB) * __shfl_sync(0xffffffffu, sx_m[m], 16);
+          float term[2];
+#pragma unroll
+          for (int jh = 0; jh < 2; ++jh) {
+            float d = sum2(acc[m][jh][0]) + 2.f * sum2(acc[m][jh][1]) - 4.f * sum2(acc[m][jh][2]);
+            if (cur_zeros) d += (4.f - (float)zp[jh]) * sx_cur[m][jh];
+            term[jh] = d * sc[jh];
+            if (CORRECT) {
+              // rounding of scale*(+/-3) in the scale's dtype: the only inexact products
+              const float r3 = round_to(3.f * sc[jh], p.scale_dtype);
+              term[jh] += corr[m][jh] * (r3 - 3.f * sc[jh]);
+            }
           }
-          float vA = dA * sA, vB = dB * sB;
-          if (CORRECT) {
-            // rounding of scale*(+/-3) in the scale's dtype: the only inexact products
-            const float cA = rh ? corr[m][1] : corr[m][0], cB = rh ? corr[m][0] : corr[m][1];
-            const float r3A = p.scale_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(3.f * sA))
-                                                       : __half2float(__float2half_rn(3.f * sA));
-            const float r3B = p.scale_dtype == FB_BF16 ? __bfloat162float(__float2bfloat16_rn(3.f * sB))
-                                                       : __half2float(__float2half_rn(3.f * sB));
-            vA += cA * (r3A - 3.f * sA);
-            vB += cB * (r3B - 3.f * sB);
-          }
+          const float both = term[0] + term[1];
           if (p.group_partials) {
             float* ws_out = reinterpret_cast<float*>(mat.out);
-            ws_out[(size_t)gA * mat.O + lrow] = vA;
-            if (hasB) ws_out[(size_t)gB * mat.O + lrow] = vB;
+#pragma unroll
+            for (int jh = 0; jh < 2; ++jh)
+              if (has[jh]) ws_out[(size_t)g_of[jh] * mat.O + lrow] = term[jh];
           } else if (p.nKB == 1) {
-            emit(mat, m, lrow, vA + vB);
+            emit(mat, m, lrow, both);
+          } else if (in_registers) {
+            carried[m] += both;
+            if (s + 1 == nS) contribute(m, ru, row, carried[m]);
           } else {
-            const float v = prev[m] + (vA + vB);
-            if (s + 1 < nS) {
+            const float v = prev[m] + both;
+            if (s + 1 < nS)
               p.partials[((size_t)sb * M + m) * p.O + row] = v;
-            } else {
-              if (m == 0) settle();  // the previous unit's answers have long arrived
-              const bool fits = fabsf(v) < 2097152.f;  // 2^21: sixteen of them stay inside 52 bits
-              pend_add[m] = fits ? ((unsigned long long)__float2ll_rn(v * 67108864.f) << 12) + 1ull : 65ull;
-              asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;"
-                           : "=l"(pend_old[m])
-                           : "l"(p.combine + (size_t)m * p.O + row), "l"(pend_add[m])
-                           : "memory");
-              pend_ru = ru;
-            }
+            else
+              contribute(m, ru, row, v);
           }
         }
       }
-      FB_WAVE_MARK(seq, 3);
+    }
+  };
+
+  build(kb_begin, 0, sx_cur);
+  __syncthreads();
+  for (int s = 0; s < nS; ++s) {
+    const bool more = s + 1 < nS;
+    if (G_::kLutSets == 2) {
+      // the other table set is free (everyone left it at the last barrier): build ahead
+      if (more) build(kb_begin + s + 1, (s + 1) & 1, sx_nxt);
+      if (s & 1)
+        run_block(std::integral_constant<int, G_::kLutSets - 1>{}, s);
+      else
+        run_block(std::integral_constant<int, 0>{}, s);
+      if (more) __syncthreads();
+    } else {
+      run_block(std::integral_constant<int, 0>{}, s);
+      if (more) {
+        __syncthreads();  // everyone has finished reading the tables
+        build(kb_begin + s + 1, 0, sx_nxt);
+        __syncthreads();
+      }
+    }
+    if (more) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        sx_cur[m][0] = sx_nxt[m][0];
+        sx_cur[m][1] = sx_nxt[m][1];
+      }
     }
   }
-
-  FB_MARK(6);
   settle();
-  FB_MARK(8);
 }
 
 struct Plan {
-  int grid, ctas_per_kb, S, nSB;
+  int slices, S, nSB;
   size_t smem;
 };
 
-size_t lut_bytes(int m) { return (size_t)32768 << (m == 1 ? 0 : (m == 2 ? 1 : 2)); }
+size_t smem_bytes(int m) {
+  switch (m) {
+    case 1: return Geom<1>::kSmemBytes;
+    case 2: return Geom<2>::kSmemBytes;
+    case 3: return Geom<3>::kSmemBytes;
+    default: return Geom<4>::kSmemBytes;
+  }
+}
 
-// Two CTAs per SM: with M = 1 a CTA needs 32 KB of tables + 72 KB of staged units, so a CTA
-// of the next kernel in the stream can be resident (and prefetching) beside one of this kernel.
+// One CTA per SM.  At most kMaxSplits partial sums per output: beyond 16 K blocks one CTA walks
+// several K blocks of its rows in turn.  The SMs are dealt over the super-blocks; the CTAs of a
+// super-block split its row units.
 Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   Plan plan;
-  // At most kMaxSplits partial sums per output: beyond that one CTA walks several K blocks of
-  // its rows in turn, so that the final reduction stays one round of loads.
   plan.S = (nKB + kMaxSplits - 1) / kMaxSplits;
   plan.nSB = (nKB + plan.S - 1) / plan.S;
-  int c = kCtasPerSm * info.sm_count / plan.nSB;
+  int c = info.sm_count / plan.nSB;
   if (c < 1) c = 1;
   if (c > nRU) c = nRU;
-  plan.ctas_per_kb = c;
-  plan.grid = plan.nSB * c;
-  plan.smem = lut_bytes(m) + (size_t)kWarps * kStages * kUnitBytes + (size_t)kWarps * kStages * sizeof(uint64_t);
+  plan.slices = c;
+  plan.smem = smem_bytes(m);
   return plan;
 }
 
 template <int M, bool CORRECT>
-int launch(const W3Params& p, const Plan& plan, int max_smem, bool pdl, cudaStream_t stream) {
+int launch(const W3Params& p, const Plan& plan, bool pdl, cudaStream_t stream) {
   // Raising the dynamic shared memory limit is a per-device, per-kernel setting; do it once.
   static std::mutex lock;
   static bool ready[64] = {};
   int device = 0;
-  cudaGetDevice(&device);
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return cuda_fail(err, "cudaGetDevice");
+  if (device < 0 || device >= 64) return fail(FB_ELIMIT, "device ordinal %d outside 0..63", device);
   {
     std::lock_guard<std::mutex> guard(lock);
     if (!ready[device]) {
-      cudaError_t err = cudaFuncSetAttribute(w3_gemv_kernel<M, CORRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+      err = cudaFuncSetAttribute(w3_gemv_kernel<M, CORRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);
       if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(w3_gemv_kernel)");
       ready[device] = true;
     }
   }
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(plan.ctas_per_kb, plan.nSB);
+  config.gridDim = dim3(plan.slices, plan.nSB);
   config.blockDim = dim3(kWarps * 32);
   config.dynamicSmemBytes = plan.smem;
   config.stream = stream;
@@ -673,7 +688,7 @@ int launch(const W3Params& p, const Plan& plan, int max_smem, bool pdl, cudaStre
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = pdl && pdl_allowed() ? 1 : 0;
-  cudaError_t err = cudaLaunchKernelEx(&config, w3_gemv_kernel<M, CORRECT>, p);
+  err = cudaLaunchKernelEx(&config, w3_gemv_kernel<M, CORRECT>, p);
   if (err != cudaSuccess) return cuda_fail(err, "w3_gemv_kernel launch");
   return FB_OK;
 }
@@ -699,54 +714,6 @@ extern "C" size_t fb_w3_gemv_scratch_bytes(int m, int out_features, int in_featu
 }
 
 namespace {
-// Descriptor of one planes tensor for the tiled copies, cached per (address, O, G): encoding is
-// pure host work, but it would otherwise be repeated on every call.
-bool plane_map(const uint8_t* planes, int O, int G, CUtensorMap* out) {
-  static std::mutex lock;
-  static PFN_cuTensorMapEncodeTiled encode = nullptr;
-  struct Key {
-    const void* ptr;
-    int O, G;
-    bool operator==(const Key& other) const { return ptr == other.ptr && O == other.O && G == other.G; }
-  };
-  struct Hash {
-    size_t operator()(const Key& key) const { return std::hash<const void*>()(key.ptr) ^ ((size_t)key.O * 1315423911u) ^ ((size_t)key.G << 40); }
-  };
-  static std::unordered_map<Key, CUtensorMap, Hash> cache;
-  std::lock_guard<std::mutex> guard(lock);
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
-    if (err != cudaSuccess || status != cudaDriverEntryPointSuccess || !fn) {
-      cuda_fail(err, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
-      return false;
-    }
-    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
-  }
-  const Key key{planes, O, G};
-  auto found = cache.find(key);
-  if (found != cache.end()) {
-    *out = found->second;
-    return true;
-  }
-  const cuuint64_t dims[3] = {128, (cuuint64_t)(O / kUnitRows), (cuuint64_t)G * 3};
-  const cuuint64_t strides[2] = {(cuuint64_t)kPlaneTile, (cuuint64_t)O * 16};  // bytes, dims 1 and 2
-  const cuuint32_t box[3] = {128, 1, 6};
-  const cuuint32_t step[3] = {1, 1, 1};
-  CUtensorMap map;
-  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(planes), dims, strides, box, step,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) {
-    fail(FB_ECUDA, "cuTensorMapEncodeTiled failed with code %d for planes [%d,3,%d,16]", (int)rc, G, O);
-    return false;
-  }
-  if (cache.size() >= 8192) cache.clear();
-  cache.emplace(key, map);
-  *out = map;
-  return true;
-}
 
 int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrices, int n_matrices, int scale_dtype,
               const int16_t* perm, int in_features, void* scratch, size_t scratch_bytes, unsigned flags,
@@ -761,8 +728,8 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
         return fail(FB_EINVAL, "fb_w3_gemv_push: exchange pointer of rank %d missing or not 8-byte aligned", r);
   }
   if (prologue < 0 || prologue > 2) return fail(FB_EINVAL, "fb_w3_gemv: unknown input transform %d", prologue);
-  if (prologue != 0 && (m != 1 || perm || !prologue_arg || !aligned(prologue_arg, 2)))
-    return fail(FB_EINVAL, "fb_w3_gemv: a fused input transform needs M = 1, identity column order and its operand");
+  if (prologue != 0 && (m != 1 || perm || !prologue_arg || !aligned(prologue_arg, 16)))
+    return fail(FB_EINVAL, "fb_w3_gemv: a fused input transform needs M = 1, identity column order and a 16-byte aligned operand");
   const bool group_partials = (flags & FB_W3_GROUP_PARTIALS) != 0;
   if (!x || !matrices) return fail(FB_EINVAL, "fb_w3_gemv: x and the matrix list must be non-null");
   if (n_matrices < 1 || n_matrices > kMaxMatrices) return fail(FB_ELIMIT, "fb_w3_gemv: %d matrices given, 1..%d supported", n_matrices, kMaxMatrices);
@@ -784,7 +751,7 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   p.prologue_arg = prologue_arg;
   p.eps = eps;
   p.push_world = push ? push->world : 0;
-  for (int r = 0; r < 8; ++r) p.push_data[r] = push && r < push->world ? static_cast<uint2*>(push->data[r]) : nullptr;
+  for (int r = 0; r < 8; ++r) p.push_data[r] = push && r < push->world ? static_cast<unsigned long long*>(push->data[r]) : nullptr;
   p.n_mats = n_matrices;
   long long total = 0;
   for (int j = 0; j < kMaxMatrices; ++j) {
@@ -802,14 +769,12 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
       return fail(FB_EINVAL, "fb_w3_gemv: planes, scales and zeros must be 16-byte aligned");
     if (!aligned(in.scales, 2) || !aligned(in.out, group_partials ? 4 : 2) || !aligned(in.residual, 2))
       return fail(FB_EINVAL, "fb_w3_gemv: 16-bit tensors must be 2-byte aligned");
-    if ((flags & FB_W3_DECODED_BF16) && in.zeros)
-      return fail(FB_EINVAL, "fb_w3_gemv: the rounding correction needs the constant zero point (zeros == NULL)");
     const size_t out_bytes = group_partials ? (size_t)G * O * 4 : (size_t)m * O * 2;
     if (overlaps(in.out, out_bytes, x, x_bytes) || overlaps(in.out, out_bytes, in.planes, (size_t)G * 3 * O * 16) ||
         overlaps(in.out, out_bytes, in.scales, (size_t)G * O * 2))
       return fail(FB_EALIAS, "fb_w3_gemv: out overlaps an input");
     if (scratch && overlaps(scratch, scratch_bytes, in.out, out_bytes)) return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps out");
-    if (!plane_map(in.planes, O, G, &p.plane_maps[j])) return FB_ECUDA;
+    if (!plane_tensor_map(in.planes, O, G, 1, 6, &p.plane_maps[j])) return FB_ECUDA;
     mat.planes = in.planes;
     mat.scales = static_cast<const unsigned short*>(in.scales);
     mat.zeros = in.zeros;
@@ -839,19 +804,18 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   p.combine = reinterpret_cast<unsigned long long*>(base + kCombineOffset);
   p.partials = reinterpret_cast<float*>(base + kPartialsOffset);
   const Plan plan = make_plan(m, p.nKB, p.nRU, *info);
-  p.ctas_per_kb = plan.ctas_per_kb;
   p.S = plan.S;
-  p.units_per_slice = p.nRU / plan.ctas_per_kb;
-  p.units_extra = p.nRU % plan.ctas_per_kb;
+  p.units_per_slice = p.nRU / plan.slices;
+  p.units_extra = p.nRU % plan.slices;
   p.nSB = plan.nSB;
   p.group_partials = group_partials ? 1 : 0;
   if (plan.smem > (size_t)info->max_smem_optin) return fail(FB_ELIMIT, "fb_w3_gemv: plan needs %zu bytes of shared memory", plan.smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool correct = (flags & FB_W3_DECODED_BF16) != 0;
   const bool pdl = (flags & FB_W3_NO_PDL) == 0;
-#define FB_DISPATCH(MM)                                                                    \
-  case MM:                                                                                 \
-    return correct ? launch<MM, true>(p, plan, info->max_smem_optin, pdl, s) : launch<MM, false>(p, plan, info->max_smem_optin, pdl, s);
+#define FB_DISPATCH(MM) \
+  case MM:              \
+    return correct ? launch<MM, true>(p, plan, pdl, s) : launch<MM, false>(p, plan, pdl, s);
   switch (m) {
     FB_DISPATCH(1)
     FB_DISPATCH(2)

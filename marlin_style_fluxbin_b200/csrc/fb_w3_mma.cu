@@ -295,54 +295,6 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
-// Descriptor of the planes for the 128-row tiled copy, cached per (address, O, G).
-bool plane_map_128(const uint8_t* planes, int O, int G, CUtensorMap* out) {
-  static std::mutex lock;
-  static PFN_cuTensorMapEncodeTiled encode = nullptr;
-  struct Key {
-    const void* ptr;
-    int O, G;
-    bool operator==(const Key& other) const { return ptr == other.ptr && O == other.O && G == other.G; }
-  };
-  struct Hash {
-    size_t operator()(const Key& key) const { return std::hash<const void*>()(key.ptr) ^ ((size_t)key.O * 1315423911u) ^ ((size_t)key.G << 40); }
-  };
-  static std::unordered_map<Key, CUtensorMap, Hash> cache;
-  std::lock_guard<std::mutex> guard(lock);
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
-    if (err != cudaSuccess || status != cudaDriverEntryPointSuccess || !fn) {
-      cuda_fail(err, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
-      return false;
-    }
-    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
-  }
-  const Key key{planes, O, G};
-  auto found = cache.find(key);
-  if (found != cache.end()) {
-    *out = found->second;
-    return true;
-  }
-  const cuuint64_t dims[3] = {128, (cuuint64_t)(O / 32), (cuuint64_t)G * 3};
-  const cuuint64_t strides[2] = {512, (cuuint64_t)O * 16};
-  const cuuint32_t box[3] = {128, kTileRows / 32, 3};
-  const cuuint32_t step[3] = {1, 1, 1};
-  CUtensorMap map;
-  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(planes), dims, strides, box, step,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (rc != CUDA_SUCCESS) {
-    fail(FB_ECUDA, "cuTensorMapEncodeTiled failed with code %d for planes [%d,3,%d,16]", (int)rc, G, O);
-    return false;
-  }
-  if (cache.size() >= 8192) cache.clear();
-  cache.emplace(key, map);
-  *out = map;
-  return true;
-}
-
 }  // namespace
 
 extern "C" size_t fb_w3_gemm_small_scratch_bytes(int m, int out_features, int in_features) {
@@ -376,7 +328,7 @@ extern "C" int fb_w3_gemm_small(const void* x, int act_dtype, int m, const uint8
   const DeviceInfo* info = device_info();
   if (!info) return FB_ECUDA;
   MmaParams p;
-  if (!plane_map_128(planes, O, G, &p.plane_map)) return FB_ECUDA;
+  if (!plane_tensor_map(planes, O, G, kTileRows / 32, 3, &p.plane_map)) return FB_ECUDA;
   p.x = x;
   p.scales = static_cast<const unsigned short*>(scales);
   p.zeros = zeros;

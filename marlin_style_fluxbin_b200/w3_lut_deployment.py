@@ -289,7 +289,11 @@ class PackedW3Linear(nn.Module):
         if arithmetic not in ARITHMETIC_MODES:
             raise ValueError(f"arithmetic must be one of {ARITHMETIC_MODES}")
         if arithmetic == "decoded_bf16" and "zeros" in layout:
-            raise ValueError("decoded_bf16 arithmetic needs the constant zero point (no zeros field)")
+            # the kernel's rounding correction covers code - zero = +/-3, the only inexact
+            # products at zero points 3 and 4; other zero points have further inexact products
+            zero_values = set(torch.unique(layout["zeros"]).tolist())
+            if not zero_values <= {3, 4}:
+                raise ValueError("decoded_bf16 arithmetic needs zero points 3 or 4")
         workspace_shape(self.out_features, self.in_features, groups_per_split)
         self.groups_per_split = groups_per_split
         self.arithmetic = arithmetic

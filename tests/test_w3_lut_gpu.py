@@ -434,3 +434,79 @@ def test_push_epilogue_and_polling_reduce_on_one_device():
     # against the two-kernel form with 16-bit partial results: the push keeps fp32 partials
     two_step = ((partial_reference[0].float() + partial_reference[1].float()).bfloat16().float() + residual.float()).bfloat16()
     assert float((outs[0].float() - two_step.float()).abs().max()) <= 2.0 ** -6 * float(two_step.float().abs().max())
+
+
+@pytest.mark.parametrize("o,k,scale_dtype", ((4096, 4096, torch.float16), (1024, 1024, torch.bfloat16), (4096, 12288, torch.float16)))
+def test_decoded_weight_arithmetic_with_zero_points(o, k, scale_dtype):
+    """The rounding correction with per-row zero points in {3, 4} (the benchmark's draw): the result
+    follows the weight dequantised in the scale's dtype, scale * (code - zero) rounded once, which is
+    the oracle's dequantise-then-matmul to fp32 summation order (reference: csrc/w3_lut.cu:105-122,
+    gptq_deployment.py:280-315 for the constant zero point)."""
+    layout, x = make_case(o, k, seed=13, zeros=True, scale_dtype=scale_dtype)
+    reference, structural = oracle_outputs(layout, x)
+    lg, xg = to_cuda(layout), x.cuda()
+    plain, _ = run(lg, xg, row_tile=1024)
+    corrected, _ = run(lg, xg, row_tile=1024, arithmetic="decoded_bf16")
+    assert_parity(corrected, reference)
+    # bf16 outputs of the corrected kernel equal the rounded oracle up to fp32 summation order:
+    # at most one 16-bit ulp, and only in a few rows
+    want = torch.from_numpy(reference).bfloat16().float()
+    got = corrected.float().cpu()
+    assert float((got != want).float().mean()) <= 0.02
+    torch.testing.assert_close(got, want, rtol=2.0 ** -7, atol=1e-3)
+    # and it is closer to that oracle than the structural arithmetic is
+    e_plain = np.abs(plain.float().cpu().numpy() - reference).mean()
+    e_corr = np.abs(got.numpy() - reference).mean()
+    assert e_corr < e_plain
+    # repeat-exact
+    assert torch.equal(run(lg, xg, row_tile=1024, arithmetic="decoded_bf16")[0], corrected)
+
+
+def test_large_finite_activations_stay_inside_the_combine_range():
+    """Residual-stream outliers: a few input columns carry activations in the thousands.  The
+    fixed-point K-split combine must carry them like the fp32 accumulation of the reference does
+    (limit: a partial sum of 2^21 in magnitude, far above what such inputs produce)."""
+    layout, x = make_case(4096, 4096, seed=21, zeros=True)
+    x = x.float()
+    x[0, [5, 777, 2048, 4095]] = torch.tensor([3000.0, -2500.0, 1800.0, 4000.0])
+    x = x.bfloat16()
+    reference, _ = oracle_outputs(layout, x)
+    out, _ = run(to_cuda(layout), x.cuda(), row_tile=1024)
+    assert_parity(out, reference)
+    layout, x = make_case(4096, 12288, seed=22, zeros=True)
+    x = x.float()
+    x[0, [1, 6000, 12287]] = torch.tensor([-3500.0, 2200.0, 3900.0])
+    x = x.bfloat16()
+    reference, _ = oracle_outputs(layout, x)
+    out, _ = run(to_cuda(layout), x.cuda(), row_tile=1024)
+    assert_parity(out, reference)
+
+
+def test_polling_reduce_gives_up_after_its_limit():
+    """One rank never delivers: the reduce kernel's bounded wait runs out (here after 5 ms), the
+    status word becomes 4, the kernel returns, and the slots are left clean."""
+    import time
+
+    from marlin_style_fluxbin_b200 import _native
+
+    n, world = 256, 2
+    buffer = torch.zeros(world * n, 2, dtype=torch.int32, device="cuda")
+    buffer[:n, 0] = torch.full((n,), 1.5).view(torch.int32)  # rank 0 delivered {1.5, mark}
+    buffer[:n, 1] = 1
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    out = torch.zeros(1, n, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    began = time.perf_counter()
+    _native.tp_reduce(buffer.data_ptr(), world, None, out, status.data_ptr(), wait_ns=5_000_000)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - began < 2.0
+    assert int(status[0]) == 4
+    assert int(buffer.abs().sum()) == 0
+    # the context is intact: a complete exchange on the same buffers works afterwards
+    status.zero_()
+    for rank in range(world):
+        buffer[rank * n:(rank + 1) * n, 0] = torch.full((n,), float(rank + 1)).view(torch.int32)
+        buffer[rank * n:(rank + 1) * n, 1] = 1
+    _native.tp_reduce(buffer.data_ptr(), world, None, out, status.data_ptr(), wait_ns=5_000_000)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0 and torch.equal(out.float().cpu(), torch.full((1, n), 3.0))
