@@ -268,6 +268,28 @@ int fb_attn_decode_fused(const void* q, const void* k, const void* v, const void
 int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream);
 
 /*
+ * LM head of a greedy decode step in one launch:
+ *   x' = norm_weight ? norm_weight * T(x * rsqrt(mean(x^2) + eps)) : x     (the final RMSNorm, as fb_rmsnorm)
+ *   logit[v] = T( sum_k weight[v,k] * x'[k] )   fp32 accumulation, weight f16|bf16 [vocab, K] row-major
+ *   *best = the lowest v whose logit is the largest (torch.argmax's tie rule on the 16-bit logits)
+ * `logits` (optional, [vocab]) receives the 16-bit logits; without it they never leave the chip.
+ * `embedding` + `next_hidden` (optional, together): after the choice is known, row
+ * (*forced_next if forced_next else *best) of embedding [vocab, K] is copied to next_hidden [K], so that the
+ * next step starts without a gather launch; next_hidden may be x itself (the copy happens after every
+ * CTA has staged x).  scratch: fb_lm_head_scratch_bytes() bytes, 16-byte
+ * aligned, zero-filled once; every call leaves it zero.  K a multiple of 8.
+ * The reference keeps this step as the stock 16-bit Linear plus torch.argmax and names it the next
+ * thing to fuse (docs/performance/NONLINEAR_FUSION.md:100); the embedding lookup is the stock module.
+ */
+size_t fb_lm_head_scratch_bytes(void);
+int fb_lm_head_argmax(const void* x, const void* norm_weight, float eps, const void* weight, int vocab, int in_features,
+                      int dtype, void* logits, int64_t* best, const int64_t* forced_next, const void* embedding,
+                      void* next_hidden, void* scratch, size_t scratch_bytes, fb_stream_t stream);
+
+/* out[0..K) = embedding[*token, 0..K): the embedding lookup of one token id held on the device. */
+int fb_embed_row(const void* embedding, const int64_t* token, void* out, int vocab, int in_features, fb_stream_t stream);
+
+/*
  * fb_w3_gemv without a scratch argument, for callers that cannot allocate device memory where
  * they call this library (all memory already handed to a pool, a framework allocator that must
  * not be bypassed, a CUDA graph capture in progress).  The split-K scratch is a fixed array of

@@ -105,6 +105,13 @@ def library() -> ctypes.CDLL:
         lib.fb_attn_decode_scratch_bytes.argtypes = [ctypes.c_int]
         lib.fb_silu_mul.restype = ctypes.c_int
         lib.fb_silu_mul.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_lm_head_scratch_bytes.restype = ctypes.c_size_t
+        lib.fb_lm_head_scratch_bytes.argtypes = []
+        lib.fb_lm_head_argmax.restype = ctypes.c_int
+        lib.fb_lm_head_argmax.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                          ctypes.c_int] + [ctypes.c_void_p] * 6 + [ctypes.c_size_t, ctypes.c_void_p]
+        lib.fb_embed_row.restype = ctypes.c_int
+        lib.fb_embed_row.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         lib.fb_w3_gemv_static.restype = ctypes.c_int
         lib.fb_w3_gemv_static.argtypes = lib.fb_w3_gemv.argtypes[:11] + [ctypes.c_uint, ctypes.c_void_p]
         _lib = lib
@@ -327,7 +334,7 @@ W3_INPUT_RMSNORM, W3_INPUT_SILU_MUL = 1, 2
 
 
 def w3_gemv_fused_input(x, transform: int, operand, eps: float, matrices, n_matrices, total_out, scale_dtype, *,
-                        pdl=True, scratch=None) -> None:
+                        pdl=True, scratch=None, decoded_bf16=False) -> None:
     """``w3_gemv_multi`` for one activation row whose producer (RMSNorm or the SwiGLU gate) runs inside the launch."""
     k = x.shape[-1]
     if scratch is None:
@@ -335,7 +342,8 @@ def w3_gemv_fused_input(x, transform: int, operand, eps: float, matrices, n_matr
     with torch.cuda.device(x.device):
         check(library().fb_w3_gemv_fused_input(ptr(x), dtype_tag(x.dtype), transform, ptr(operand), float(eps), matrices, n_matrices,
                                                dtype_tag(scale_dtype), k, ptr(scratch), scratch.numel() * scratch.element_size(),
-                                               0 if pdl else FB_W3_NO_PDL, stream_handle(x.device)))
+                                               (0 if pdl else FB_W3_NO_PDL) | (FB_W3_DECODED_BF16 if decoded_bf16 else 0),
+                                               stream_handle(x.device)))
 
 
 def w3_gemm_small(x, planes, scales, zeros, perm, out, *, scratch=None) -> None:
@@ -360,12 +368,14 @@ def w3_push_descriptor(data_ptrs) -> W3Push:
     return push
 
 
-def w3_gemv_push(x, transform: int, operand, eps: float, matrix, k: int, scale_dtype, push: W3Push, *, scratch, pdl=True) -> None:
+def w3_gemv_push(x, transform: int, operand, eps: float, matrix, k: int, scale_dtype, push: W3Push, *, scratch, pdl=True,
+                 decoded_bf16=False) -> None:
     """Row-split Linear of a tensor-parallel rank: results go to every rank's exchange buffer (see the header)."""
     with torch.cuda.device(x.device):
         check(library().fb_w3_gemv_push(ptr(x), dtype_tag(x.dtype), transform, ptr(operand), float(eps), matrix, dtype_tag(scale_dtype), k,
                                         ctypes.byref(push), ptr(scratch), scratch.numel() * scratch.element_size(),
-                                        0 if pdl else FB_W3_NO_PDL, stream_handle(x.device)))
+                                        (0 if pdl else FB_W3_NO_PDL) | (FB_W3_DECODED_BF16 if decoded_bf16 else 0),
+                                        stream_handle(x.device)))
 
 
 def tp_reduce(parts_ptr: int, world: int, residual, out, status_ptr: int, wait_ns: int = 0) -> None:
@@ -376,3 +386,26 @@ def tp_reduce(parts_ptr: int, world: int, residual, out, status_ptr: int, wait_n
     with torch.cuda.device(out.device):
         check(library().fb_tp_reduce(ctypes.c_void_p(parts_ptr), world, ptr(residual), ptr(out), out.numel(), dtype_tag(out.dtype),
                                      ctypes.c_void_p(status_ptr), int(wait_ns), stream_handle(out.device)))
+
+
+def lm_head_scratch_bytes() -> int:
+    return int(library().fb_lm_head_scratch_bytes())
+
+
+def lm_head_argmax(x, norm_weight, eps: float, weight, best, *, logits=None, forced_next=None, embedding=None, next_hidden=None,
+                   scratch) -> None:
+    """Greedy LM head in one launch: optional final RMSNorm of ``x [1,K]``, ``weight [V,K]`` GEMV, argmax into
+    ``best`` (int64 ``[1]``); optionally the 16-bit logits, and the embedding row of the next token
+    (``forced_next`` int64 ``[1]`` on the device, else the choice) copied into ``next_hidden``."""
+    vocab, k = weight.shape
+    with torch.cuda.device(x.device):
+        check(library().fb_lm_head_argmax(ptr(x), ptr(norm_weight), float(eps), ptr(weight), vocab, k, dtype_tag(x.dtype), ptr(logits),
+                                          ptr(best), ptr(forced_next), ptr(embedding), ptr(next_hidden), ptr(scratch),
+                                          scratch.numel() * scratch.element_size(), stream_handle(x.device)))
+
+
+def embed_row(embedding, token, out) -> None:
+    """``out[0, :] = embedding[token[0], :]`` for a token id held on the device (int64 ``[1]``)."""
+    vocab, k = embedding.shape
+    with torch.cuda.device(out.device):
+        check(library().fb_embed_row(ptr(embedding), ptr(token), ptr(out), vocab, k, stream_handle(out.device)))

@@ -54,34 +54,43 @@ const DeviceInfo* device_info() {
   return &table[device];
 }
 
-bool plane_tensor_map(const uint8_t* planes, int O, int G, int box_units, int box_runs, CUtensorMap* out) {
-  static std::mutex lock;
-  static PFN_cuTensorMapEncodeTiled encode = nullptr;
-  struct Key {
-    const void* ptr;
-    int O, G, box;
-    bool operator==(const Key& other) const { return ptr == other.ptr && O == other.O && G == other.G && box == other.box; }
-  };
-  struct Hash {
-    size_t operator()(const Key& key) const {
-      return std::hash<const void*>()(key.ptr) ^ ((size_t)key.O * 1315423911u) ^ ((size_t)key.G << 40) ^ ((size_t)key.box << 52);
-    }
-  };
-  static std::unordered_map<Key, CUtensorMap, Hash> cache;
-  std::lock_guard<std::mutex> guard(lock);
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
-    if (err != cudaSuccess || status != cudaDriverEntryPointSuccess || !fn) {
-      cuda_fail(err, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
-      return false;
-    }
-    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+namespace {
+// One cache for every descriptor this library encodes, keyed by (address, O, G, kind).
+struct MapKey {
+  const void* ptr;
+  int O, G, kind;
+  bool operator==(const MapKey& other) const { return ptr == other.ptr && O == other.O && G == other.G && kind == other.kind; }
+};
+struct MapHash {
+  size_t operator()(const MapKey& key) const {
+    return std::hash<const void*>()(key.ptr) ^ ((size_t)key.O * 1315423911u) ^ ((size_t)key.G << 40) ^ ((size_t)key.kind << 52);
   }
-  const Key key{planes, O, G, box_units * 256 + box_runs};
-  auto found = cache.find(key);
-  if (found != cache.end()) {
+};
+std::mutex g_map_lock;
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
+PFN_cuTensorMapEncodeTiled g_encode = nullptr;
+
+// Caller holds g_map_lock.
+bool encoder_ready() {
+  if (g_encode) return true;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult status;
+  cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+  if (err != cudaSuccess || status != cudaDriverEntryPointSuccess || !fn) {
+    cuda_fail(err, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    return false;
+  }
+  g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+  return true;
+}
+}  // namespace
+
+bool plane_tensor_map(const uint8_t* planes, int O, int G, int box_units, int box_runs, CUtensorMap* out) {
+  std::lock_guard<std::mutex> guard(g_map_lock);
+  if (!encoder_ready()) return false;
+  const MapKey key{planes, O, G, box_units * 256 + box_runs};
+  auto found = g_maps.find(key);
+  if (found != g_maps.end()) {
     *out = found->second;
     return true;
   }
@@ -90,15 +99,42 @@ bool plane_tensor_map(const uint8_t* planes, int O, int G, int box_units, int bo
   const cuuint32_t box[3] = {128, (cuuint32_t)box_units, (cuuint32_t)box_runs};
   const cuuint32_t step[3] = {1, 1, 1};
   CUtensorMap map;
-  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(planes), dims, strides, box, step,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult rc = g_encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(planes), dims, strides, box, step,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) {
     fail(FB_ECUDA, "cuTensorMapEncodeTiled failed with code %d for planes [%d,3,%d,16]", (int)rc, G, O);
     return false;
   }
-  if (cache.size() >= 8192) cache.clear();
-  cache.emplace(key, map);
+  if (g_maps.size() >= 16384) g_maps.clear();
+  g_maps.emplace(key, map);
+  *out = map;
+  return true;
+}
+
+bool group_row_tensor_map(const void* base, int elem_bytes, int O, int G, CUtensorMap* out) {
+  std::lock_guard<std::mutex> guard(g_map_lock);
+  if (!encoder_ready()) return false;
+  const MapKey key{base, O, G, 1 << 20 | elem_bytes};
+  auto found = g_maps.find(key);
+  if (found != g_maps.end()) {
+    *out = found->second;
+    return true;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)O, (cuuint64_t)G};
+  const cuuint64_t strides[1] = {(cuuint64_t)O * elem_bytes};
+  const cuuint32_t box[2] = {32, 2};
+  const cuuint32_t step[2] = {1, 1};
+  CUtensorMap map;
+  const CUresult rc = g_encode(&map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                               strides, box, step, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    fail(FB_ECUDA, "cuTensorMapEncodeTiled failed with code %d for a [%d,%d] tensor of %d-byte elements", (int)rc, G, O, elem_bytes);
+    return false;
+  }
+  if (g_maps.size() >= 16384) g_maps.clear();
+  g_maps.emplace(key, map);
   *out = map;
   return true;
 }

@@ -33,6 +33,9 @@ bool pdl_allowed();
 // `box_units` 32-row units.  Encoding is pure host work; descriptors are cached per
 // (address, O, G, box).  Returns false after recording the error.
 bool plane_tensor_map(const uint8_t* planes, int O, int G, int box_units, int box_runs, CUtensorMap* out);
+// Descriptor of a per-(group, row) tensor [G][O] of 1- or 2-byte elements (zero points, scales),
+// box = 32 rows x 2 groups; rows of the box beyond G read as zero.
+bool group_row_tensor_map(const void* base, int elem_bytes, int O, int G, CUtensorMap* out);
 
 // Launch with the programmatic-dependent-launch attribute (unless switched off): the kernel's
 // prologue may overlap the tail of the previous kernel in the stream.

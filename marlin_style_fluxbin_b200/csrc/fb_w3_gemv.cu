@@ -21,8 +21,10 @@
 //    floor(SMs / super-blocks) CTAs that split its rows, so the 32 KB of tables of a K block are
 //    built once per SM and shared by 16 warps.
 //  * A CTA that walks several K blocks (K > 4096) keeps two table sets (M = 1): the tables of
-//    the next K block are built while the current block's lookups run, one barrier per block.
+//    the next K block are built before the current block's lookups, one barrier per block.
 //    A warp whose rows are a single unit carries its sum across the K blocks in registers.
+//  * Scales and zero points of a unit are requested from global memory one unit ahead of their
+//    use, so HBM latency never sits between a unit's lookups and its result.
 //  * Two lookups are added with one packed fp32x2 add (an even-step and an odd-step partial sum
 //    per plane share a 64-bit register pair), which halves the adds of the main loop.
 //  * Launched with programmatic dependent launch: barrier set-up and the first weight copies
@@ -52,7 +54,7 @@ using namespace fb;
 
 constexpr int kUnitRows = 32;
 constexpr int kPlaneTile = kUnitRows * 16;      // 512 B: one plane of one group for a unit
-constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B staged per unit
+constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B of planes staged per unit
 constexpr int kWarps = 16;
 constexpr int kMaxM = 4;
 constexpr int kMaxSplits = 16;  // partial sums per output (one arrival count of 6 bits, 52-bit fixed-point sum)
@@ -117,15 +119,18 @@ struct Geom {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Two fp32 values in one 64-bit register pair, added lane-wise by one instruction.
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+// acc + {table entry at a0, table entry at a1}: the two loads land in the halves of one 64-bit
+// register pair, which the packed add consumes as it is.
+__device__ __forceinline__ uint64_t add2_lds(uint64_t acc, uint32_t a0, uint32_t a1) {
   uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  asm volatile(
+      "{\n\t.reg .f32 lo, hi;\n\t.reg .b64 both;\n\t"
+      "ld.shared.f32 lo, [%2];\n\t"
+      "ld.shared.f32 hi, [%3];\n\t"
+      "mov.b64 both, {lo, hi};\n\t"
+      "add.rn.f32x2 %0, %1, both;\n\t}"
+      : "=l"(r)
+      : "l"(acc), "r"(a0), "r"(a1));
   return r;
 }
 // Shared-memory load at a 32-bit address plus a compile-time offset (folded into the instruction).
@@ -150,15 +155,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   unsigned char* const lut = smem;
   // Every warp owns a private ring of kStages staged units, [stage][group half * 3 + plane][32 rows
   // x 16 B], and one mbarrier per stage: warps never wait for one another between table builds.
-  unsigned char* const ring = smem + G_::kRingOffset;
-  uint64_t* const full_bars = reinterpret_cast<uint64_t*>(smem + G_::kBarOffset);
+  const uint32_t ring_u32 = smem_u32(smem + G_::kRingOffset) + (uint32_t)(warp * kStages * kUnitBytes);
+  const uint32_t bars_u32 = smem_u32(smem + G_::kBarOffset) + (uint32_t)(warp * kStages * 8);
 
   // The next kernel in the stream may be scheduled as soon as this grid's CTAs leave; it orders
   // itself after this grid with its own wait before touching activations or scratch.
   pdl_launch_dependents();
 
   if (threadIdx.x < kWarps * kStages) {
-    mbar_init(smem_u32(&full_bars[threadIdx.x]), 1);  // the issuing lane's expect_tx
+    mbar_init(smem_u32(smem + G_::kBarOffset) + threadIdx.x * 8, 1);  // the issuing lane's expect_tx
     mbar_init_fence();
   }
   __syncthreads();
@@ -174,37 +179,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
     while (j + 1 < p.n_mats && ru >= p.mats[j + 1].ru_begin) ++j;
     return j;
   };
-  bool dead = false;
-  // Stage unit (kb_, ru) into ring slot `slot`: one tiled copy brings all six runs (lane 0 announces
-  // the bytes and issues it).  The slot is free: the warp itself finished reading it (all lanes
-  // pass a __syncwarp before this is called).
-  auto issue_unit = [&](int slot, int kb_, int ru) {
-    const int ngroups = min(2, p.G - 2 * kb_);
-    const uint32_t bar = smem_u32(&full_bars[warp * kStages + slot]);
-    if (ngroups == 2) {
-      if (lane == 0) {
-        const int j = locate(ru);
-        mbar_expect_tx(bar, (uint32_t)kUnitBytes);
-        asm volatile(
-            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-                smem_u32(ring + (size_t)(warp * kStages + slot) * kUnitBytes)),
-            "l"(&p.plane_maps[j]), "r"(0), "r"(ru - p.mats[j].ru_begin), "r"(6 * kb_), "r"(bar)
-            : "memory");
-      }
-      return;
-    }
-    // a single trailing group: three plain runs
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(3 * kPlaneTile));
-    __syncwarp();
-    if (lane < 3) {
-      const W3Matrix& mat = p.mats[locate(ru)];
-      const uint8_t* src = mat.planes + (((size_t)(2 * kb_) * 3 + lane) * mat.O + (size_t)(ru - mat.ru_begin) * kUnitRows) * 16;
-      bulk_g2s(smem_u32(ring + ((size_t)(warp * kStages + slot) * 6 + lane) * kPlaneTile), src, (uint32_t)kPlaneTile, bar);
-    }
-  };
   // Final value of one output element: rounded to the 16-bit dtype, then the optional residual
   // is added and the sum rounded again (what separate Linear and add kernels produce).
-  auto emit = [&](const W3Matrix& mat, int m, int lrow, float value) {
+  auto emit = [&](int m, int ru, float value) {
+    const W3Matrix& mat = p.mats[locate(ru)];
+    const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
     if (p.push_world > 0) {  // one 8-byte store {value, mark = 1} into every rank's exchange buffer
       const unsigned long long slot = (1ull << 32) | (unsigned long long)__float_as_uint(value);
       for (int r = 0; r < p.push_world; ++r)
@@ -219,8 +198,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   const int rb = lane & 3, rh = (lane >> 2) & 1, rw = (lane >> 3) & 3;
   // Per-lane constants of the rotated walk, all as 32-bit shared-memory addresses / offsets so
   // that the hot loop does no 64-bit pointer arithmetic.  A lookup is: one 4-way byte dot product
-  // (entry * stride + table address), the shared-memory load, and half a packed add.
-  const uint32_t lut_u32 = smem_u32(lut), ring_u32 = smem_u32(ring);
+  // (entry * stride + table address), the shared-memory load, and half a packed add.  The table
+  // addresses xl[] point into the table set in use and are flipped to the other set per K block.
+  const uint32_t lut_u32 = smem_u32(lut);
   uint32_t sel[4], xl[2][4][4], woff[2][4];
 #pragma unroll
   for (int b = 0; b < 4; ++b) sel[b] = 128u << (8 * ((b + rb) & 3));  // weight 128 at byte (b+rb)%4
@@ -228,7 +208,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
     for (int jw = 0; jw < 4; ++jw) {
-      woff[jh][jw] = (uint32_t)(((jh ^ rh) * 3) * kPlaneTile + ((jw + rw) & 3) * 4);
+      woff[jh][jw] = (uint32_t)(((jh ^ rh) * 3) * kPlaneTile + ((jw + rw) & 3) * 4 + lane * 16);
 #pragma unroll
       for (int b = 0; b < 4; ++b) xl[jh][jw][b] = lut_u32 + 64u * (jh ^ rh) + 16u * ((jw + rw) & 3) + 4u * ((b + rb) & 3);
     }
@@ -251,21 +231,84 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   const int kb_begin = sb * p.S, nS = min(p.S, p.nKB - kb_begin);
   const int my_count = cta_count > warp ? (cta_count - warp + kWarps - 1) / kWarps : 0;
   const int my_tasks = nS * my_count;
-  int pf_task = 0, pf_slot = 0, pf_kb = kb_begin, pf_ru = cta_first + warp;  // the next task to stage
+  const int my_first = cta_first + warp, my_end = cta_first + cta_count;
+  // Staging of this warp's tasks, in task order, into its ring: lane 0 announces the bytes of a unit
+  // and issues ONE tiled copy that brings its six plane runs.  A slot is refilled only after the
+  // warp has finished reading it (all lanes pass a __syncwarp first).  The matrix a unit belongs
+  // to changes rarely: its descriptor and bounds are cached.
+  int pf_left = my_tasks, pf_slot = 0, pf_kb = kb_begin, pf_ru = my_first;  // the next task to stage
+  int pf_j = 0, pf_begin = 0, pf_end = -1;
   auto issue_next = [&]() {
-    issue_unit(pf_slot, pf_kb, pf_ru);
-    ++pf_task;
+    if (pf_ru < pf_begin || pf_ru >= pf_end) {
+      pf_j = locate(pf_ru);
+      pf_begin = p.mats[pf_j].ru_begin;
+      pf_end = pf_j + 1 < p.n_mats ? p.mats[pf_j + 1].ru_begin : p.nRU;
+    }
+    if (lane == 0) {
+      const uint32_t bar = bars_u32 + (uint32_t)(pf_slot * 8);
+      const uint32_t dst = ring_u32 + (uint32_t)(pf_slot * kUnitBytes);
+      if (2 * pf_kb + 1 < p.G) {
+        mbar_expect_tx(bar, (uint32_t)kUnitBytes);
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+            "l"(&p.plane_maps[pf_j]), "r"(0), "r"(pf_ru - pf_begin), "r"(6 * pf_kb), "r"(bar)
+            : "memory");
+      } else {  // a single trailing group: three plain runs
+        const W3Matrix& mat = p.mats[pf_j];
+        mbar_expect_tx(bar, (uint32_t)(3 * kPlaneTile));
+        for (int pl = 0; pl < 3; ++pl)
+          bulk_g2s(dst + (uint32_t)(pl * kPlaneTile),
+                   mat.planes + (((size_t)(2 * pf_kb) * 3 + pl) * mat.O + (size_t)(pf_ru - pf_begin) * kUnitRows) * 16, (uint32_t)kPlaneTile, bar);
+      }
+    }
+    --pf_left;
     pf_slot = pf_slot + 1 == kStages ? 0 : pf_slot + 1;
     pf_ru += kWarps;
-    if (pf_ru >= cta_first + cta_count) {
-      pf_ru = cta_first + warp;
+    if (pf_ru >= my_end) {
+      pf_ru = my_first;
       ++pf_kb;
     }
   };
   // Weights never change, so staging needs no wait.  Only one unit per warp goes out before the
-  // wait on the previous kernel: the whole grid's requests are served in order, and the small
-  // activation loads that follow the wait must not queue behind 20 MB of weights.
-  if (my_tasks > 0) issue_next();
+  // wait on the previous kernel: requests are served in order, and a whole grid's worth of weights
+  // ahead of the wait slows the tail of the kernel still running and the small activation loads
+  // that follow the wait.
+  if (pf_left > 0) issue_next();
+
+  // Scales and zero points of a task come straight from global memory (one coalesced run per
+  // group), requested ONE TASK AHEAD of their use so that HBM latency never sits between a
+  // unit's lookups and its result.  Half jh of a lane's walk covers group 2*kb + (jh ^ rh).
+  uint32_t nx_scale[2] = {0u, 0u}, nx_zero[2] = {4u, 4u};
+  int ax_j = 0, ax_begin = 0, ax_end = -1;
+  bool any_zeros = false;
+  for (int j = 0; j < p.n_mats; ++j) any_zeros = any_zeros || p.mats[j].zeros != nullptr;
+  auto request_aux = [&](int kb_, int ru) {
+    if (ru < ax_begin || ru >= ax_end) {  // entering another matrix of the launch: rare
+      ax_j = locate(ru);
+      ax_begin = p.mats[ax_j].ru_begin;
+      ax_end = ax_j + 1 < p.n_mats ? p.mats[ax_j + 1].ru_begin : p.nRU;
+    }
+    const W3Matrix& mat = p.mats[ax_j];
+    const int lrow = (ru - ax_begin) * kUnitRows + lane;
+#pragma unroll
+    for (int jh = 0; jh < 2; ++jh) {
+      const int g = min(2 * kb_ + (jh ^ rh), p.G - 1);  // an odd G: the empty half reads a valid address, its term is dropped
+      const int at = g * mat.O + lrow;                  // G * O < 2^24
+      asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(nx_scale[jh]) : "l"(mat.scales + at));
+      nx_zero[jh] = 4u;
+      if (mat.zeros) asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(nx_zero[jh]) : "l"(mat.zeros + at));
+    }
+  };
+  if (my_tasks > 0) request_aux(kb_begin, my_first);  // constant data: may precede the wait as well
+  // the walk constants are computed here, while the launch waits for the previous kernel anyway
+#pragma unroll
+  for (int jh = 0; jh < 2; ++jh)
+#pragma unroll
+    for (int jw = 0; jw < 4; ++jw) {
+      asm volatile("" : "+r"(woff[jh][jw]));
+#pragma unroll
+      for (int b = 0; b < 4; ++b) asm volatile("" : "+r"(xl[jh][jw][b]));
+    }
 
   // Everything below reads activations and writes scratch / outputs of this stream.
   pdl_wait_prior_grid();
@@ -312,7 +355,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
     inv_rms = rsqrtf(ss / (float)p.K + p.eps);
     __syncthreads();
   }
-  for (int t = 1; t < kStages && t < my_tasks; ++t) issue_next();  // the rest of the ring, behind the activation loads
+  for (int t = 1; t < kStages && pf_left > 0; ++t) issue_next();  // the rest of the ring, behind the activation loads
 
   // ---- build the 32 tables of K block kb_ into table set `set`: lane = table; warp w owns the
   // entries whose low nibble is w, so that the walk over the high nibble unrolls with constant
@@ -399,87 +442,58 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       if (((unsigned)pend_old[m] & 63u) == (unsigned)(p.nSB - 1)) {  // rare: one contribution in nSB
-        const W3Matrix& owner = p.mats[locate(pend_ru)];
-        const int lrow = (pend_ru - owner.ru_begin) * kUnitRows + lane;
         const unsigned long long total = pend_old[m] + pend_add[m];
         float value = __ll2float_rn((long long)total >> 12) * 1.4901161193847656e-08f;  // 2^-26
         if ((total >> 6) & 63ull) value = __int_as_float(0x7fc00000);
-        emit(owner, m, lrow, value);
+        emit(m, pend_ru, value);
         p.combine[(size_t)m * p.O + pend_ru * kUnitRows + lane] = 0ull;
       }
     }
     pend_ru = -1;
   };
-  auto contribute = [&](int m, int ru, int row, float v) {
+  auto contribute = [&](int m, int ru, float v) {
     if (m == 0) settle();  // the previous unit's answers have long arrived
     const bool fits = fabsf(v) < 2097152.f;  // 2^21: sixteen of them stay inside 52 bits
     pend_add[m] = fits ? ((unsigned long long)__float2ll_rn(v * 67108864.f) << 12) + 1ull : 65ull;
     asm volatile("atom.add.relaxed.gpu.global.u64 %0, [%1], %2;"
                  : "=l"(pend_old[m])
-                 : "l"(p.combine + (size_t)m * p.O + row), "l"(pend_add[m])
+                 : "l"(p.combine + (size_t)m * p.O + ru * kUnitRows + lane), "l"(pend_add[m])
                  : "memory");
     pend_ru = ru;
   };
 
-  // A warp with a single unit carries its sum over the K blocks of the super-block in registers;
-  // with more units the running sums of a super-block go through the L2-resident partials.
-  const bool in_registers = my_count == 1;
+  // What becomes of a unit's sum over one K block (decided once):
+  //   0 group partials to the fp32 workspace   1 final (a single K block): emit
+  //   2 carried in registers over the K blocks (a warp with one unit), then combined
+  //   3 running sum through the L2-resident partials (several units and several K blocks)
+  //   4 one K block per CTA: combined at once
+  const int mode = p.group_partials ? 0 : (p.nKB == 1 ? 1 : (nS == 1 ? 4 : (my_count == 1 ? 2 : 3)));
   float carried[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) carried[m] = 0.f;
   int c_slot = 0;
   uint32_t c_phase = 0;
+  bool dead = false;
   float sx_cur[M][2], sx_nxt[M][2];
 
-  // ---- the units of this warp for K block kb = kb_begin + s, tables in set SET ----
-  auto run_block = [&](auto set_tag, int s) {
-    constexpr int kSetOffset = decltype(set_tag)::value * G_::kLutBytes;
+  // ---- the units of this warp for K block kb = kb_begin + s ----
+  auto run_block = [&](int s) {
     const int kb = kb_begin + s;
-    int cur_j = 0, cur_begin = 0, cur_end = -1, cur_O = 0;
-    const unsigned short* cur_scales = nullptr;
-    const uint8_t* cur_zeros = nullptr;
-    // half jh of this lane's walk covers group 2*kb + (jh ^ rh); an odd G leaves the last one empty
-    const int g_of[2] = {2 * kb + rh, 2 * kb + (rh ^ 1)};
-    const bool has[2] = {g_of[0] < p.G, g_of[1] < p.G};
-    for (int i = 0; i < my_count; ++i) {
-      const int ru = cta_first + i * kWarps + warp;
-      const int row = ru * kUnitRows + lane;  // in the concatenated row space
-      if (ru < cur_begin || ru >= cur_end) {  // entering another matrix of the launch: rare
-        cur_j = locate(ru);
-        cur_begin = p.mats[cur_j].ru_begin;
-        cur_end = cur_j + 1 < p.n_mats ? p.mats[cur_j + 1].ru_begin : p.nRU;
-        cur_O = p.mats[cur_j].O;
-        cur_scales = p.mats[cur_j].scales;
-        cur_zeros = p.mats[cur_j].zeros;
+    const bool last_block = s + 1 == nS;
+    // an odd G leaves the second group of the last K block empty
+    const bool has[2] = {2 * kb + rh < p.G, 2 * kb + (rh ^ 1) < p.G};
+    for (int ru = my_first; ru < my_end; ru += kWarps) {
+      // this task's scales and zero points were requested a task ago; now request the next task's
+      const uint32_t sbits[2] = {nx_scale[0], nx_scale[1]}, zp[2] = {nx_zero[0], nx_zero[1]};
+      {
+        const bool wraps = ru + kWarps >= my_end;
+        if (!wraps || !last_block) request_aux(wraps ? kb + 1 : kb, wraps ? my_first : ru + kWarps);
       }
-      const W3Matrix& mat = p.mats[cur_j];
-      const int lrow = (ru - cur_begin) * kUnitRows + lane;
-      // scales and zero points straight from global memory (one coalesced 64-byte run per group):
-      // requested now, needed only after the lookups
-      // (volatile, so that the requests stay HERE and their first use stays after the lookups:
-      // left to itself the compiler may move the pair together and expose the round trip)
-      uint32_t sbits[2] = {0u, 0u}, zp[2] = {4u, 4u};
-      if (!dead) {
-#pragma unroll
-        for (int jh = 0; jh < 2; ++jh)
-          if (has[jh]) {
-            const int at = g_of[jh] * cur_O + lrow;  // G * O < 2^24
-            asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sbits[jh]) : "l"(cur_scales + at));
-            if (cur_zeros) asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(zp[jh]) : "l"(cur_zeros + at));
-          }
-      }
-      bool ok = dead ? false : mbar_wait_bounded(smem_u32(&full_bars[warp * kStages + c_slot]), c_phase);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok && !dead) {
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars_u32 + (uint32_t)(c_slot * 8), c_phase))) {
+        if (lane == 0) atomicExch(p.status, 1u);  // the copy never landed: give up, keep the barriers
         dead = true;
-        if (lane == 0) atomicExch(p.status, 1u);
+        return;
       }
-      // later K blocks of the super-block add to the partial this same thread stored before
-      float prev[M];
-#pragma unroll
-      for (int m = 0; m < M; ++m)
-        prev[m] = (s > 0 && !in_registers && !dead && !p.group_partials) ? __ldcg(&p.partials[((size_t)sb * M + m) * p.O + row]) : 0.f;
-
       // per activation row, group half and plane: an (even byte step, odd byte step) pair of sums
       uint64_t acc[M][2][3];
       float corr[M][2];
@@ -491,8 +505,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
 #pragma unroll
           for (int pl = 0; pl < 3; ++pl) acc[m][jh][pl] = 0ull;
         }
-
-      if (!dead) {
+      {
         // the rounding correction needs the zero points during the lookups (code - zero = +/-3 is
         // code 7 / 1 at zero point 4 and code 6 / 0 at zero point 3)
         uint32_t flip[2] = {0u, 0u};
@@ -500,39 +513,32 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
           flip[0] = zp[0] == 3u ? 0xffffffffu : 0u;
           flip[1] = zp[1] == 3u ? 0xffffffffu : 0u;
         }
-        const uint32_t wbase = ring_u32 + (uint32_t)((warp * kStages + c_slot) * kUnitBytes + lane * 16);
-        // staged words are fetched one (half, word) step ahead of their use: six live registers
-        auto fetch = [&](int jh, int jw, uint32_t (&dst)[3]) {
-          const uint32_t wa = wbase + woff[jh][jw];
+        const uint32_t wbase = ring_u32 + (uint32_t)(c_slot * kUnitBytes);
+        // staged words are fetched one (half, word) step ahead of their use, into two register
+        // sets used in turn
+        auto fetch = [&](int step, uint32_t (&dst)[3]) {
+          const uint32_t wa = wbase + woff[step >> 2][step & 3];
           asm volatile("ld.shared.u32 %0, [%1];" : "=r"(dst[0]) : "r"(wa));
           asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[1]) : "r"(wa), "n"(kPlaneTile));
           asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(dst[2]) : "r"(wa), "n"(2 * kPlaneTile));
         };
-        uint32_t cur[3], nxt[3];
-        fetch(0, 0, cur);
-#pragma unroll
-        for (int step = 0; step < 8; ++step) {
+        auto walk = [&](int step, const uint32_t (&w)[3]) {
           const int jh = step >> 2, jw = step & 3;
-          if (step + 1 < 8) fetch((step + 1) >> 2, (step + 1) & 3, nxt);
           uint32_t plus3 = 0, minus3 = 0;
           if (CORRECT) {
-            const uint32_t low = cur[0] ^ flip[jh];
-            plus3 = low & cur[1] & ~cur[2];   // code - zero = +3 (the stored high plane is inverted)
-            minus3 = low & ~cur[1] & cur[2];  // code - zero = -3
+            const uint32_t low = w[0] ^ flip[jh];
+            plus3 = low & w[1] & ~w[2];   // code - zero = +3 (the stored high plane is inverted)
+            minus3 = low & ~w[1] & w[2];  // code - zero = -3
           }
 #pragma unroll
           for (int bp = 0; bp < 2; ++bp) {  // byte steps 2bp (even) and 2bp + 1 (odd) make one packed add
 #pragma unroll
             for (int pl = 0; pl < 3; ++pl) {
-              const uint32_t a0 = lookup_address(cur[pl], 2 * bp, xl[jh][jw][2 * bp]);
-              const uint32_t a1 = lookup_address(cur[pl], 2 * bp + 1, xl[jh][jw][2 * bp + 1]);
+              const uint32_t a0 = lookup_address(w[pl], 2 * bp, xl[jh][jw][2 * bp]);
+              const uint32_t a1 = lookup_address(w[pl], 2 * bp + 1, xl[jh][jw][2 * bp + 1]);
 #pragma unroll
-              for (int m = 0; m < M; ++m) {
-                // activation row m sits m * 128 bytes further (M > 1 has a single table set)
-                const float v0 = M == 1 ? lds_at<kSetOffset>(a0) : lds_at<0>(a0 + (uint32_t)(m * 128));
-                const float v1 = M == 1 ? lds_at<kSetOffset>(a1) : lds_at<0>(a1 + (uint32_t)(m * 128));
-                acc[m][jh][pl] = add2(acc[m][jh][pl], pack2(v0, v1));
-              }
+              for (int m = 0; m < M; ++m)  // activation row m sits m * 128 bytes further
+                acc[m][jh][pl] = add2_lds(acc[m][jh][pl], a0 + (uint32_t)(m * 128), a1 + (uint32_t)(m * 128));
             }
             if (CORRECT) {
 #pragma unroll
@@ -540,65 +546,83 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
                 const uint32_t ap = lookup_address(plus3, b, xl[jh][jw][b]);
                 const uint32_t am = lookup_address(minus3, b, xl[jh][jw][b]);
 #pragma unroll
-                for (int m = 0; m < M; ++m) {
-                  const float vp = M == 1 ? lds_at<kSetOffset>(ap) : lds_at<0>(ap + (uint32_t)(m * 128));
-                  const float vm = M == 1 ? lds_at<kSetOffset>(am) : lds_at<0>(am + (uint32_t)(m * 128));
-                  corr[m][jh] += vp - vm;
-                }
+                for (int m = 0; m < M; ++m) corr[m][jh] += lds_at<0>(ap + (uint32_t)(m * 128)) - lds_at<0>(am + (uint32_t)(m * 128));
               }
             }
           }
+        };
+        uint32_t wa[3], wb[3];
+        fetch(0, wa);
 #pragma unroll
-          for (int pl = 0; pl < 3; ++pl) cur[pl] = nxt[pl];
+        for (int step = 0; step < 8; step += 2) {
+          fetch(step + 1, wb);
+          walk(step, wa);
+          if (step + 2 < 8) fetch(step + 2, wa);
+          walk(step + 1, wb);
         }
       }
 
       // all lanes are done with the staged bytes: the slot takes this warp's task kStages ahead
       __syncwarp();
-      if (!dead && pf_task < my_tasks) issue_next();
+      if (pf_left > 0) issue_next();
       if (++c_slot == kStages) {
         c_slot = 0;
         c_phase ^= 1u;
       }
 
-      if (!dead) {
-        asm volatile("" : "+r"(sbits[0]), "+r"(sbits[1]), "+r"(zp[0]), "+r"(zp[1]));  // first use: after the lookups
-        const float sc[2] = {bits_to_float((unsigned short)sbits[0], p.scale_dtype), bits_to_float((unsigned short)sbits[1], p.scale_dtype)};
+      const float sc[2] = {has[0] ? bits_to_float((unsigned short)sbits[0], p.scale_dtype) : 0.f,
+                           has[1] ? bits_to_float((unsigned short)sbits[1], p.scale_dtype) : 0.f};
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float term[2];
+      for (int m = 0; m < M; ++m) {
+        float term[2];
 #pragma unroll
-          for (int jh = 0; jh < 2; ++jh) {
-            float d = sum2(acc[m][jh][0]) + 2.f * sum2(acc[m][jh][1]) - 4.f * sum2(acc[m][jh][2]);
-            if (cur_zeros) d += (4.f - (float)zp[jh]) * sx_cur[m][jh];
-            term[jh] = d * sc[jh];
-            if (CORRECT) {
-              // rounding of scale*(+/-3) in the scale's dtype: the only inexact products
-              const float r3 = round_to(3.f * sc[jh], p.scale_dtype);
-              term[jh] += corr[m][jh] * (r3 - 3.f * sc[jh]);
-            }
+        for (int jh = 0; jh < 2; ++jh) {
+          float d = sum2(acc[m][jh][0]) + 2.f * sum2(acc[m][jh][1]) - 4.f * sum2(acc[m][jh][2]);
+          if (any_zeros) d += (4.f - (float)zp[jh]) * sx_cur[m][jh];
+          term[jh] = d * sc[jh];
+          if (CORRECT) {
+            // rounding of scale*(+/-3) in the scale's dtype: the only inexact products
+            const float r3 = round_to(3.f * sc[jh], p.scale_dtype);
+            term[jh] += corr[m][jh] * (r3 - 3.f * sc[jh]);
           }
-          const float both = term[0] + term[1];
-          if (p.group_partials) {
-            float* ws_out = reinterpret_cast<float*>(mat.out);
+        }
+        const float both = term[0] + term[1];
+        if (mode == 4) {
+          contribute(m, ru, both);
+        } else if (mode == 2) {
+          carried[m] += both;
+          if (last_block) contribute(m, ru, carried[m]);
+        } else if (mode == 3) {
+          // later K blocks of the super-block add to the partial this same thread stored before
+          float* slot = &p.partials[((size_t)sb * M + m) * p.O + ru * kUnitRows + lane];
+          const float v = (s > 0 ? __ldcg(slot) : 0.f) + both;
+          if (last_block)
+            contribute(m, ru, v);
+          else
+            *slot = v;
+        } else if (mode == 1) {
+          emit(m, ru, both);
+        } else {
+          const W3Matrix& mat = p.mats[locate(ru)];
+          float* ws_out = reinterpret_cast<float*>(mat.out);
+          const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
 #pragma unroll
-            for (int jh = 0; jh < 2; ++jh)
-              if (has[jh]) ws_out[(size_t)g_of[jh] * mat.O + lrow] = term[jh];
-          } else if (p.nKB == 1) {
-            emit(mat, m, lrow, both);
-          } else if (in_registers) {
-            carried[m] += both;
-            if (s + 1 == nS) contribute(m, ru, row, carried[m]);
-          } else {
-            const float v = prev[m] + both;
-            if (s + 1 < nS)
-              p.partials[((size_t)sb * M + m) * p.O + row] = v;
-            else
-              contribute(m, ru, row, v);
-          }
+          for (int jh = 0; jh < 2; ++jh)
+            if (has[jh]) ws_out[(size_t)(2 * kb + (jh ^ rh)) * mat.O + lrow] = term[jh];
         }
       }
     }
+  };
+  // the table addresses of the walk point into set 0; move them to the other set and back
+  uint32_t set_step = (uint32_t)G_::kLutBytes;
+  auto flip_tables = [&]() {
+#pragma unroll
+    for (int jh = 0; jh < 2; ++jh)
+#pragma unroll
+      for (int jw = 0; jw < 4; ++jw)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) xl[jh][jw][b] += set_step;
+    set_step = 0u - set_step;
   };
 
   build(kb_begin, 0, sx_cur);
@@ -608,13 +632,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
     if (G_::kLutSets == 2) {
       // the other table set is free (everyone left it at the last barrier): build ahead
       if (more) build(kb_begin + s + 1, (s + 1) & 1, sx_nxt);
-      if (s & 1)
-        run_block(std::integral_constant<int, G_::kLutSets - 1>{}, s);
-      else
-        run_block(std::integral_constant<int, 0>{}, s);
-      if (more) __syncthreads();
+      if (!dead) run_block(s);
+      if (more) {
+        __syncthreads();
+        flip_tables();
+      }
     } else {
-      run_block(std::integral_constant<int, 0>{}, s);
+      if (!dead) run_block(s);
       if (more) {
         __syncthreads();  // everyone has finished reading the tables
         build(kb_begin + s + 1, 0, sx_nxt);

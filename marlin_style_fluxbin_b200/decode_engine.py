@@ -12,6 +12,10 @@ kernels), which is the same-box baseline the packed path is compared with, and s
 tensor-parallel: q/k/v/gate/up by output rows, o/down by input groups; after each of the two
 row-split GEMVs of a layer the packed arm pushes its rows into every rank's exchange buffer from
 the GEMV epilogue (``tp_push``), the BF16 arm runs an NCCL sum-allreduce.
+
+Both arms end a step with the same LM-head launch (final RMSNorm, dense 16-bit GEMV, argmax and
+the next token's embedding row in one kernel).  ``truth_logits`` runs the same model in fp32
+(activations and dequantised weights) as the yardstick either arm is measured against.
 """
 from __future__ import annotations
 
@@ -88,9 +92,14 @@ class DecodeEngine:
 
     def __init__(self, shape: ModelShape, *, device, max_positions: int, arm: str = "w3", seed: int = 20260916,
                  tp_rank: int = 0, tp_size: int = 1, group=None, dtype=torch.bfloat16, fuse_inputs: bool = True,
-                 fuse_attention: bool = True, tp_push: bool | None = None):
+                 fuse_attention: bool = True, tp_push: bool | None = None, arithmetic: str = "structural"):
         if arm not in ("w3", "bf16"):
             raise ValueError("arm must be w3 or bf16")
+        if arithmetic not in ("structural", "decoded_bf16"):
+            raise ValueError("arithmetic must be structural or decoded_bf16")
+        # packed arm: "decoded_bf16" follows the weight dequantised in the scale's dtype
+        # (the reference's fast_corrected route), "structural" is scale * integer dot
+        self.decoded = arithmetic == "decoded_bf16"
         if shape.q_heads % tp_size or shape.kv_heads % tp_size or (shape.hidden // 128) % tp_size or (shape.intermediate // 128) % tp_size:
             raise ValueError("heads and group counts must divide by the tensor-parallel size")
         self.shape, self.device, self.arm, self.dtype = shape, torch.device(device), arm, dtype
@@ -139,11 +148,17 @@ class DecodeEngine:
         # activation buffers of one token
         buf = lambda n: torch.zeros(1, n, device=self.device, dtype=dtype)  # noqa: E731
         self.h, self.h_next, self.xn = buf(s.hidden), buf(s.hidden), buf(s.hidden)
-        self.q, self.k, self.v = buf(self.q_heads * s.head_dim), buf(self.kv_heads * s.head_dim), buf(self.kv_heads * s.head_dim)
-        self.q_rot, self.attn = buf(self.q_heads * s.head_dim), buf(self.q_heads * s.head_dim)
-        self.gate, self.up, self.act = buf(self.inter), buf(self.inter), buf(self.inter)
+        # q/k/v and gate/up live side by side, so that the dense arm's fused GEMMs write them in place
+        qw, kw = self.q_heads * s.head_dim, self.kv_heads * s.head_dim
+        self.qkv, self.gate_up = buf(qw + 2 * kw), buf(2 * self.inter)
+        self.q, self.k, self.v = self.qkv[:, :qw], self.qkv[:, qw:qw + kw], self.qkv[:, qw + kw:]
+        self.gate, self.up = self.gate_up[:, :self.inter], self.gate_up[:, self.inter:]
+        self.q_rot, self.attn, self.act = buf(qw), buf(qw), buf(self.inter)
         self.logits = torch.zeros(1, s.vocab, device=self.device, dtype=dtype)
         self.next_token = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.head_scratch = torch.zeros(_native.lm_head_scratch_bytes(), dtype=torch.uint8, device=self.device)
+        self.keep_logits = True      # False: the 16-bit logits never leave the chip (greedy decode only)
+        self._h_is_embedded = False  # the LM head of the previous step already wrote the next embedding row into h
         self.launches_per_step = 0
         self.attn_scratch = torch.zeros(_native.attn_scratch_bytes(self.q_heads), dtype=torch.uint8, device=self.device)
         if arm == "w3":
@@ -240,36 +255,35 @@ class DecodeEngine:
         return F.linear(last, self.lm_head)
 
     # ------------------------------------------------------------------ one decode step
-    def _linear(self, layer, which, x):
-        """BF16 arm: cuBLAS on the dense shard.  Returns a new tensor."""
-        return F.linear(x, layer.dense[which])
-
     @torch.inference_mode()
-    def step(self, token: torch.Tensor, position: int) -> None:
-        """Decode one token (``token``: device int64 ``[1]``) at ``position``; leaves the logits in
-        ``self.logits`` and the greedy choice in ``self.next_token``.  No allocation, no host sync."""
+    def step(self, token: torch.Tensor, position: int, next_forced: torch.Tensor | None = None, embed_next: bool = False) -> None:
+        """Decode one token (``token``: device int64 ``[1]``) at ``position``; leaves the greedy choice in
+        ``self.next_token`` (and the logits in ``self.logits`` while ``keep_logits``).  No allocation, no host sync.
+
+        ``embed_next``: the LM-head launch also writes the embedding row of the next token (``next_forced``,
+        a device int64 ``[1]``, or the greedy choice) into the hidden-state buffer, and the next ``step`` then
+        skips its gather launch."""
         s, nat = self.shape, _native
         w3 = self.arm == "w3"
         f16 = torch.float16
-        torch.index_select(self.embedding, 0, token, out=self.h)
+        launches = 0
+        if not self._h_is_embedded:
+            nat.embed_row(self.embedding, token, self.h)
+            launches += 1
         cos, sin = self.cos[position], self.sin[position]
         scale = 1.0 / math.sqrt(s.head_dim)
-        launches = 1
+        dec = self.decoded
         for index, layer in enumerate(self.layers):
             fuse = w3 and self.fuse_inputs
             if not fuse:
                 nat.rmsnorm(self.h, layer.ln1, self.xn, s.eps)
             if fuse:
                 nat.w3_gemv_fused_input(self.h, nat.W3_INPUT_RMSNORM, layer.ln1, s.eps, layer.qkv_list, 3,
-                                        self.q.numel() + 2 * self.k.numel(), f16, scratch=self.scratch)
+                                        self.qkv.numel(), f16, scratch=self.scratch, decoded_bf16=dec)
             elif w3:
-                nat.w3_gemv_multi(self.xn, layer.qkv_list, 3, self.q.numel() + 2 * self.k.numel(), f16, None, scratch=self.scratch)
+                nat.w3_gemv_multi(self.xn, layer.qkv_list, 3, self.qkv.numel(), f16, None, scratch=self.scratch, decoded_bf16=dec)
             else:
-                qkv = self._linear(layer, "qkv", self.xn)
-                self.q.copy_(qkv[:, :self.q.numel()])
-                self.k.copy_(qkv[:, self.q.numel():self.q.numel() + self.k.numel()])
-                self.v.copy_(qkv[:, self.q.numel() + self.k.numel():])
-                launches += 3
+                torch.mm(self.xn, layer.dense["qkv"].t(), out=self.qkv)  # q, k, v are views of this buffer
             if self.fuse_attention:
                 nat.attn_decode_fused(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.k_cache[index],
                                       self.v_cache[index], self.attn, position, s.eps, scale, self.attn_scratch)
@@ -279,56 +293,74 @@ class DecodeEngine:
                 nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale, self.attn_scratch)
             if self.tp_push:
                 site = self._sites[0]
-                nat.w3_gemv_push(self.attn, 0, None, 0.0, layer.o_push, self.attn.shape[-1], f16, site["push"], scratch=self.scratch)
+                nat.w3_gemv_push(self.attn, 0, None, 0.0, layer.o_push, self.attn.shape[-1], f16, site["push"], scratch=self.scratch,
+                                 decoded_bf16=dec)
                 nat.tp_reduce(site["parts"], self.tp_size, self.h, self.h_next, site["status"])
             elif w3:
-                nat.w3_gemv_multi(self.attn, layer.o_list, 1, s.hidden, f16, None, scratch=self.scratch)
+                nat.w3_gemv_multi(self.attn, layer.o_list, 1, s.hidden, f16, None, scratch=self.scratch, decoded_bf16=dec)
+            elif self.tp_rank == 0:
+                torch.addmm(self.h, self.attn, layer.dense["o"].t(), out=self.h_next)  # the residual rides in the GEMM epilogue
             else:
                 torch.mm(self.attn, layer.dense["o"].t(), out=self.h_next)
-                if self.tp_rank == 0:
-                    self.h_next.add_(self.h)
-                    launches += 1
             if not self.tp_push:
                 self._allreduce(self.h_next)
             if not fuse:
                 nat.rmsnorm(self.h_next, layer.ln2, self.xn, s.eps)
             if fuse:
                 nat.w3_gemv_fused_input(self.h_next, nat.W3_INPUT_RMSNORM, layer.ln2, s.eps, layer.gu_list, 2, 2 * self.inter, f16,
-                                        scratch=self.scratch)
+                                        scratch=self.scratch, decoded_bf16=dec)
             elif w3:
-                nat.w3_gemv_multi(self.xn, layer.gu_list, 2, 2 * self.inter, f16, None, scratch=self.scratch)
+                nat.w3_gemv_multi(self.xn, layer.gu_list, 2, 2 * self.inter, f16, None, scratch=self.scratch, decoded_bf16=dec)
             else:
-                gu = self._linear(layer, "gate_up", self.xn)
-                self.gate.copy_(gu[:, :self.inter])
-                self.up.copy_(gu[:, self.inter:])
-                launches += 2
+                torch.mm(self.xn, layer.dense["gate_up"].t(), out=self.gate_up)  # gate, up are views of this buffer
             if not fuse:
                 nat.silu_mul(self.gate, self.up, self.act)
             if self.tp_push:
                 site = self._sites[1]
                 if fuse:
                     nat.w3_gemv_push(self.gate, nat.W3_INPUT_SILU_MUL, self.up, 0.0, layer.down_push, self.inter, f16, site["push"],
-                                     scratch=self.scratch)
+                                     scratch=self.scratch, decoded_bf16=dec)
                 else:
-                    nat.w3_gemv_push(self.act, 0, None, 0.0, layer.down_push, self.inter, f16, site["push"], scratch=self.scratch)
+                    nat.w3_gemv_push(self.act, 0, None, 0.0, layer.down_push, self.inter, f16, site["push"], scratch=self.scratch,
+                                     decoded_bf16=dec)
                 nat.tp_reduce(site["parts"], self.tp_size, self.h_next, self.h, site["status"])
             elif fuse:
                 nat.w3_gemv_fused_input(self.gate, nat.W3_INPUT_SILU_MUL, self.up, 0.0, layer.down_list, 1, s.hidden, f16,
-                                        scratch=self.scratch)
+                                        scratch=self.scratch, decoded_bf16=dec)
             elif w3:
-                nat.w3_gemv_multi(self.act, layer.down_list, 1, s.hidden, f16, None, scratch=self.scratch)
+                nat.w3_gemv_multi(self.act, layer.down_list, 1, s.hidden, f16, None, scratch=self.scratch, decoded_bf16=dec)
+            elif self.tp_rank == 0:
+                torch.addmm(self.h_next, self.act, layer.dense["down"].t(), out=self.h)
             else:
                 torch.mm(self.act, layer.dense["down"].t(), out=self.h)
-                if self.tp_rank == 0:
-                    self.h.add_(self.h_next)
-                    launches += 1
             if not self.tp_push:
                 self._allreduce(self.h)
-            launches += (6 if fuse else 9) - (1 if self.fuse_attention else 0) + (2 if self.tp_size > 1 else 0)
-        nat.rmsnorm(self.h, self.final_norm, self.xn, s.eps)
-        torch.mm(self.xn, self.lm_head.t(), out=self.logits)
-        torch.argmax(self.logits, dim=-1, out=self.next_token)
-        self.launches_per_step = launches + 3
+            launches += (5 if fuse else 8) + (0 if self.fuse_attention else 1) + (2 if self.tp_size > 1 else 0)
+        # final RMSNorm + LM head + argmax (+ the next token's embedding row, written over the hidden
+        # state once every CTA has staged it) in one launch
+        nat.lm_head_argmax(self.h, self.final_norm, s.eps, self.lm_head, self.next_token, logits=self.logits if self.keep_logits else None,
+                           forced_next=next_forced if embed_next else None, embedding=self.embedding if embed_next else None,
+                           next_hidden=self.h if embed_next else None, scratch=self.head_scratch)
+        self._h_is_embedded = embed_next
+        self.launches_per_step = launches + 1
+
+    def check_status(self) -> None:
+        """After a synchronise: raise if a bounded device-side wait gave up (W3 GEMV staging: 1, tensor-core
+        kernel: 3, tensor-parallel reduce: 4).  The scratch and exchange words are re-zeroed so that the
+        engine is usable again; the outputs of the failed run are invalid."""
+        codes = {}
+        if self.arm == "w3":
+            codes["w3 scratch"] = int(self.scratch[:4].view(torch.int32)[0])
+        if self.tp_push:
+            codes["tp exchange"] = int(self._xchg[:1].view(torch.int32)[0])
+        bad = {k: v for k, v in codes.items() if v}
+        if bad:
+            if self.arm == "w3":
+                self.scratch.zero_()
+            if self.tp_push:
+                self._xchg.zero_()
+            self.head_scratch.zero_()
+            raise RuntimeError(f"a device-side wait expired: {bad}; scratch re-zeroed, results of that run are invalid")
 
     # ------------------------------------------------------------------ whole continuation
     @torch.inference_mode()
@@ -336,6 +368,7 @@ class DecodeEngine:
         """Eagerly decode ``steps`` tokens from ``start``; returns (tokens fed, greedy predictions, logits)."""
         fed, predicted, logits = [], [], []
         token = first_token.reshape(1).to(self.device)
+        self._h_is_embedded = False
         for i in range(steps):
             if forced is not None:
                 token = forced[i:i + 1].to(self.device)
@@ -344,13 +377,16 @@ class DecodeEngine:
             predicted.append(self.next_token.clone())
             logits.append(self.logits.clone())
             token = self.next_token
+        torch.cuda.synchronize(self.device)
+        self.check_status()
         return torch.cat(fed), torch.cat(predicted), torch.cat(logits)
 
     @torch.inference_mode()
     def capture(self, first_token: torch.Tensor, start: int, steps: int, forced: torch.Tensor | None = None):
         """Capture the whole continuation in one CUDA graph (greedy feedback through a device
         buffer, or teacher-forced tokens).  Returns ``(graph, predictions [steps], last logits)``;
-        replaying needs the KV cache prefix in place (later positions are simply overwritten)."""
+        replaying needs the KV cache prefix in place (later positions are simply overwritten).
+        After a replay, synchronise and call ``check_status``."""
         self.token_in = first_token.reshape(1).to(self.device).clone()
         forced_dev = None if forced is None else forced.to(self.device).clone()
         predictions = torch.zeros(steps, dtype=torch.long, device=self.device)
@@ -361,13 +397,15 @@ class DecodeEngine:
         stream.wait_stream(torch.cuda.current_stream(self.device))
 
         def body():
-            token = self.token_in
+            # one gather for the first token; every later step finds its embedding row written by the
+            # LM-head launch of the step before (the forced token, or the greedy choice)
+            self._h_is_embedded = False
             for i in range(steps):
-                if forced_dev is not None:
-                    token = forced_dev[i:i + 1]
-                self.step(token, start + i)
+                last = i + 1 == steps
+                following = None if forced_dev is None or last else forced_dev[i + 1:i + 2]
+                self.step(self.token_in if forced_dev is None else forced_dev[0:1], start + i, next_forced=following, embed_next=not last)
                 predictions[i:i + 1].copy_(self.next_token)
-                token = self.next_token
+            self._h_is_embedded = False
 
         with torch.cuda.stream(stream):
             self.step(self.token_in, start)  # warm-up: kernel attributes, scratch, cuBLAS handles
@@ -377,3 +415,46 @@ class DecodeEngine:
                 body()
         torch.cuda.current_stream(self.device).wait_stream(stream)
         return graph, predictions, self.logits
+
+    # ------------------------------------------------------------------ fp32 yardstick
+    @torch.inference_mode()
+    def truth_logits(self, input_ids: torch.Tensor, fed: torch.Tensor) -> torch.Tensor:
+        """Logits of the decode steps with fp32 activations and fp32 dequantised weights: the prompt
+        followed by the tokens fed at each step runs through ONE causal forward pass (cached decode equals
+        the full-prefix forward, reference tests/test_full_model_trial.py:34-55).  Weights are dequantised
+        layer by layer, scale * (code - zero) rounded once in the scale's dtype and widened; rotary
+        angles stay fp32.  Returns ``[steps, vocab]`` fp32.  Unsharded engines only."""
+        if self.tp_size != 1:
+            raise ValueError("the fp32 yardstick runs on an unsharded engine")
+        s = self.shape
+        tokens = torch.cat((input_ids.reshape(-1).to(self.device), fed.reshape(-1).to(self.device)))
+        t, steps = tokens.numel(), fed.numel()
+        h = self.embedding[tokens].float()
+        inv_freq = 1.0 / (s.rope_theta ** (torch.arange(0, s.head_dim, 2, device=self.device, dtype=torch.float32) / s.head_dim))
+        angles = torch.arange(t, device=self.device, dtype=torch.float32)[:, None] * inv_freq[None, :]
+        angles = torch.cat((angles, angles), dim=-1)
+        cos, sin = angles.cos().unsqueeze(0), angles.sin().unsqueeze(0)
+        rotate = lambda x: torch.cat((-x[..., s.head_dim // 2:], x[..., :s.head_dim // 2]), dim=-1)  # noqa: E731
+        norm = lambda x, w: w.float() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + s.eps))  # noqa: E731
+        dq = lambda lay: restore_planar_w3(lay, dtype=torch.float32)  # noqa: E731
+        previous = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            for layer in self.layers:
+                x = norm(h, layer.ln1)
+                q = F.linear(x, dq(layer.q)).reshape(t, s.q_heads, s.head_dim)
+                k = F.linear(x, dq(layer.k)).reshape(t, s.kv_heads, s.head_dim)
+                v = F.linear(x, dq(layer.v)).reshape(t, s.kv_heads, s.head_dim).transpose(0, 1)
+                q = norm(q, layer.q_norm).transpose(0, 1)
+                k = norm(k, layer.k_norm).transpose(0, 1)
+                q = q * cos + rotate(q) * sin
+                k = k * cos + rotate(k) * sin
+                attn = F.scaled_dot_product_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), is_causal=True, enable_gqa=True)
+                h = h + F.linear(attn[0].transpose(0, 1).reshape(t, -1), dq(layer.o))
+                x = norm(h, layer.ln2)
+                act = F.silu(F.linear(x, dq(layer.gate))) * F.linear(x, dq(layer.up))
+                h = h + F.linear(act, dq(layer.down))
+            last = norm(h[t - steps:], self.final_norm)
+            return F.linear(last, self.lm_head.float())
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = previous

@@ -75,6 +75,31 @@ def test_packed_arm_matches_dense_arm_and_graph_replays_exactly():
     assert torch.equal(predictions2, own)
 
 
+def test_both_arms_against_the_fp32_yardstick_and_decoded_weight_arithmetic():
+    """Neither 16-bit arm is the truth: both are measured against the same model run with fp32
+    activations and fp32 dequantised weights.  The packed arm with the dequantised-weight
+    arithmetic must not be further from it than the dense arm (whose weights carry one more
+    rounding, fp16 product to bf16)."""
+    from marlin_style_fluxbin_b200.decode_engine import DecodeEngine
+
+    shape, steps, prompt = small_shape(), 6, 20
+    ids = torch.randint(0, 640, (1, prompt), generator=torch.Generator().manual_seed(4))
+    dense = DecodeEngine(shape, device="cuda", max_positions=64, arm="bf16", seed=9)
+    first = dense.prefill(ids).argmax(-1)
+    fed, _, logits_dense = dense.decode(first, prompt, steps)
+    truth = dense.truth_logits(ids, fed)
+    assert tuple(truth.shape) == (steps, shape.vocab) and truth.dtype == torch.float32
+    gaps = {"bf16": nrmse(logits_dense, truth)}
+    for arithmetic in ("structural", "decoded_bf16"):
+        packed = DecodeEngine(shape, device="cuda", max_positions=64, arm="w3", seed=9, arithmetic=arithmetic)
+        packed.prefill(ids)
+        _, _, logits_packed = packed.decode(first, prompt, steps, forced=fed)
+        gaps[arithmetic] = nrmse(logits_packed, truth)
+        packed.check_status()
+    assert max(gaps.values()) < 0.02, gaps
+    assert gaps["decoded_bf16"] <= 1.25 * gaps["bf16"], gaps
+
+
 def test_fused_input_launches_match_separate_glue_kernels():
     """Six launches per layer (RMSNorm and the SwiGLU gate inside the GEMVs) against nine."""
     from marlin_style_fluxbin_b200.decode_engine import DecodeEngine
@@ -86,7 +111,7 @@ def test_fused_input_launches_match_separate_glue_kernels():
         engine = DecodeEngine(shape, device="cuda", max_positions=64, arm="w3", seed=7, fuse_inputs=fuse)
         first = engine.prefill(ids).argmax(-1)
         _, _, logits[fuse] = engine.decode(first, prompt, 4)
-        assert engine.launches_per_step == 4 + shape.layers * (5 if fuse else 8)
+        assert engine.launches_per_step == 2 + shape.layers * (5 if fuse else 8)  # gather, layers, fused LM head
     assert nrmse(logits[True], logits[False]) < 5e-3, nrmse(logits[True], logits[False])
 
 
