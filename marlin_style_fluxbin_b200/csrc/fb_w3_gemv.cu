@@ -25,8 +25,9 @@
 //    A warp whose rows are a single unit carries its sum across the K blocks in registers.
 //  * Scales and zero points of a unit are requested from global memory one unit ahead of their
 //    use, so HBM latency never sits between a unit's lookups and its result.
-//  * Two lookups are added with one packed fp32x2 add (an even-step and an odd-step partial sum
-//    per plane share a 64-bit register pair), which halves the adds of the main loop.
+//  * Two lookups are accumulated by one packed fp32x2 add or multiply-add (an even-step and an
+//    odd-step partial sum share a 64-bit register pair; the plane weights 1, 2, -4 ride in the
+//    multiply-add), which halves the arithmetic of the main loop and leaves four accumulators.
 //  * Launched with programmatic dependent launch: barrier set-up and the first weight copies
 //    come before griddepcontrol.wait; everything that reads activations or touches scratch
 //    comes after it.
@@ -76,6 +77,11 @@ struct W3Params {
   // One tiled-copy descriptor per matrix: the planes seen as uint32 [G*3][O/32][128], so that a
   // box of 6 x 1 x 128 is the six 512-byte runs of one unit (two groups x three planes).
   alignas(64) CUtensorMap plane_maps[kMaxMatrices];
+  // Scales and zero points as [G][O] tensors, box = 32 rows x 2 groups: the 128 + 64 bytes a unit
+  // needs of them are staged beside its planes.  Groups beyond G read as zero, which drops the
+  // empty half of the last K block of an odd G without any test in the kernel.
+  CUtensorMap scale_maps[kMaxMatrices];
+  CUtensorMap zero_maps[kMaxMatrices];
   const void* x;
   W3Matrix mats[kMaxMatrices];
   int n_mats;
@@ -111,8 +117,12 @@ struct Geom {
   static constexpr int kLutBytes = 256 << kStrideLog;
   static constexpr int kLutSets = M == 1 ? 2 : 1;
   static constexpr int kStages = M <= 2 ? 3 : 2;
+  // a staged unit: its planes, then (M <= 2; with 128 KB of tables there is no room) its scales at
+  // +3072 (2 groups x 64 B) and its zero points at +3200 (2 groups x 32 B)
+  static constexpr bool kStageAux = M <= 2;
+  static constexpr int kSlotBytes = kUnitBytes + (kStageAux ? 256 : 0);
   static constexpr int kRingOffset = kLutSets * kLutBytes;
-  static constexpr int kBarOffset = kRingOffset + kWarps * kStages * kUnitBytes;
+  static constexpr int kBarOffset = kRingOffset + kWarps * kStages * kSlotBytes;
   static constexpr int kSmemBytes = kBarOffset + kWarps * kStages * 8;
 };
 
@@ -133,6 +143,20 @@ __device__ __forceinline__ uint64_t add2_lds(uint64_t acc, uint32_t a0, uint32_t
       : "l"(acc), "r"(a0), "r"(a1));
   return r;
 }
+// acc + w * {table entry at a0, table entry at a1} with w = {2, 2} or {-4, -4}: the plane weights of
+// code - 4 = b0 + 2 b1 - 4 b2' applied as the entries are accumulated (products by 2 and 4 are exact).
+__device__ __forceinline__ uint64_t fma2_lds(uint64_t acc, uint32_t a0, uint32_t a1, uint64_t w) {
+  uint64_t r;
+  asm volatile(
+      "{\n\t.reg .f32 lo, hi;\n\t.reg .b64 both;\n\t"
+      "ld.shared.f32 lo, [%2];\n\t"
+      "ld.shared.f32 hi, [%3];\n\t"
+      "mov.b64 both, {lo, hi};\n\t"
+      "fma.rn.f32x2 %0, both, %4, %1;\n\t}"
+      : "=l"(r)
+      : "l"(acc), "r"(a0), "r"(a1), "l"(w));
+  return r;
+}
 // Shared-memory load at a 32-bit address plus a compile-time offset (folded into the instruction).
 template <int OFFSET>
 __device__ __forceinline__ float lds_at(uint32_t address) {
@@ -146,6 +170,39 @@ __device__ __forceinline__ float sum2(uint64_t v) {
   return lo + hi;
 }
 
+// Matrix that owns 32-row unit `ru` of the concatenated row space.
+__device__ __forceinline__ int locate_unit(const W3Params& p, int ru) {
+  int j = 0;
+  while (j + 1 < p.n_mats && ru >= p.mats[j + 1].ru_begin) ++j;
+  return j;
+}
+
+// Final value of one output element: rounded to the 16-bit dtype, then the optional residual is
+// added and the sum rounded again (what separate Linear and add kernels produce); or, for the
+// tensor-parallel push, one 8-byte store {value, mark = 1} into every rank's exchange buffer.
+// Reached once per output row: kept out of line, away from the main loop's registers and code.
+__device__ __forceinline__ void emit_row(const W3Params& p, int m, int ru, int lane, float value) {
+  const W3Matrix& mat = p.mats[locate_unit(p, ru)];
+  const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
+  if (p.push_world > 0) {
+    const unsigned long long slot = (1ull << 32) | (unsigned long long)__float_as_uint(value);
+    for (int r = 0; r < p.push_world; ++r)
+      asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p.push_data[r] + lrow), "l"(slot) : "memory");
+    return;
+  }
+  if (mat.residual) value = round_to(value, p.act_dtype) + load_act(mat.residual, p.act_dtype, m * mat.O + lrow);
+  store_act(mat.out, p.act_dtype, m * mat.O + lrow, value);
+}
+
+// The contributor that read back the last arrival count: fixed point to float, NaN if any partial
+// had no fixed-point form, emit, and leave the combine word zero for the next launch.
+__device__ __forceinline__ void emit_combined(const W3Params& p, int m, int ru, int lane, unsigned long long total) {
+  float value = __ll2float_rn((long long)total >> 12) * 1.4901161193847656e-08f;  // 2^-26
+  if ((total >> 6) & 63ull) value = __int_as_float(0x7fc00000);
+  emit_row(p, m, ru, lane, value);
+  p.combine[(size_t)m * p.O + ru * kUnitRows + lane] = 0ull;
+}
+
 template <int M, bool CORRECT>
 __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_constant__ W3Params p) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -155,7 +212,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   unsigned char* const lut = smem;
   // Every warp owns a private ring of kStages staged units, [stage][group half * 3 + plane][32 rows
   // x 16 B], and one mbarrier per stage: warps never wait for one another between table builds.
-  const uint32_t ring_u32 = smem_u32(smem + G_::kRingOffset) + (uint32_t)(warp * kStages * kUnitBytes);
+  const uint32_t ring_u32 = smem_u32(smem + G_::kRingOffset) + (uint32_t)(warp * kStages * G_::kSlotBytes);
   const uint32_t bars_u32 = smem_u32(smem + G_::kBarOffset) + (uint32_t)(warp * kStages * 8);
 
   // The next kernel in the stream may be scheduled as soon as this grid's CTAs leave; it orders
@@ -173,26 +230,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   const int sb = (int)blockIdx.y;
   const int cta_first = (int)blockIdx.x * p.units_per_slice + min((int)blockIdx.x, p.units_extra);
   const int cta_count = p.units_per_slice + ((int)blockIdx.x < p.units_extra ? 1 : 0);
-  // Matrix that owns 32-row unit `ru` of the concatenated row space.
-  auto locate = [&](int ru) {
-    int j = 0;
-    while (j + 1 < p.n_mats && ru >= p.mats[j + 1].ru_begin) ++j;
-    return j;
-  };
-  // Final value of one output element: rounded to the 16-bit dtype, then the optional residual
-  // is added and the sum rounded again (what separate Linear and add kernels produce).
-  auto emit = [&](int m, int ru, float value) {
-    const W3Matrix& mat = p.mats[locate(ru)];
-    const int lrow = (ru - mat.ru_begin) * kUnitRows + lane;
-    if (p.push_world > 0) {  // one 8-byte store {value, mark = 1} into every rank's exchange buffer
-      const unsigned long long slot = (1ull << 32) | (unsigned long long)__float_as_uint(value);
-      for (int r = 0; r < p.push_world; ++r)
-        asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p.push_data[r] + lrow), "l"(slot) : "memory");
-      return;
-    }
-    if (mat.residual) value = round_to(value, p.act_dtype) + load_act(mat.residual, p.act_dtype, m * mat.O + lrow);
-    store_act(mat.out, p.act_dtype, m * mat.O + lrow, value);
-  };
+  auto locate = [&](int ru) { return locate_unit(p, ru); };
+  auto emit = [&](int m, int ru, float value) { emit_row(p, m, ru, lane, value); };
 
   // Lane rotation (byte, half, word): at every step the 32 lanes hit 32 different tables.
   const int rb = lane & 3, rh = (lane >> 2) & 1, rw = (lane >> 3) & 3;
@@ -233,32 +272,40 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   const int my_tasks = nS * my_count;
   const int my_first = cta_first + warp, my_end = cta_first + cta_count;
   // Staging of this warp's tasks, in task order, into its ring: lane 0 announces the bytes of a unit
-  // and issues ONE tiled copy that brings its six plane runs.  A slot is refilled only after the
+  // and issues ONE tiled copy that brings its six plane runs (and two small ones for its scales and
+  // zero points).  A slot is refilled only after the
   // warp has finished reading it (all lanes pass a __syncwarp first).  The matrix a unit belongs
   // to changes rarely: its descriptor and bounds are cached.
   int pf_left = my_tasks, pf_slot = 0, pf_kb = kb_begin, pf_ru = my_first;  // the next task to stage
   int pf_j = 0, pf_begin = 0, pf_end = -1;
+  bool pf_zeros = false;
   auto issue_next = [&]() {
     if (pf_ru < pf_begin || pf_ru >= pf_end) {
       pf_j = locate(pf_ru);
       pf_begin = p.mats[pf_j].ru_begin;
       pf_end = pf_j + 1 < p.n_mats ? p.mats[pf_j + 1].ru_begin : p.nRU;
+      pf_zeros = p.mats[pf_j].zeros != nullptr;
     }
     if (lane == 0) {
       const uint32_t bar = bars_u32 + (uint32_t)(pf_slot * 8);
-      const uint32_t dst = ring_u32 + (uint32_t)(pf_slot * kUnitBytes);
-      if (2 * pf_kb + 1 < p.G) {
-        mbar_expect_tx(bar, (uint32_t)kUnitBytes);
-        asm volatile(
-            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-            "l"(&p.plane_maps[pf_j]), "r"(0), "r"(pf_ru - pf_begin), "r"(6 * pf_kb), "r"(bar)
-            : "memory");
-      } else {  // a single trailing group: three plain runs
-        const W3Matrix& mat = p.mats[pf_j];
-        mbar_expect_tx(bar, (uint32_t)(3 * kPlaneTile));
-        for (int pl = 0; pl < 3; ++pl)
-          bulk_g2s(dst + (uint32_t)(pl * kPlaneTile),
-                   mat.planes + (((size_t)(2 * pf_kb) * 3 + pl) * mat.O + (size_t)(pf_ru - pf_begin) * kUnitRows) * 16, (uint32_t)kPlaneTile, bar);
+      const uint32_t dst = ring_u32 + (uint32_t)(pf_slot * G_::kSlotBytes);
+      const int lru = pf_ru - pf_begin;
+      // the boxes are always whole: what lies beyond G reads as zero and still counts as bytes
+      mbar_expect_tx(bar, (uint32_t)(kUnitBytes + (G_::kStageAux ? 128 + (pf_zeros ? 64 : 0) : 0)));
+      asm volatile(
+          "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+          "l"(&p.plane_maps[pf_j]), "r"(0), "r"(lru), "r"(6 * pf_kb), "r"(bar)
+          : "memory");
+      if (G_::kStageAux) {
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                         dst + (uint32_t)kUnitBytes),
+                     "l"(&p.scale_maps[pf_j]), "r"(lru * kUnitRows), "r"(2 * pf_kb), "r"(bar)
+                     : "memory");
+        if (pf_zeros)
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                           dst + (uint32_t)(kUnitBytes + 128)),
+                       "l"(&p.zero_maps[pf_j]), "r"(lru * kUnitRows), "r"(2 * pf_kb), "r"(bar)
+                       : "memory");
       }
     }
     --pf_left;
@@ -275,9 +322,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   // that follow the wait.
   if (pf_left > 0) issue_next();
 
-  // Scales and zero points of a task come straight from global memory (one coalesced run per
-  // group), requested ONE TASK AHEAD of their use so that HBM latency never sits between a
-  // unit's lookups and its result.  Half jh of a lane's walk covers group 2*kb + (jh ^ rh).
+  // Without room in the ring (M > 2) the scales and zero points of a task come straight from global
+  // memory (one coalesced run per group), requested ONE TASK AHEAD of their use so that HBM latency
+  // never sits between a unit's lookups and its result.  Half jh of a lane's walk covers group
+  // 2*kb + (jh ^ rh).
   uint32_t nx_scale[2] = {0u, 0u}, nx_zero[2] = {4u, 4u};
   int ax_j = 0, ax_begin = 0, ax_end = -1;
   bool any_zeros = false;
@@ -299,7 +347,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
       if (mat.zeros) asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(nx_zero[jh]) : "l"(mat.zeros + at));
     }
   };
-  if (my_tasks > 0) request_aux(kb_begin, my_first);  // constant data: may precede the wait as well
+  if (!G_::kStageAux && my_tasks > 0) request_aux(kb_begin, my_first);  // constant data: may precede the wait as well
+  // staged form: this lane's scale / zero point of walk half 0 within a slot; half 1 is the other group
+  const uint32_t aux_scale0 = (uint32_t)(kUnitBytes + rh * 64 + lane * 2), aux_zero0 = (uint32_t)(kUnitBytes + 128 + rh * 32 + lane);
   // the walk constants are computed here, while the launch waits for the previous kernel anyway
 #pragma unroll
   for (int jh = 0; jh < 2; ++jh)
@@ -441,13 +491,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
     if (pend_ru < 0) return;
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-      if (((unsigned)pend_old[m] & 63u) == (unsigned)(p.nSB - 1)) {  // rare: one contribution in nSB
-        const unsigned long long total = pend_old[m] + pend_add[m];
-        float value = __ll2float_rn((long long)total >> 12) * 1.4901161193847656e-08f;  // 2^-26
-        if ((total >> 6) & 63ull) value = __int_as_float(0x7fc00000);
-        emit(m, pend_ru, value);
-        p.combine[(size_t)m * p.O + pend_ru * kUnitRows + lane] = 0ull;
-      }
+      if (((unsigned)pend_old[m] & 63u) == (unsigned)(p.nSB - 1))  // rare: one contribution in nSB
+        emit_combined(p, m, pend_ru, lane, pend_old[m] + pend_add[m]);
     }
     pend_ru = -1;
   };
@@ -482,10 +527,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
     const bool last_block = s + 1 == nS;
     // an odd G leaves the second group of the last K block empty
     const bool has[2] = {2 * kb + rh < p.G, 2 * kb + (rh ^ 1) < p.G};
+    int cu_begin = 0, cu_end = -1;
+    bool cu_zeros = false;
     for (int ru = my_first; ru < my_end; ru += kWarps) {
-      // this task's scales and zero points were requested a task ago; now request the next task's
-      const uint32_t sbits[2] = {nx_scale[0], nx_scale[1]}, zp[2] = {nx_zero[0], nx_zero[1]};
-      {
+      // unstaged form: this task's scales and zero points were requested a task ago; now request the next task's
+      uint32_t sbits[2] = {nx_scale[0], nx_scale[1]}, zp[2] = {nx_zero[0], nx_zero[1]};
+      if (!G_::kStageAux) {
         const bool wraps = ru + kWarps >= my_end;
         if (!wraps || !last_block) request_aux(wraps ? kb + 1 : kb, wraps ? my_first : ru + kWarps);
       }
@@ -494,17 +541,36 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
         dead = true;
         return;
       }
-      // per activation row, group half and plane: an (even byte step, odd byte step) pair of sums
-      uint64_t acc[M][2][3];
+      const uint32_t wbase = ring_u32 + (uint32_t)(c_slot * G_::kSlotBytes);
+      if (G_::kStageAux) {
+        // the slot's low address bits are zero (slots are multiples of 256 bytes), so the other
+        // group's entry is one flipped bit away
+        const uint32_t as = wbase + aux_scale0, az = wbase + aux_zero0;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sbits[0]) : "r"(as));
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sbits[1]) : "r"(as ^ 64u));
+        if (any_zeros && (ru < cu_begin || ru >= cu_end)) {  // entering another matrix of the launch: rare
+          const int j = locate(ru);
+          cu_begin = p.mats[j].ru_begin;
+          cu_end = j + 1 < p.n_mats ? p.mats[j + 1].ru_begin : p.nRU;
+          cu_zeros = p.mats[j].zeros != nullptr;
+        }
+        if (cu_zeros) {  // a matrix without zero points stages none: they stay 4
+          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zp[0]) : "r"(az));
+          asm volatile("ld.shared.u8 %0, [%1];" : "=r"(zp[1]) : "r"(az ^ 32u));
+        }
+      }
+      // per activation row and group half: an (even byte step, odd byte step) pair of sums of
+      // entry(plane 0) + 2 entry(plane 1) - 4 entry(plane 2)
+      uint64_t acc[M][2];
       float corr[M][2];
 #pragma unroll
       for (int m = 0; m < M; ++m)
 #pragma unroll
         for (int jh = 0; jh < 2; ++jh) {
           corr[m][jh] = 0.f;
-#pragma unroll
-          for (int pl = 0; pl < 3; ++pl) acc[m][jh][pl] = 0ull;
+          acc[m][jh] = 0ull;
         }
+      const uint64_t two2 = 0x4000000040000000ull, minus_four2 = 0xc0800000c0800000ull;  // {2.f, 2.f}, {-4.f, -4.f}
       {
         // the rounding correction needs the zero points during the lookups (code - zero = +/-3 is
         // code 7 / 1 at zero point 4 and code 6 / 0 at zero point 3)
@@ -513,7 +579,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
           flip[0] = zp[0] == 3u ? 0xffffffffu : 0u;
           flip[1] = zp[1] == 3u ? 0xffffffffu : 0u;
         }
-        const uint32_t wbase = ring_u32 + (uint32_t)(c_slot * kUnitBytes);
         // staged words are fetched one (half, word) step ahead of their use, into two register
         // sets used in turn
         auto fetch = [&](int step, uint32_t (&dst)[3]) {
@@ -537,8 +602,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
               const uint32_t a0 = lookup_address(w[pl], 2 * bp, xl[jh][jw][2 * bp]);
               const uint32_t a1 = lookup_address(w[pl], 2 * bp + 1, xl[jh][jw][2 * bp + 1]);
 #pragma unroll
-              for (int m = 0; m < M; ++m)  // activation row m sits m * 128 bytes further
-                acc[m][jh][pl] = add2_lds(acc[m][jh][pl], a0 + (uint32_t)(m * 128), a1 + (uint32_t)(m * 128));
+              for (int m = 0; m < M; ++m) {  // activation row m sits m * 128 bytes further
+                const uint32_t b0 = a0 + (uint32_t)(m * 128), b1 = a1 + (uint32_t)(m * 128);
+                acc[m][jh] = pl == 0 ? add2_lds(acc[m][jh], b0, b1) : fma2_lds(acc[m][jh], b0, b1, pl == 1 ? two2 : minus_four2);
+              }
             }
             if (CORRECT) {
 #pragma unroll
@@ -570,14 +637,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
         c_phase ^= 1u;
       }
 
-      const float sc[2] = {has[0] ? bits_to_float((unsigned short)sbits[0], p.scale_dtype) : 0.f,
-                           has[1] ? bits_to_float((unsigned short)sbits[1], p.scale_dtype) : 0.f};
+      const float sc[2] = {G_::kStageAux || has[0] ? bits_to_float((unsigned short)sbits[0], p.scale_dtype) : 0.f,
+                           G_::kStageAux || has[1] ? bits_to_float((unsigned short)sbits[1], p.scale_dtype) : 0.f};
 #pragma unroll
       for (int m = 0; m < M; ++m) {
         float term[2];
 #pragma unroll
         for (int jh = 0; jh < 2; ++jh) {
-          float d = sum2(acc[m][jh][0]) + 2.f * sum2(acc[m][jh][1]) - 4.f * sum2(acc[m][jh][2]);
+          float d = sum2(acc[m][jh]);
           if (any_zeros) d += (4.f - (float)zp[jh]) * sx_cur[m][jh];
           term[jh] = d * sc[jh];
           if (CORRECT) {
@@ -783,6 +850,8 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
     if (j >= n_matrices) {
       mat = W3Matrix{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
       p.plane_maps[j] = p.plane_maps[0];
+      p.scale_maps[j] = p.scale_maps[0];
+      p.zero_maps[j] = p.zero_maps[0];
       continue;
     }
     const fb_w3_matrix_t& in = matrices[j];
@@ -799,6 +868,14 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
       return fail(FB_EALIAS, "fb_w3_gemv: out overlaps an input");
     if (scratch && overlaps(scratch, scratch_bytes, in.out, out_bytes)) return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps out");
     if (!plane_tensor_map(in.planes, O, G, 1, 6, &p.plane_maps[j])) return FB_ECUDA;
+    if (m <= 2) {  // the kernels for M <= 2 stage scales and zero points with the planes
+      if (!group_row_tensor_map(in.scales, 2, O, G, &p.scale_maps[j])) return FB_ECUDA;
+      if (in.zeros && !group_row_tensor_map(in.zeros, 1, O, G, &p.zero_maps[j])) return FB_ECUDA;
+      if (!in.zeros) p.zero_maps[j] = p.scale_maps[j];
+    } else {
+      p.scale_maps[j] = p.plane_maps[j];
+      p.zero_maps[j] = p.plane_maps[j];
+    }
     mat.planes = in.planes;
     mat.scales = static_cast<const unsigned short*>(in.scales);
     mat.zeros = in.zeros;
