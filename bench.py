@@ -2,11 +2,15 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1]): all seven Qwen3-8B Linear shapes as W3 group-128
-GEMVs at M=1, for 36 layers of DISTINCT synthetic weights (2.8 GB, far larger than L2, so
-every weight byte comes from HBM), value distributions as configs[0] states (uniform codes,
-fp16 scales U(0.005,0.02), zero points in {3,4}, x ~ N(0,1) bf16).  One step = one pass over
-all 252 GEMVs = the Linear work of one decoded token, replayed from a CUDA graph.
+Workload: all seven Qwen3-8B Linear shapes as W3 group-128 GEMVs at M=1, for 36 layers of
+DISTINCT synthetic weights (2.8 GB, far larger than L2, so every weight byte comes from HBM):
+uniform codes, fp16 scales U(0.005,0.02), zero points in {3,4}, x ~ N(0,1) bf16.  One step = one
+pass over all 252 GEMVs = the Linear work of one decoded token, replayed from a CUDA graph.
+
+One GPU: one launch per Linear through the module interface.  Several GPUs (torchrun): the same
+252 GEMVs sharded tensor-parallel, q/k/v/gate/up by output rows, o/down by input groups, each
+row-split GEMV followed by its exchange (results pushed from the GEMV epilogue into every rank's
+buffer over NVLink, summed by a polling kernel): strong scaling of one token's Linear work.
 
 Metric: HBM GB/s on the algorithmic bytes (stored planes + scales + zero points + x + y).
 """
@@ -15,6 +19,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -30,7 +35,9 @@ SHAPES = (  # name, out_features, in_features (Qwen3-8B)
 )
 LAYERS = 36
 NOMINAL_HBM_GBS = 8000.0
-DRAM_TRAFFIC_RATIO = 20.203 / 20.087
+# DRAM bytes over algorithmic bytes of a 12288x4096 launch, from one profiler capture of that launch;
+# traffic grows with the bytes a launch streams, so other launches are scaled by the same ratio.
+DRAM_TRAFFIC_RATIO = 20.226 / 20.087
 METRIC = "W3 GEMV HBM GB/s (% of 8 TB/s) per Qwen3-8B shape; batch-1 decode tokens/s"
 
 
@@ -38,6 +45,12 @@ def gemv_bytes(o: int, k: int, zeros: bool = True) -> int:
     """Algorithmic bytes of one M=1 GEMV: planes, fp16 scales, uint8 zero points, x and y."""
     g = k // 128
     return 3 * o * k // 8 + 2 * g * o + (g * o if zeros else 0) + 2 * k + 2 * o
+
+
+def bb_bytes(o: int, k: int, n_salient: int = 32) -> int:
+    """Algorithmic bytes of one two-base GEMV with matrix-wide scales: two sign planes, fp16 row and
+    column scales, 32 dense bf16 salient columns with their indices, x and y."""
+    return 2 * o * k // 8 + 4 * o + 4 * k + 2 * n_salient * o + 4 * n_salient + 2 * k + 2 * o
 
 
 def measured_peak():
@@ -95,14 +108,61 @@ def synthetic_layout(torch, o, k, device, gen):
     }
 
 
-def run_ours(args, rank, world, local_rank):
+def capture(torch, fn, stream):
+    """Run ``fn`` once eagerly on ``stream`` (sizes scratch, sets kernel attributes), then capture it."""
+    fn()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        fn()
+    return graph
+
+
+def paired_rounds(torch, graphs, launches, stream, *, warmup=20, repeats=100, rounds=7):
+    """The reference's timing protocol (acceleration_checks.py:42-64, run_w3_lut_benchmark.py:278-285) on
+    CUDA graphs: ``warmup`` replays of every arm, then ``rounds`` rounds of ``repeats`` replays each,
+    the order of the arms reversed every other round.  Per arm: median microseconds per LAUNCH,
+    (max - min) / median over the rounds, and ``stable`` when that is at most 10 %."""
+    for graph in graphs.values():
+        for _ in range(warmup):
+            graph.replay()
+    stream.synchronize()
+    order = list(graphs)
+    samples = {name: [] for name in order}
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for index in range(rounds):
+        for name in order if index % 2 == 0 else reversed(order):
+            begin.record(stream)
+            for _ in range(repeats):
+                graphs[name].replay()
+            end.record(stream)
+            stream.synchronize()
+            samples[name].append(begin.elapsed_time(end) * 1000 / (repeats * launches[name]))
+    report = {}
+    for name, values in samples.items():
+        median = statistics.median(values)
+        spread = (max(values) - min(values)) / median if median > 0 else float("inf")
+        report[name] = {"us": round(median, 3), "relative_range": round(spread, 4), "stable": spread <= 0.10}
+    return report
+
+
+def clock_note(us, clocks):
+    """time x median SM MHz: the same kernel at another clock scales by this product."""
+    mhz = clocks.get("sm_mhz")
+    return None if mhz is None else round(us * mhz, 1)
+
+
+def run_single_gpu(args, local_rank):
+    """One GPU: 252 launches, one per Linear, through ``PackedW3Linear`` (the reference's module surface)."""
     import torch
 
+    from marlin_style_fluxbin_b200 import _native
+    from marlin_style_fluxbin_b200.gptq_deployment import restore_planar_w3
     from marlin_style_fluxbin_b200.w3_lut_deployment import PackedW3Linear
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    gen = torch.Generator(device=device).manual_seed(20260916 + rank)
+    gen = torch.Generator(device=device).manual_seed(20260916)
     with torch.inference_mode():
         modules = []  # LAYERS x 7 bound modules, distinct weights
         for _ in range(LAYERS):
@@ -122,12 +182,9 @@ def run_ours(args, rank, world, local_rank):
         stream = torch.cuda.Stream(device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
-            for _ in range(2):
-                one_pass()
-            stream.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                one_pass()
+            one_pass()
+            graph = capture(torch, one_pass, stream)
+            scratch = _native.scratch_for(device, 1)  # the per-stream scratch the modules launched with
 
             def e2e_step():
                 for k in x_dev:
@@ -137,107 +194,70 @@ def run_ours(args, rank, world, local_rank):
                     host.copy_(module._decode_output.view(1, 1, -1), non_blocking=True)
                 stream.synchronize()
 
-            def barrier():
-                stream.synchronize()
-                if world > 1:
-                    torch.distributed.barrier()
-                stream.synchronize()
-
             for _ in range(max(args.warmup, 3)):
                 graph.replay()
-            barrier()
+            stream.synchronize()
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             with ClockSampler(local_rank) as clocks:
                 begin.record(stream)
                 for _ in range(args.steps):
                     graph.replay()
                 end.record(stream)
-                barrier()
-                # the K timed steps last tens of milliseconds: keep the same graph running for
-                # about a second under the sampler, so that the clock record holds samples taken
-                # under this very load (reported beside the number, not instead of it)
-                # (not in the --headline-only form, which profiling commands run)
-                held = 1 if args.headline_only else max(1, int(1000.0 / max(begin.elapsed_time(end) / args.steps, 1e-3)))
-                hold_begin, hold_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                hold_begin.record(stream)
-                for _ in range(held):
-                    graph.replay()
-                hold_end.record(stream)
-                barrier()
+                stream.synchronize()
+                # the K timed steps last tens of milliseconds: the protocol rounds below keep the same
+                # graph running for about a second under the sampler, so that the clock record holds
+                # samples taken under this very load
+                protocol = None if args.headline_only else paired_rounds(torch, {"step": graph}, {"step": 1}, stream, warmup=3)["step"]
             step_ms = begin.elapsed_time(end) / args.steps
-            held_ms = hold_begin.elapsed_time(hold_end) / held
+            clock_summary = clocks.summary()
 
-            # per-shape: the same protocol on 36 distinct weights of one shape
             per_shape = {}
-            for name, o, k in SHAPES:
-                if args.headline_only or name in ("v_proj", "up_proj", "o_proj"):
-                    continue
-                mods = [m for n, m in modules if n == name]
-                shape_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(shape_graph, stream=stream):
-                    for m in mods:
-                        m(x_dev[k])
-                for _ in range(3):
-                    shape_graph.replay()
-                stream.synchronize()
-                begin.record(stream)
-                for _ in range(20):
-                    shape_graph.replay()
-                end.record(stream)
-                stream.synchronize()
-                us = begin.elapsed_time(end) * 1000 / (20 * len(mods))
-                gbs = gemv_bytes(o, k) / us / 1e3
-                per_shape[f"{o}x{k}"] = {"us": round(us, 3), "gbs": round(gbs, 1), "bytes": gemv_bytes(o, k),
-                                         "bytes_zeros_as_fp16": gemv_bytes(o, k) + (k // 128) * o}
+            if not args.headline_only:
+                for name, o, k in SHAPES:
+                    if name in ("v_proj", "up_proj", "o_proj"):
+                        continue
+                    mods = [m for n, m in modules if n == name]
+                    dense = [restore_planar_w3(m.layout(), dtype=torch.bfloat16) for m in mods[:6]]  # 6 x 100 MB > L2 for the large shapes
+                    y = torch.empty(1, o, device=device, dtype=torch.bfloat16)
+                    x2 = x_dev[k].view(1, k)
+                    graphs = {"w3": capture(torch, lambda: [m(x_dev[k]) for m in mods], stream),
+                              "cublas_bf16": capture(torch, lambda: [torch.mm(x2, w.t(), out=y) for w in dense], stream)}
+                    report = paired_rounds(torch, graphs, {"w3": len(mods), "cublas_bf16": len(dense)}, stream)
+                    us = report["w3"]["us"]
+                    per_shape[f"{o}x{k}"] = {
+                        "us": us, "relative_range": report["w3"]["relative_range"], "stable": report["w3"]["stable"],
+                        "gbs": round(gemv_bytes(o, k) / us / 1e3, 1), "bytes": gemv_bytes(o, k),
+                        "bytes_zeros_as_fp16": gemv_bytes(o, k) + (k // 128) * o,
+                        "us_x_sm_mhz": clock_note(us, clock_summary),
+                        "cublas_bf16_dense_us": report["cublas_bf16"]["us"], "speedup_over_cublas_bf16": round(report["cublas_bf16"]["us"] / us, 2)}
+                    del dense, graphs
 
-            # the same seven Linears as the decode engine launches them: q/k/v and gate/up share a
-            # launch, so a layer is four launches; and the M sweep of configs[1] on two shapes
-            extras = world == 1 and not args.headline_only
-            fused = fused_layer_pass(torch, modules, x_dev, stream, begin, end) if extras else None
-            sweep = m_sweep(torch, modules, device, stream, begin, end) if extras else None
+            extras = not args.headline_only
+            fused = fused_layer_pass(torch, modules, x_dev, stream) if extras else None
+            sweep = m_sweep(torch, modules, device, stream) if extras else None
 
             for _ in range(3):
                 e2e_step()
-            barrier()
+            stream.synchronize()
             t0 = time.perf_counter()
             begin.record(stream)
             for _ in range(args.steps):
                 e2e_step()
             end.record(stream)
-            barrier()
+            stream.synchronize()
             e2e_ms = max(begin.elapsed_time(end), (time.perf_counter() - t0) * 1e3) / args.steps
+            status = int(scratch[:4].view(torch.int32)[0])
 
-    if world > 1:
-        t = torch.tensor([step_ms, e2e_ms], device=device, dtype=torch.float64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        step_ms, e2e_ms = float(t[0]), float(t[1])
     step_bytes = LAYERS * sum(gemv_bytes(o, k) for _, o, k in SHAPES)
     return {
         "step_ms": step_ms, "e2e_ms": e2e_ms, "step_bytes": step_bytes, "per_shape": per_shape, "fused": fused, "m_sweep": sweep,
-        "clocks": dict(clocks.summary(), sampled_over_steps=args.steps + held, ms_per_step_while_sampled=round(held_ms, 4)),
-        "launches": len(modules) * args.steps,
+        "protocol": protocol, "clocks": dict(clock_summary, sampled_over="the timed steps and the protocol rounds of the same graph"),
+        "launches": len(modules) * args.steps, "status": status,
         "h2d": sum(v.numel() * 2 for v in x_host.values()), "d2h": sum(v.numel() * 2 for v in out_host),
     }
 
 
-def _graph_time(torch, fn, stream, begin, end, launches, repeats=20):
-    graph = torch.cuda.CUDAGraph()
-    fn()
-    stream.synchronize()
-    with torch.cuda.graph(graph, stream=stream):
-        fn()
-    for _ in range(3):
-        graph.replay()
-    stream.synchronize()
-    begin.record(stream)
-    for _ in range(repeats):
-        graph.replay()
-    end.record(stream)
-    stream.synchronize()
-    return begin.elapsed_time(end) * 1000 / (repeats * launches)
-
-
-def fused_layer_pass(torch, modules, x_dev, stream, begin, end):
+def fused_layer_pass(torch, modules, x_dev, stream):
     """Four launches per layer (q/k/v, o, gate/up, down) over the weights of the headline step."""
     from marlin_style_fluxbin_b200 import _native
 
@@ -255,12 +275,13 @@ def fused_layer_pass(torch, modules, x_dev, stream, begin, end):
         for array, n, total, k, _ in plan:
             _native.w3_gemv_multi(x_dev[k].view(1, k), array, n, total, torch.float16, None, scratch=scratch)
 
-    us = _graph_time(torch, run, stream, begin, end, len(by_layer))
+    report = paired_rounds(torch, {"layer": capture(torch, run, stream)}, {"layer": len(by_layer)}, stream, warmup=5, repeats=30)["layer"]
     layer_bytes = sum(gemv_bytes(o, k) for _, o, k in SHAPES)
-    return {"launches_per_layer": 4, "us_per_layer": round(us, 2), "gbs": round(layer_bytes / us / 1e3, 1)}
+    return {"launches_per_layer": 4, "us_per_layer": report["us"], "relative_range": report["relative_range"], "stable": report["stable"],
+            "gbs": round(layer_bytes / report["us"] / 1e3, 1), "status": int(scratch[:4].view(torch.int32)[0])}
 
 
-def m_sweep(torch, modules, device, stream, begin, end):
+def m_sweep(torch, modules, device, stream):
     """M in {1,2,4,8,16} on q_proj and gate_proj: table-lookup kernel (M <= 4), tensor-core kernel, cuBLAS bf16."""
     from marlin_style_fluxbin_b200 import _native
     from marlin_style_fluxbin_b200.gptq_deployment import restore_planar_w3
@@ -270,37 +291,38 @@ def m_sweep(torch, modules, device, stream, begin, end):
     for name in ("q_proj", "gate_proj"):
         mods = [m for n, m in modules if n == name][:12]
         o, k = mods[0].out_features, mods[0].in_features
-        dense = [restore_planar_w3(m.layout(), dtype=torch.bfloat16) for m in mods[:4]]
+        dense = [restore_planar_w3(m.layout(), dtype=torch.bfloat16) for m in mods[:6]]
         for rows in (1, 2, 4, 8, 16):
             x = torch.randn(rows, k, device=device).bfloat16()
             y = torch.empty(rows, o, device=device, dtype=torch.bfloat16)
-            entry = {}
+            graphs, launches = {}, {}
             if rows <= 4:
-                entry["lut_us"] = round(_graph_time(torch, lambda: [_native.w3_gemv(x, m.planes, m.scales, getattr(m, "zeros", None), None, y, scratch=scratch["lut"]) for m in mods], stream, begin, end, len(mods)), 2)
-            entry["mma_us"] = round(_graph_time(torch, lambda: [_native.w3_gemm_small(x, m.planes, m.scales, getattr(m, "zeros", None), None, y, scratch=scratch["mma"]) for m in mods], stream, begin, end, len(mods)), 2)
-            entry["cublas_bf16_us"] = round(_graph_time(torch, lambda: [torch.mm(x, w.t(), out=y) for w in dense], stream, begin, end, len(dense)), 2)
-            best = min(v for key, v in entry.items() if key != "cublas_bf16_us")
+                graphs["lut_us"] = capture(torch, lambda: [_native.w3_gemv(x, m.planes, m.scales, getattr(m, "zeros", None), None, y, scratch=scratch["lut"]) for m in mods], stream)
+                launches["lut_us"] = len(mods)
+            graphs["mma_us"] = capture(torch, lambda: [_native.w3_gemm_small(x, m.planes, m.scales, getattr(m, "zeros", None), None, y, scratch=scratch["mma"]) for m in mods], stream)
+            launches["mma_us"] = len(mods)
+            graphs["cublas_bf16_us"] = capture(torch, lambda: [torch.mm(x, w.t(), out=y) for w in dense], stream)
+            launches["cublas_bf16_us"] = len(dense)
+            report = paired_rounds(torch, graphs, launches, stream, warmup=5, repeats=30, rounds=5)
+            entry = {key: value["us"] for key, value in report.items()}
+            entry["stable"] = all(value["stable"] for value in report.values())
+            best = min(v for key, v in entry.items() if key in ("lut_us", "mma_us"))
             entry["packed_gbs"] = round(gemv_bytes(o, k) / best / 1e3, 1)
             out[f"{o}x{k} M={rows}"] = entry
         del dense
     return out
 
 
-def bb_bytes(o: int, k: int, n_salient: int = 32) -> int:
-    """Algorithmic bytes of one two-base GEMV with matrix-wide scales (BASELINE.json configs[2])."""
-    return 2 * o * k // 8 + 4 * o + 4 * k + 2 * n_salient * o + 4 * n_salient + 2 * k + 2 * o
-
-
 def run_binary_basis(torch, device):
-    """configs[2]: the two-base binary-basis GEMV (1 bit per weight and base, fp16 row / column scales,
-    32 dense bf16 salient columns) on the seven shapes, 12 distinct weight sets per shape."""
+    """The two-base binary-basis GEMV (1 bit per weight and base, fp16 row / column scales, 32 dense
+    bf16 salient columns) on the seven shapes, 12 distinct weight sets per shape."""
     from marlin_style_fluxbin_b200 import _native
     from marlin_style_fluxbin_b200.binary_global import global_two_base_m1_out
 
     gen = torch.Generator(device=device).manual_seed(20260917)
     stream = torch.cuda.Stream(device)
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    table, total_us, total_bytes = {}, 0.0, 0
+    stream.wait_stream(torch.cuda.current_stream())
+    table, total_us, total_bytes, status = {}, 0.0, 0, 0
     with torch.inference_mode(), torch.cuda.stream(stream):
         for name, o, k in SHAPES:
             key = f"{o}x{k}"
@@ -327,35 +349,165 @@ def run_binary_basis(torch, device):
                                            layout["salient_indices"], layout["salient_values"], y, scratch=scratch)
 
             global_two_base_m1_out(x, layouts[0], y)  # the public call, once, validates the layout
-            us = _graph_time(torch, run, stream, begin, end, len(layouts))
-            table[key] = {"us": round(us, 3), "bytes": bb_bytes(o, k), "gbs": round(bb_bytes(o, k) / us / 1e3, 1)}
-            total_us += us
+            report = paired_rounds(torch, {"bb": capture(torch, run, stream)}, {"bb": len(layouts)}, stream, warmup=5, repeats=50)["bb"]
+            table[key] = {"us": report["us"], "relative_range": report["relative_range"], "stable": report["stable"],
+                          "bytes": bb_bytes(o, k), "gbs": round(bb_bytes(o, k) / report["us"] / 1e3, 1)}
+            total_us += report["us"]
             total_bytes += bb_bytes(o, k)
+            status |= int(scratch[:4].view(torch.int32)[0])
             del layouts
-    return table, total_us, total_bytes
+    torch.cuda.current_stream().wait_stream(stream)
+    return table, total_us, total_bytes, status
 
 
-def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=("bf16", "w3"), repeats=5, tp_push=None):
-    """Full-model batch-1 decode (BASELINE.json configs[3] / [4]): random-init Qwen3 shape, all Linears
-    W3 g128, LM head bf16; prefill `prompt` random ids, then `steps` tokens from ONE CUDA graph.  The
-    BF16 arm runs the same engine with dense dequantised weights through cuBLAS.  Tensor parallel
+def run_tensor_parallel(args, rank, world, local_rank):
+    """Several GPUs: the 252 GEMVs of one token sharded tensor-parallel (one process per GPU).
+
+    q/k/v/gate/up keep a slice of their output rows and need no exchange; o/down keep a slice of
+    their input groups, and their partial rows are pushed from the GEMV epilogue into every rank's
+    exchange buffer (plain peer stores over NVLink) and summed there by a polling kernel.  One step
+    = the 252 sharded GEMVs + 72 exchanges; the step time is the maximum over the ranks."""
+    import torch
+    import torch.distributed._symmetric_memory as symm
+
+    from marlin_style_fluxbin_b200 import _native
+    from marlin_style_fluxbin_b200.decode_engine import shard_groups, shard_rows
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    gen = torch.Generator(device=device).manual_seed(20260916)  # the same draws on every rank: every rank shards the same weights
+    hidden, f16 = 4096, torch.float16
+    with torch.inference_mode():
+        x_dev = {k: torch.randn(1, k, device=device, generator=gen).bfloat16() for k in (4096, 12288)}
+        x_host = {k: v.cpu().pin_memory() for k, v in x_dev.items()}
+        header = 64
+        xchg = symm.empty(2 * (header + 2 * world * hidden), dtype=torch.float32, device=device)
+        xchg.zero_()
+        handle = symm.rendezvous(xchg, torch.distributed.group.WORLD.group_name)
+        bases = [int(ptr) for ptr in handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        torch.distributed.barrier()
+        sites = []
+        for site in range(2):
+            data = 8 * (header + site * world * hidden)
+            sites.append({"push": _native.w3_push_descriptor([base + data + 8 * rank * hidden for base in bases]), "parts": bases[rank] + data})
+        scratch = torch.zeros(_native.w3_scratch_bytes(1, 12288, 12288), dtype=torch.uint8, device=device)
+        residual = torch.zeros(1, hidden, device=device, dtype=torch.bfloat16)
+        plan, keep, outs_last = [], [], []
+        for _ in range(LAYERS):
+            exchanges = 0
+            for name, o, k in SHAPES:
+                full = synthetic_layout(torch, o, k, device, gen)
+                row_split = name in ("o_proj", "down_proj")
+                shard = shard_groups(full, rank, world) if row_split else shard_rows(full, rank, world)
+                del full
+                out = torch.empty(1, shard["planes"].shape[2], device=device, dtype=torch.bfloat16)
+                matrix = _native.w3_matrix_list([(shard["planes"], shard["scales"], shard["zeros"], out, None)])
+                k_local = shard["planes"].shape[0] * 128
+                x_local = x_dev[k][:, rank * k_local:(rank + 1) * k_local].contiguous() if row_split else x_dev[k]
+                plan.append((row_split, sites[exchanges % 2] if row_split else None, matrix, x_local, k_local, out))
+                exchanges += int(row_split)
+                keep.append(shard)
+            outs_last = [entry[5] for entry in plan[-len(SHAPES):]]
+        out_host = [torch.empty_like(o, device="cpu").pin_memory() for o in outs_last]
+
+        def one_pass():
+            for row_split, site, matrix, x_local, k_local, out in plan:
+                if row_split:
+                    _native.w3_gemv_push(x_local, 0, None, 0.0, matrix, k_local, f16, site["push"], scratch=scratch)
+                    _native.tp_reduce(site["parts"], world, residual, out, bases[rank])
+                else:
+                    _native.w3_gemv_multi(x_local, matrix, 1, out.shape[1], f16, None, scratch=scratch)
+
+        stream = torch.cuda.Stream(device)
+        stream.wait_stream(torch.cuda.current_stream())
+
+        def barrier():
+            stream.synchronize()
+            torch.distributed.barrier()
+            stream.synchronize()
+
+        with torch.cuda.stream(stream):
+            one_pass()
+            barrier()
+            graph = capture(torch, one_pass, stream)
+            barrier()
+
+            def e2e_step():
+                for k in x_dev:
+                    x_dev[k].copy_(x_host[k], non_blocking=True)
+                graph.replay()
+                for host, out in zip(out_host, outs_last):
+                    host.copy_(out, non_blocking=True)
+                stream.synchronize()
+
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            barrier()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(local_rank) as clocks:
+                begin.record(stream)
+                for _ in range(args.steps):
+                    graph.replay()
+                end.record(stream)
+                barrier()
+                held = max(1, int(500.0 / max(begin.elapsed_time(end) / args.steps, 1e-3)))  # half a second more under the sampler
+                for _ in range(held):
+                    graph.replay()
+                barrier()
+            step_ms = begin.elapsed_time(end) / args.steps
+            for _ in range(3):
+                e2e_step()
+            barrier()
+            t0 = time.perf_counter()
+            begin.record(stream)
+            for _ in range(args.steps):
+                e2e_step()
+            end.record(stream)
+            barrier()
+            e2e_ms = max(begin.elapsed_time(end), (time.perf_counter() - t0) * 1e3) / args.steps
+            status = int(scratch[:4].view(torch.int32)[0]) | int(xchg[:1].view(torch.int32)[0])
+        times = torch.tensor([step_ms, e2e_ms, float(status)], device=device, dtype=torch.float64)
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    return {
+        "step_ms": float(times[0]), "e2e_ms": float(times[1]), "status": int(times[2]),
+        "step_bytes": LAYERS * sum(gemv_bytes(o, k) for _, o, k in SHAPES),
+        "clocks": clocks.summary(), "launches": (len(plan) + 2 * LAYERS) * args.steps,
+        "exchange_bytes_per_step": 2 * LAYERS * hidden * 8 * (world - 1),
+        "h2d": sum(v.numel() * 2 for v in x_host.values()), "d2h": sum(v.numel() * 2 for v in out_host),
+    }
+
+
+def nrmse(a, b):
+    a, b = a.double(), b.double()
+    return round(float((a - b).square().mean().sqrt() / b.square().mean().sqrt()), 5)
+
+
+def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=("bf16", "w3"), repeats=5, tp_push=None, truth=True):
+    """Full-model batch-1 decode: random-init Qwen3 shape, all Linears W3 g128, LM head bf16; prefill
+    `prompt` random ids, then `steps` tokens from ONE CUDA graph.  The BF16 arm runs the same engine
+    with dense dequantised weights through cuBLAS.  All arms are fed the BF16 arm's greedy tokens, and
+    (unsharded) each arm's logits are measured against the same model run in fp32.  Tensor parallel
     over `world` ranks when world > 1."""
     from marlin_style_fluxbin_b200.decode_engine import QWEN3_8B, QWEN3_32B, DecodeEngine
 
     shape = {"qwen3-8b": QWEN3_8B, "qwen3-32b": QWEN3_32B}[shape_name]
     device = torch.device("cuda", local_rank)
     ids = torch.randint(0, shape.vocab, (1, prompt), generator=torch.Generator().manual_seed(1))
-    out, forced, reference = {}, None, None
+    out, forced, traces, truth_logits = {}, None, {}, None
     for arm in arms:
-        engine = DecodeEngine(shape, device=device, max_positions=prompt + steps + 8, arm=arm,
+        engine_arm, arithmetic = ("w3", "decoded_bf16") if arm == "w3_decoded" else (arm, "structural")
+        engine = DecodeEngine(shape, device=device, max_positions=prompt + steps + 8, arm=engine_arm, arithmetic=arithmetic,
                               tp_rank=rank, tp_size=world, tp_push=tp_push)
         first = engine.prefill(ids).argmax(-1)
         fed, greedy, logits = engine.decode(first, prompt, steps, forced=forced)
         engine.prefill(ids)
+        engine.keep_logits = False  # the timed graph is a greedy decode: the logits stay on the chip
         graph, predictions, _ = engine.capture(first, prompt, steps, forced=forced)
         engine.prefill(ids)
         graph.replay()
         torch.cuda.synchronize(device)
+        engine.check_status()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         times = []
         for _ in range(repeats):
@@ -366,49 +518,56 @@ def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=(
             end.record()
             torch.cuda.synchronize(device)
             times.append(begin.elapsed_time(end))
+        engine.check_status()
         ms = sorted(times)[len(times) // 2]
         if world > 1:
             t = torch.tensor([ms], device=device, dtype=torch.float64)
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
             ms = float(t[0])
         entry = {"tokens_per_s": round(steps / ms * 1e3, 1), "ms_per_token": round(ms / steps, 4),
-                 "launches_per_token": engine.launches_per_step, "graph_equals_eager": bool(torch.equal(predictions, greedy))}
+                 "launches_per_token": engine.launches_per_step,  # in the graph only the first step gathers its embedding row
+                 "graph_equals_eager": bool(torch.equal(predictions, greedy)), "status": 0}
         if forced is None:
-            forced, reference = fed, (greedy, logits)
-        else:
-            a, b = logits.double(), reference[1].double()
-            entry["greedy_agreement_forced"] = round(float((greedy == reference[0]).float().mean()), 4)
-            entry["logits_nrmse_vs_bf16_arm"] = round(float((a - b).square().mean().sqrt() / b.square().mean().sqrt()), 5)
-            # a disagreement is a near-tie when the bf16 arm's margin between its own choice and the
-            # packed arm's choice is within four times the rms difference of the two arms' logits
-            rms = float((a - b).square().mean().sqrt())
-            differ = (greedy != reference[0]).nonzero().flatten().tolist()
-            margins = [float(b[i, reference[0][i]] - b[i, greedy[i]]) for i in differ]
-            entry["disagreements"] = len(differ)
-            entry["disagreements_outside_near_ties"] = sum(1 for v in margins if v > 4 * rms)
-        if arm == "w3":
-            tp_forced, tp_greedy, tp_logits = fed, greedy, logits
+            forced = fed
+            if truth and world == 1:
+                truth_logits = engine.truth_logits(ids, fed)
+        traces[arm] = (greedy, logits)
+        if truth_logits is not None:
+            entry["logits_nrmse_vs_fp32"] = nrmse(logits, truth_logits)
+            entry["greedy_agreement_with_fp32"] = round(float((greedy == truth_logits.argmax(-1)).float().mean()), 4)
+        if arm != arms[0]:
+            entry["greedy_agreement_forced"] = round(float((greedy == traces[arms[0]][0]).float().mean()), 4)
+            entry[f"logits_nrmse_vs_{arms[0]}_arm"] = nrmse(logits, traces[arms[0]][1])
+        if engine_arm == "bf16":
+            weights = sum(v.numel() * 2 for layer in engine.layers for v in layer.dense.values()) + engine.lm_head.numel() * 2
+            entry["weight_bytes_per_token"] = weights
+            entry["weight_gbs"] = round(weights / (ms / steps) / 1e6, 1)
         out[arm] = entry
+        last_engine_fed = fed
         del engine, graph
         torch.cuda.empty_cache()
-    if world > 1 and "w3" in out:
+    packed = [a for a in arms if a.startswith("w3")]
+    if world > 1 and packed:
         # the sharded engine against an unsharded engine with the same weights, on rank 0:
-        # the allreduce changes the summation order, nothing else
+        # the exchange changes the summation order, nothing else
         if rank == 0:
             single = DecodeEngine(shape, device=device, max_positions=prompt + steps + 8, arm="w3", tp_rank=0, tp_size=1)
-            first_single = single.prefill(ids).argmax(-1)
-            _, greedy_single, logits_single = single.decode(first_single, prompt, min(steps, 8), forced=tp_forced[:min(steps, 8)])
-            a, b = tp_logits[:min(steps, 8)].double(), logits_single.double()
-            out["w3"]["tp_vs_single_logits_nrmse"] = round(float((a - b).square().mean().sqrt() / b.square().mean().sqrt()), 5)
-            out["w3"]["tp_vs_single_greedy_agreement"] = round(float((tp_greedy[:min(steps, 8)] == greedy_single).float().mean()), 4)
+            single.prefill(ids)
+            few = min(steps, 8)
+            _, greedy_single, logits_single = single.decode(last_engine_fed[:1], prompt, few, forced=last_engine_fed[:few])
+            out[packed[0]]["tp_vs_single_logits_nrmse"] = nrmse(traces[packed[0]][1][:few], logits_single)
+            out[packed[0]]["tp_vs_single_greedy_agreement"] = round(float((traces[packed[0]][0][:few] == greedy_single).float().mean()), 4)
             del single
             torch.cuda.empty_cache()
         torch.distributed.barrier()
     if "w3" in out and "bf16" in out:
         out["w3_over_bf16"] = round(out["w3"]["tokens_per_s"] / out["bf16"]["tokens_per_s"], 3)
+    if truth_logits is not None:
+        out["fp32_yardstick"] = ("one causal forward pass of prompt + fed tokens with fp32 activations and fp32 dequantised weights; "
+                                 "every arm is fed the first arm's greedy tokens")
     exchange = "none" if world == 1 else ("nccl allreduce" if tp_push is False else "pushed from the GEMV epilogue into peer buffers (packed arm)")
     out["config"] = {"model": shape_name, "prompt_tokens": prompt, "decode_tokens": steps, "tensor_parallel": world, "exchange": exchange,
-                     "graph": "whole continuation, teacher-forced from the bf16 arm's greedy tokens"}
+                     "graph": "whole continuation, teacher-forced from the first arm's greedy tokens, logits kept on the chip"}
     return out
 
 
@@ -480,7 +639,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--workload", default="gemv", choices=("gemv", "decode-8b", "tp-decode-32b", "binary-basis"),
-                        help="gemv (default): the seven Linear shapes plus the 8B decode; tp-decode-32b: tensor-parallel decode over --gpus ranks")
+                        help="gemv (default): the seven Linear shapes (plus, on one GPU, the two-base kernel and the 8B decode; "
+                             "on several, the tensor-parallel 32B-shaped decode); the others run one part alone")
     parser.add_argument("--case", default=None, metavar="OxK",
                         help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
     parser.add_argument("--prompt-tokens", type=int, default=512, help="decode-8b: prompt length")
@@ -492,6 +652,7 @@ def main():
     parser.add_argument("--rows", type=int, default=1, help="with --case: activation rows (above 1 runs the tensor-core kernel)")
     parser.add_argument("--headline-only", action="store_true",
                         help="time only the headline step (no per-shape table, sweeps, decode or CPU leg): for profiler launch lists")
+    parser.add_argument("--no-tp-decode", action="store_true", help="several GPUs: skip the 32B-shaped decode")
     args = parser.parse_args()
     if args.case:
         return small_case(args)
@@ -499,10 +660,11 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     config = {
-        "workload": "qwen3-8b all seven Linear shapes, W3 g128 GEMV, M=1, 36 layers of distinct weights (configs[1])",
+        "workload": "qwen3-8b all seven Linear shapes, W3 g128 GEMV, M=1, 36 layers of distinct weights",
         "shapes": [f"{o}x{k}" for _, o, k in SHAPES], "layers": LAYERS, "gemvs_per_step": LAYERS * len(SHAPES),
         "cache": "inputs larger than L2 (2.8 GB of weights per pass), no flush needed",
-        "zero_points": "uint8 per (group,row), counted at their stored size", "parallelism": f"replicas x{world}",
+        "zero_points": "uint8 per (group,row), counted at their stored size",
+        "parallelism": "single GPU" if world == 1 else f"tensor-parallel x{world}, exchange: push",
     }
 
     if args.impl == "reference":
@@ -512,7 +674,7 @@ def main():
         line = {
             "impl": "reference", "metric": METRIC, "value": round(ref["value"], 3), "unit": "GB/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ref["step_ms"], 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
             "cpu_baseline": {"value": round(ref["value"], 3), "unit": "GB/s", "cores": ref["cores"], "kind": "port", "sample": ref["sample"]},
             "e2e": {"value": round(ref["value"], 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
@@ -525,14 +687,15 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the packed kernels have no CPU path")
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peak, peak_kind = measured_peak()
     if args.workload == "tp-decode-32b":
         torch.cuda.set_device(local_rank)
         decode = run_decode(torch, "qwen3-32b", 1024, 64, rank, world, local_rank, arms=("w3",) if world > 1 else ("bf16", "w3"),
-                            tp_push=False if args.tp_exchange == "nccl" else None)
+                            tp_push=False if args.tp_exchange == "nccl" else None, truth=False)
         if rank == 0:
             print(json.dumps({"metric": "batch-1 decode tokens/s, Qwen3-32B-shaped W3 g128, tensor parallel", "unit": "tokens/s",
                               "value": decode["w3"]["tokens_per_s"], "n_gpus": world, "higher_is_better": True, "scaling": "strong",
-                              "data": "synthetic", "dtype": "f32", "decode": decode}))
+                              "data": "synthetic", "dtype": "bf16", "decode": decode}))
         if world > 1:
             torch.distributed.barrier()
             torch.distributed.destroy_process_group()
@@ -540,59 +703,71 @@ def main():
     if args.workload == "decode-8b":
         torch.cuda.set_device(local_rank)
         decode = run_decode(torch, "qwen3-8b", args.prompt_tokens, args.decode_tokens, 0, 1, local_rank,
-                            arms=("w3",) if args.packed_arm_only else ("bf16", "w3"))
+                            arms=("w3",) if args.packed_arm_only else ("bf16", "w3", "w3_decoded"), truth=not args.packed_arm_only)
         if rank == 0:
-            print(json.dumps({"metric": "batch-1 decode tokens/s, Qwen3-8B random init, W3 g128 (configs[3])", "unit": "tokens/s",
+            print(json.dumps({"metric": "batch-1 decode tokens/s, Qwen3-8B random init, W3 g128", "unit": "tokens/s",
                               "value": decode["w3"]["tokens_per_s"], "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
-                              "dtype": "f32", "decode": decode}))
+                              "dtype": "bf16", "decode": decode}))
         return
     if args.workload == "binary-basis":
         torch.cuda.set_device(local_rank)
-        table, total_us, total_bytes = run_binary_basis(torch, torch.device("cuda", local_rank))
-        peak, peak_kind = measured_peak()
+        table, total_us, total_bytes, status = run_binary_basis(torch, torch.device("cuda", local_rank))
         if rank == 0:
-            print(json.dumps({"metric": "two-base binary-basis GEMV HBM GB/s per Qwen3-8B shape (configs[2])", "unit": "GB/s",
+            print(json.dumps({"metric": "two-base binary-basis GEMV HBM GB/s per Qwen3-8B shape", "unit": "GB/s",
                               "value": round(total_bytes / total_us / 1e3, 1), "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
-                              "dtype": "f32", "us_per_layer": round(total_us, 2), "per_shape": table,
+                              "dtype": "bf16", "us_per_layer": round(total_us, 2), "per_shape": table, "status": status,
                               "roofline": {"bound": "hbm", "achieved": round(total_bytes / total_us / 1e3, 1), "peak": peak, "unit": "GB/s",
                                            "frac": round(total_bytes / total_us / 1e3 / peak, 4), "peak_kind": peak_kind, "traffic": None}}))
         return
-    result = run_ours(args, rank, world, local_rank)
-    decode = None
-    if world == 1 and not args.headline_only:
+
+    result = run_single_gpu(args, local_rank) if world == 1 else run_tensor_parallel(args, rank, world, local_rank)
+    extras = {}
+    if not args.headline_only:
         torch.cuda.empty_cache()
-        decode = run_decode(torch, "qwen3-8b", 512, 32, 0, 1, local_rank)
+        if world == 1:
+            table, total_us, total_bytes, status = run_binary_basis(torch, torch.device("cuda", local_rank))
+            extras["binary_basis"] = {"us_per_layer": round(total_us, 2), "gbs": round(total_bytes / total_us / 1e3, 1),
+                                      "frac": round(total_bytes / total_us / 1e3 / peak, 4), "per_shape": table, "status": status}
+            torch.cuda.empty_cache()
+            extras["decode"] = run_decode(torch, "qwen3-8b", 512, 32, 0, 1, local_rank, arms=("bf16", "w3", "w3_decoded"))
+        elif not args.no_tp_decode:
+            push = run_decode(torch, "qwen3-32b", 1024, 64, rank, world, local_rank, arms=("w3",), truth=False)
+            nccl = run_decode(torch, "qwen3-32b", 1024, 64, rank, world, local_rank, arms=("w3",), tp_push=False, truth=False)
+            extras["tp_decode"] = {"push": push, "nccl_allreduce": nccl}
     if rank == 0:
-        peak, peak_kind = measured_peak()
-        total_bytes = result["step_bytes"] * world
+        total_bytes = result["step_bytes"]  # one token's Linear work, whatever the number of ranks
         value = total_bytes / (result["step_ms"] * 1e-3) / 1e9
         per_gpu = value / world
         e2e = total_bytes / (result["e2e_ms"] * 1e-3) / 1e9
-        for entry in result["per_shape"].values():
+        for entry in result.get("per_shape", {}).values():
             entry["pct_of_8TBps"] = round(100 * entry["gbs"] / NOMINAL_HBM_GBS, 1)
             entry["pct_of_measured"] = round(100 * entry["gbs"] / peak, 1)
-            # the same time against the byte count with zero points held as fp16, as the config words them
-            entry["gbs_zeros_as_fp16"] = round(entry["gbs"] * (1 + (entry["bytes_zeros_as_fp16"] - entry["bytes"]) / entry["bytes"]), 1)
+            # the same time against the byte count with zero points held as fp16
+            entry["gbs_zeros_as_fp16"] = round(entry["gbs"] * entry["bytes_zeros_as_fp16"] / entry["bytes"], 1)
         cpu = cpu_reference(3, 1) if world == 1 and not args.headline_only else None
+        launches_per_step = result["launches"] // args.steps
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(result["step_ms"], 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
             "pct_of_8TBps": round(100 * per_gpu / NOMINAL_HBM_GBS, 1),
-            "linear_tokens_per_s": round(world * 1e3 / result["step_ms"], 1),
-            "per_shape": result["per_shape"], "fused_launches": result["fused"], "m_sweep": result["m_sweep"], "clocks": result["clocks"],
+            "linear_tokens_per_s": round(1e3 / result["step_ms"], 1), "status": result["status"],
+            "clocks": result["clocks"],
             "e2e": {"value": round(e2e, 1), "unit": "GB/s", "h2d_bytes_per_step": result["h2d"] * world, "d2h_bytes_per_step": result["d2h"] * world},
-            "gpu_launches": result["launches"] * world,  # whole job: every rank launches the same graph
+            "gpu_launches": result["launches"] * world,  # whole job: every rank launches its own graph
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(per_gpu / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "w3_gemv_kernel<1,false>", "bytes_per_launch_avg": result["step_bytes"] // (LAYERS * len(SHAPES))},
+                         "frac": round(per_gpu / peak, 4), "peak_kind": peak_kind, "kernel": "w3_gemv_kernel<1,false>",
+                         "bytes_per_launch_avg": result["step_bytes"] // world // (LAYERS * len(SHAPES)),
+                         "traffic": int(DRAM_TRAFFIC_RATIO * (result["step_bytes"] // world // (LAYERS * len(SHAPES)))),
+                         "note": "per GPU: each rank streams 1/N of the bytes" if world > 1 else "one launch per Linear"},
         }
-        # DRAM bytes per launch: ncu measured 20.203 MB for the 12288x4096 launch against 20.087 MB
-        # algorithmic (profiles/w3_gemv_12288x4096_m1.md); traffic grows with the bytes a launch
-        # streams, so the average launch of this mixed-shape step is scaled by the same ratio.
-        line["roofline"]["traffic"] = int(DRAM_TRAFFIC_RATIO * line["roofline"]["bytes_per_launch_avg"])
-        if decode is not None:
-            line["decode"] = decode
+        if world == 1:
+            line.update({"protocol": result["protocol"], "per_shape": result["per_shape"], "fused_launches": result["fused"], "m_sweep": result["m_sweep"]})
+        else:
+            line["tensor_parallel"] = {"launches_per_step_per_rank": launches_per_step, "exchanges_per_step": 2 * LAYERS,
+                                       "nvlink_bytes_sent_per_rank_per_step": result["exchange_bytes_per_step"],
+                                       "limiter": "launch chain: each rank still runs 324 dependent launches per step while its bytes shrink by 1/N"}
+        line.update(extras)
         if cpu is not None:
             line["cpu_baseline"] = {"value": round(cpu["value"], 3), "unit": "GB/s", "cores": cpu["cores"], "kind": "port", "sample": cpu["sample"]}
         print(json.dumps(line))

@@ -147,10 +147,22 @@ def w3_scratch_bytes(m: int, out_features: int, in_features: int) -> int:
     return int(library().fb_w3_gemv_scratch_bytes(m, out_features, in_features))
 
 
-# One zero-initialised scratch per (device, stream): calls ordered on one stream may share
-# it; the kernels leave it ready for the next call.  Grown on demand, which allocates, so
-# the first call of a given size must happen before CUDA-graph capture (warm-up).
+# One zero-initialised scratch per (device, stream, kernel family): calls ordered on one stream may
+# share it; the kernels leave it ready for the next call.  It is allocated ONCE at the largest size
+# its family can ask for, so that a CUDA graph captured earlier on the stream never holds the
+# address of a buffer that a later, larger call replaced; should a call still need more, the old
+# buffer is retired, not freed.  The first call allocates, so it must come before graph capture.
 _scratch: dict[tuple[int, int, str], torch.Tensor] = {}
+_retired: list[torch.Tensor] = []
+
+
+def _family_bytes(family: str) -> int:
+    lib = library()
+    if family == "w3":
+        return int(lib.fb_w3_gemv_scratch_bytes(4, 65536, 32640))
+    if family == "w3mma":
+        return int(lib.fb_w3_gemm_small_scratch_bytes(16, 65536, 32640))
+    return int(lib.fb_bb_gemv_scratch_bytes(65536, 32640, 1))
 
 
 def scratch_for(device: torch.device, nbytes: int, family: str = "w3") -> torch.Tensor:
@@ -162,9 +174,26 @@ def scratch_for(device: torch.device, nbytes: int, family: str = "w3") -> torch.
     if buf is None or buf.numel() < nbytes:
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("packed GEMV scratch must be sized by a warm-up call before graph capture")
-        buf = torch.zeros(max(nbytes, 1 << 21), dtype=torch.uint8, device=device)
+        if buf is not None:
+            _retired.append(buf)
+        buf = torch.zeros(max(nbytes, _family_bytes(family)), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if a bounded device-side wait expired in any kernel that used a scratch
+    handed out by ``scratch_for`` (status word 1: W3 GEMV staging, 3: tensor-core kernel); the scratch
+    is re-zeroed, the results of the calls since the last check are invalid."""
+    torch.cuda.synchronize(device)
+    bad = {}
+    for key, buf in _scratch.items():
+        code = int(buf[:4].view(torch.int32)[0])
+        if code:
+            bad[key] = code
+            buf.zero_()
+    if bad:
+        raise NativeError(f"a device-side wait expired: {bad}; scratch re-zeroed")
 
 
 def w3_gemv(x, planes, scales, zeros, perm, out, *, decoded_bf16=False, group_partials=False,

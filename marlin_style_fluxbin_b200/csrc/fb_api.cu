@@ -149,8 +149,8 @@ extern "C" int64_t fb_query(const char* key) {
   if (!strcmp(key, "w3_max_m")) return 4;            // table-lookup kernel
   if (!strcmp(key, "w3_mma_max_m")) return 16;       // tensor-core kernel
   if (!strcmp(key, "w3_max_splits")) return 16;      // contributions combined per output
-  if (!strcmp(key, "w3_ctas_per_sm")) return 1;
-  if (!strcmp(key, "w3_smem_bytes")) return 2 * 32768 + 16 * 3 * 3072 + 16 * 3 * 8;  // M = 1: two table sets + per-warp rings + barriers
+  if (!strcmp(key, "w3_ctas_per_sm")) return 2;
+  if (!strcmp(key, "w3_smem_bytes")) return 32768 + 8 * 3 * 3328 + 8 * 3 * 8;  // M = 1: tables + per-warp rings (planes, scales, zero points) + barriers
   if (!strcmp(key, "tp_max_world")) return 8;
   if (!strcmp(key, "sm_count") || !strcmp(key, "max_smem")) {
     const fb::DeviceInfo* info = fb::device_info();

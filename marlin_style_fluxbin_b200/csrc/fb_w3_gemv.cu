@@ -17,14 +17,14 @@
 //    private ring of staged units and refills a slot as soon as it has read it, so warps never
 //    wait for one another between table builds; scales and zero points come straight from
 //    global memory, requested before the lookups and used after them.
-//  * One CTA of 16 warps per SM (the whole register file): each K super-block is served by
-//    floor(SMs / super-blocks) CTAs that split its rows, so the 32 KB of tables of a K block are
-//    built once per SM and shared by 16 warps.
-//  * A CTA that walks several K blocks (K > 4096) keeps two table sets (M = 1): the tables of
-//    the next K block are built before the current block's lookups, one barrier per block.
-//    A warp whose rows are a single unit carries its sum across the K blocks in registers.
-//  * Scales and zero points of a unit are requested from global memory one unit ahead of their
-//    use, so HBM latency never sits between a unit's lookups and its result.
+//  * Two CTAs of 8 warps per SM (together the whole register file; 110 KB of shared memory each
+//    with M = 1): each K super-block is served by floor(2 SMs / super-blocks) CTAs that split its
+//    rows.  Two smaller CTAs beat one of 16 warps: when the first of a pair leaves, CTAs of the
+//    next kernel in the stream move in and stage weights beside the one still running.
+//  * A warp whose rows are a single unit carries its sum across the K blocks its CTA walks
+//    (K > 4096) in registers; otherwise the running sums go through an L2-resident scratch.
+//  * Scales and zero points of a unit ride with its planes (two more small tiled copies into
+//    the same ring slot), so HBM latency never sits between a unit's lookups and its result.
 //  * Two lookups are accumulated by one packed fp32x2 add or multiply-add (an even-step and an
 //    odd-step partial sum share a 64-bit register pair; the plane weights 1, 2, -4 ride in the
 //    multiply-add), which halves the arithmetic of the main loop and leaves four accumulators.
@@ -56,7 +56,8 @@ using namespace fb;
 constexpr int kUnitRows = 32;
 constexpr int kPlaneTile = kUnitRows * 16;      // 512 B: one plane of one group for a unit
 constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B of planes staged per unit
-constexpr int kWarps = 16;
+constexpr int kWarps = 8;
+constexpr int kCtasPerSm = 2;
 constexpr int kMaxM = 4;
 constexpr int kMaxSplits = 16;  // partial sums per output (one arrival count of 6 bits, 52-bit fixed-point sum)
 constexpr int kMaxMatrices = 4;
@@ -108,20 +109,18 @@ struct W3Params {
 // Shared-memory geometry.  Entry p of table t for activation row m lives at byte
 //   p * kStride + m * 128 + t * 4,   kStride = 128 * (M rounded up to a power of two),
 // so with M = 1 the 32 tables of a K block take 32 KB and the bank of a lookup is the table
-// number.  M = 1 keeps two table sets (the next K block's are built during this block's
-// lookups); the ring holds three staged units per warp, two when the tables take 128 KB.
+// number.  The ring holds three staged units per warp, two when the tables take 128 KB.
 template <int M>
 struct Geom {
   static constexpr int kStrideLog = 7 + (M == 1 ? 0 : (M == 2 ? 1 : 2));
   static constexpr int kStride = 1 << kStrideLog;
   static constexpr int kLutBytes = 256 << kStrideLog;
-  static constexpr int kLutSets = M == 1 ? 2 : 1;
   static constexpr int kStages = M <= 2 ? 3 : 2;
   // a staged unit: its planes, then (M <= 2; with 128 KB of tables there is no room) its scales at
   // +3072 (2 groups x 64 B) and its zero points at +3200 (2 groups x 32 B)
   static constexpr bool kStageAux = M <= 2;
   static constexpr int kSlotBytes = kUnitBytes + (kStageAux ? 256 : 0);
-  static constexpr int kRingOffset = kLutSets * kLutBytes;
+  static constexpr int kRingOffset = kLutBytes;
   static constexpr int kBarOffset = kRingOffset + kWarps * kStages * kSlotBytes;
   static constexpr int kSmemBytes = kBarOffset + kWarps * kStages * 8;
 };
@@ -204,7 +203,7 @@ __device__ __forceinline__ void emit_combined(const W3Params& p, int m, int ru, 
 }
 
 template <int M, bool CORRECT>
-__global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_constant__ W3Params p) {
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const __grid_constant__ W3Params p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   using G_ = Geom<M>;
   constexpr int kStages = G_::kStages;
@@ -237,8 +236,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   const int rb = lane & 3, rh = (lane >> 2) & 1, rw = (lane >> 3) & 3;
   // Per-lane constants of the rotated walk, all as 32-bit shared-memory addresses / offsets so
   // that the hot loop does no 64-bit pointer arithmetic.  A lookup is: one 4-way byte dot product
-  // (entry * stride + table address), the shared-memory load, and half a packed add.  The table
-  // addresses xl[] point into the table set in use and are flipped to the other set per K block.
+  // (entry * stride + table address), the shared-memory load, and half a packed add.
   const uint32_t lut_u32 = smem_u32(lut);
   uint32_t sel[4], xl[2][4][4], woff[2][4];
 #pragma unroll
@@ -407,13 +405,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   }
   for (int t = 1; t < kStages && pf_left > 0; ++t) issue_next();  // the rest of the ring, behind the activation loads
 
-  // ---- build the 32 tables of K block kb_ into table set `set`: lane = table; warp w owns the
-  // entries whose low nibble is w, so that the walk over the high nibble unrolls with constant
-  // offsets.  sx[m][jh]: the sum of the activations of the group this lane walks in half jh. ----
-  auto build = [&](int kb_, int set, float (&sx)[M][2]) {
+  // ---- build the 32 tables of K block kb_: lane = table; warp w owns the entries whose low
+  // nibble is 2w or 2w + 1, so that the walk over the high nibble unrolls with constant offsets.  sx[m][jh]: the sum of the activations of the group this lane walks in half jh. ----
+  auto build = [&](int kb_, float (&sx)[M][2]) {
     const int g = 2 * kb_ + (lane >> 4);
     const int kbase = g * 128 + (lane & 15) * 8;
-    unsigned char* const tables = lut + (size_t)set * G_::kLutBytes;
+    unsigned char* const tables = lut;
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float v8[8];
@@ -519,7 +516,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
   int c_slot = 0;
   uint32_t c_phase = 0;
   bool dead = false;
-  float sx_cur[M][2], sx_nxt[M][2];
+  float sx_cur[M][2];
 
   // ---- the units of this warp for K block kb = kb_begin + s ----
   auto run_block = [&](int s) {
@@ -680,44 +677,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) w3_gemv_kernel(const __grid_co
       }
     }
   };
-  // the table addresses of the walk point into set 0; move them to the other set and back
-  uint32_t set_step = (uint32_t)G_::kLutBytes;
-  auto flip_tables = [&]() {
-#pragma unroll
-    for (int jh = 0; jh < 2; ++jh)
-#pragma unroll
-      for (int jw = 0; jw < 4; ++jw)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) xl[jh][jw][b] += set_step;
-    set_step = 0u - set_step;
-  };
-
-  build(kb_begin, 0, sx_cur);
+  build(kb_begin, sx_cur);
   __syncthreads();
   for (int s = 0; s < nS; ++s) {
-    const bool more = s + 1 < nS;
-    if (G_::kLutSets == 2) {
-      // the other table set is free (everyone left it at the last barrier): build ahead
-      if (more) build(kb_begin + s + 1, (s + 1) & 1, sx_nxt);
-      if (!dead) run_block(s);
-      if (more) {
-        __syncthreads();
-        flip_tables();
-      }
-    } else {
-      if (!dead) run_block(s);
-      if (more) {
-        __syncthreads();  // everyone has finished reading the tables
-        build(kb_begin + s + 1, 0, sx_nxt);
-        __syncthreads();
-      }
-    }
-    if (more) {
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        sx_cur[m][0] = sx_nxt[m][0];
-        sx_cur[m][1] = sx_nxt[m][1];
-      }
+    if (!dead) run_block(s);
+    if (s + 1 < nS) {
+      __syncthreads();  // everyone has finished reading the tables
+      build(kb_begin + s + 1, sx_cur);
+      __syncthreads();
     }
   }
   settle();
@@ -744,7 +711,7 @@ Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   Plan plan;
   plan.S = (nKB + kMaxSplits - 1) / kMaxSplits;
   plan.nSB = (nKB + plan.S - 1) / plan.S;
-  int c = info.sm_count / plan.nSB;
+  int c = kCtasPerSm * info.sm_count / plan.nSB;
   if (c < 1) c = 1;
   if (c > nRU) c = nRU;
   plan.slices = c;
