@@ -451,8 +451,11 @@ def run_tensor_parallel(args, rank, world, local_rank):
                     graph.replay()
                 end.record(stream)
                 barrier()
-                held = max(1, int(500.0 / max(begin.elapsed_time(end) / args.steps, 1e-3)))  # half a second more under the sampler
-                for _ in range(held):
+                # about half a second more under the sampler; every rank must replay the same number
+                # of times (each replay waits for the peers' contributions), so the count is agreed on
+                pace = torch.tensor([begin.elapsed_time(end) / args.steps], device=device, dtype=torch.float64)
+                torch.distributed.all_reduce(pace, op=torch.distributed.ReduceOp.MAX)
+                for _ in range(max(1, int(500.0 / max(float(pace[0]), 1e-3)))):
                     graph.replay()
                 barrier()
             step_ms = begin.elapsed_time(end) / args.steps
