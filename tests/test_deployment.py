@@ -245,7 +245,7 @@ def test_dense_oracle_tolerance_and_interleaved_equals_planar():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("o,k", ((4096, 4096), (1024, 4096), (4096, 12288), (96, 256)))
+@pytest.mark.parametrize("o,k", ((4096, 4096), (1024, 4096), (12288, 4096), (4096, 12288), (96, 256)))
 def test_global_two_base_kernel(o, k):
     layout, bases, x = make_global_case(o, k, seed=o + k)
     sign_planes = np.ascontiguousarray(np.packbits((bases.numpy() > 0), axis=-1, bitorder="little"))
@@ -268,6 +268,37 @@ def test_global_two_base_kernel(o, k):
     twice = out.float() * 2
     assert float((doubled.float() != twice).float().mean()) <= 5e-3
     assert float((doubled.float() - twice).abs().max()) <= float(twice.abs().max()) * 2.0 ** -7
+
+
+@pytest.mark.gpu
+def test_two_base_kernels_carry_large_finite_activations():
+    """Residual-stream outliers (a few activations in the thousands) must go through the fixed-point
+    combine over the groups like the reference's fp32 accumulation carries them: both scale
+    conventions against their fp64 oracles."""
+    o, k = 1024, 2048
+    layout, bases, x = make_global_case(o, k, seed=5)
+    x = x.float()
+    x[0, [3, 700, 2047]] = torch.tensor([3000.0, -2200.0, 3800.0])
+    x = x.bfloat16()
+    sign_planes = np.ascontiguousarray(np.packbits((bases.numpy() > 0), axis=-1, bitorder="little"))
+    ref = orc.bb_global_gemv_f64(orc.bits(x), orc.BF16, sign_planes, orc.bits(layout["row_scales"]), orc.bits(layout["column_scales"]),
+                                 layout["salient_indices"].numpy(), orc.bits(layout["salient_values"]))
+    out = torch.full((1, o), float("nan"), device="cuda", dtype=torch.bfloat16)
+    binary_global.global_two_base_m1_out(x.cuda(), {name: value.cuda() for name, value in layout.items()}, out)
+    got = out.float().cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all() and np.abs(got - ref).max() / np.abs(ref).max() <= 1e-2
+    # the reference's hybrid payload (per-group fp32 scales of the size its quantiser produces)
+    payload = make_payload(256, 4, seed=11)
+    kernel_layout = convert_artifact(payload, kernel="v5")
+    xh = torch.randn(1, 512, generator=torch.Generator().manual_seed(3))
+    xh[0, [0, 130, 511]] = torch.tensor([2500.0, -3100.0, 1900.0])
+    xh = xh.bfloat16()
+    want = _structural(xh, kernel_layout).numpy().astype(np.float64).reshape(1, -1)
+    outh = torch.full((1, 256), float("nan"), device="cuda", dtype=torch.bfloat16)
+    workspace = torch.empty(workspace_shape(256, 512, 1, kernel="v5"), device="cuda")
+    m1_out(xh.cuda(), {name: value.cuda() for name, value in kernel_layout.items()}, outh, workspace, groups_per_split=1, kernel="v5")
+    goth = outh.float().cpu().numpy().astype(np.float64)
+    assert np.isfinite(goth).all() and np.abs(goth - want).max() / np.abs(want).max() <= 1e-2
 
 
 @pytest.mark.gpu

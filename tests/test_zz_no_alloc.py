@@ -10,13 +10,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _problem(o, k, seed):
+def _problem(o, k, seed, m=1):
     gen = torch.Generator().manual_seed(seed)
     groups = k // 128
     planes = torch.randint(0, 256, (groups, 3, o, 16), generator=gen, dtype=torch.uint8).cuda()
     scales = (torch.rand(groups, o, generator=gen) * 0.015 + 0.005).half().cuda()
     zeros = torch.randint(3, 5, (groups, o), generator=gen, dtype=torch.uint8).cuda()
-    x = torch.randn(1, k, generator=gen).bfloat16().cuda()
+    x = torch.randn(m, k, generator=gen).bfloat16().cuda()
     return x, planes, scales, zeros
 
 
@@ -34,6 +34,33 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
             torch.cuda.synchronize()
             assert bool(torch.isfinite(got).all()), (o, k, repeat)
             torch.testing.assert_close(got.float(), expected.float(), rtol=0, atol=0)
+
+
+def test_static_scratch_with_several_rows_and_with_a_long_k():
+    """Four activation rows use four times the combine words; K = 12288 makes a CTA walk three K
+    blocks (running sums in registers, or in the partials area of the array behind the combine words)."""
+    from marlin_style_fluxbin_b200 import _native
+
+    for o, k, m in ((2048, 1024, 4), (4096, 12288, 1), (1024, 12288, 2)):
+        x, planes, scales, zeros = _problem(o, k, seed=o + k + m, m=m)
+        assert _native.w3_scratch_bytes(m, o, k) <= _native.FB_W3_STATIC_SCRATCH_BYTES
+        expected = torch.full((m, o), float("nan"), device="cuda", dtype=torch.bfloat16)
+        scratch = torch.zeros(_native.w3_scratch_bytes(m, o, k), dtype=torch.uint8, device="cuda")
+        _native.w3_gemv(x, planes, scales, zeros, None, expected, scratch=scratch)
+        for _ in range(2):
+            got = torch.full((m, o), float("nan"), device="cuda", dtype=torch.bfloat16)
+            _native.w3_gemv_static(x, planes, scales, zeros, None, got)
+            torch.cuda.synchronize()
+            assert torch.equal(got, expected), (o, k, m)
+    if torch.cuda.device_count() > 1:  # the array exists once per GPU: its address is looked up per device
+        with torch.cuda.device(1):
+            x, planes, scales, zeros = (t.to("cuda:1") for t in _problem(1024, 2048, seed=3))
+            want = torch.empty(1, 1024, device="cuda:1", dtype=torch.bfloat16)
+            _native.w3_gemv(x, planes, scales, zeros, None, want, scratch=torch.zeros(_native.w3_scratch_bytes(1, 1024, 2048), dtype=torch.uint8, device="cuda:1"))
+            got = torch.empty_like(want)
+            _native.w3_gemv_static(x, planes, scales, zeros, None, got)
+            torch.cuda.synchronize("cuda:1")
+            assert torch.equal(got, want)
 
 
 def test_static_scratch_rejects_oversized_problem_without_launching():
