@@ -617,9 +617,23 @@ def small_case(args):
 
     from marlin_style_fluxbin_b200.w3_lut_deployment import w3_lut_gemv_out, w3_lut_m1_out, workspace_shape
 
-    o, k = (int(v) for v in args.case.lower().split("x"))
     device = torch.device("cuda", 0)
     gen = torch.Generator(device=device).manual_seed(1)
+    if args.case.lower().startswith("lm_head:"):  # the fused LM head on a VxK bf16 weight, a few launches
+        from marlin_style_fluxbin_b200 import _native
+
+        v, k = (int(n) for n in args.case.split(":")[1].lower().split("x"))
+        weight = (torch.randn(v, k, device=device, generator=gen) * 0.02).bfloat16()
+        x = torch.randn(1, k, device=device, generator=gen).bfloat16()
+        norm = torch.ones(k, device=device, dtype=torch.bfloat16)
+        best = torch.zeros(1, dtype=torch.long, device=device)
+        scratch = torch.zeros(_native.lm_head_scratch_bytes(), dtype=torch.uint8, device=device)
+        for _ in range(args.copies):
+            _native.lm_head_argmax(x, norm, 1e-6, weight, best, scratch=scratch)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "launches": args.copies, "bytes_per_launch": v * k * 2, "choice": int(best[0])}))
+        return
+    o, k = (int(v) for v in args.case.lower().split("x"))
     layouts = [synthetic_layout(torch, o, k, device, gen) for _ in range(args.copies)]
     x = torch.randn(args.rows, k, device=device, generator=gen).bfloat16()
     out = torch.empty(args.rows, o, device=device, dtype=torch.bfloat16)
@@ -645,7 +659,8 @@ def main():
                         help="gemv (default): the seven Linear shapes (plus, on one GPU, the two-base kernel and the 8B decode; "
                              "on several, the tensor-parallel 32B-shaped decode); the others run one part alone")
     parser.add_argument("--case", default=None, metavar="OxK",
-                        help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit")
+                        help="profiling helper: launch the GEMV of one shape on --copies distinct weights and exit "
+                             "(lm_head:VxK launches the fused LM head --copies times instead)")
     parser.add_argument("--prompt-tokens", type=int, default=512, help="decode-8b: prompt length")
     parser.add_argument("--decode-tokens", type=int, default=32, help="decode-8b: tokens decoded in the graph")
     parser.add_argument("--packed-arm-only", action="store_true", help="decode-8b: skip the BF16 arm (for profiler launch lists)")
