@@ -538,8 +538,10 @@ def run_decode(torch, shape_name, prompt, steps, rank, world, local_rank, arms=(
         if truth_logits is not None:
             entry["logits_nrmse_vs_fp32"] = nrmse(logits, truth_logits)
             entry["greedy_agreement_with_fp32"] = round(float((greedy == truth_logits.argmax(-1)).float().mean()), 4)
+            entry["steps_differing_from_fp32"] = (greedy != truth_logits.argmax(-1)).nonzero().flatten().tolist()
         if arm != arms[0]:
             entry["greedy_agreement_forced"] = round(float((greedy == traces[arms[0]][0]).float().mean()), 4)
+            entry[f"steps_differing_from_{arms[0]}_arm"] = (greedy != traces[arms[0]][0]).nonzero().flatten().tolist()
             entry[f"logits_nrmse_vs_{arms[0]}_arm"] = nrmse(logits, traces[arms[0]][1])
         if engine_arm == "bf16":
             weights = sum(v.numel() * 2 for layer in engine.layers for v in layer.dense.values()) + engine.lm_head.numel() * 2
