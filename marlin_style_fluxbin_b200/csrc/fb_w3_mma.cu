@@ -6,13 +6,17 @@
 // shared-memory operand tile and lets one tcgen05.mma apply it to all rows of the batch:
 //   * a CTA owns 128 output rows and a contiguous range of K groups (split-K over CTAs);
 //   * the three bit planes of (group, 128 rows) arrive by one tiled TMA copy (6 KB);
-//   * 256 threads turn them into a 128 x 128 tile of 16-bit weights T((code - zero) * T(scale)),
-//     written straight in the K-major "core matrix" order that the MMA's shared-memory descriptor
-//     walks (8 rows x 16 bytes per core matrix, no swizzle): one 16-byte store per 8 weights;
+//   * 256 threads turn them into a 128 x 128 tile of 16-bit weights T((code - zero) * T(scale)):
+//     every 4 plane bits index a 16-entry table of four 16-bit floats (0 / 1), kept in sixteen
+//     bank-disjoint copies, and packed 16-bit multiply-adds combine the planes, the zero point
+//     and the scale; tiles are written straight in the K-major "core matrix" order that the MMA's
+//     shared-memory descriptor walks (8 rows x 16 bytes per core matrix, no swizzle): one 16-byte
+//     store per 8 weights;
 //   * the activations of the group (M rows padded to N = 16) are stored the same way;
-//   * one thread issues 8 x tcgen05.mma (128 x 16 x 16 each), accumulating in 16 TMEM columns
-//     over all groups of the CTA; tiles are double-buffered, so the next group is dequantised
-//     while the tensor core works;
+//   * warp-specialised: eight warps dequantise, the elected lane of a ninth issues the plane
+//     copies and 8 x tcgen05.mma (128 x 16 x 16 each) per group, accumulating in 16 TMEM columns
+//     over all groups of the CTA; tiles are double-buffered and the two sides meet on mbarriers
+//     only (tile complete: 256 arrivals; buffer free: the MMAs' commit), never on a CTA barrier;
 //   * the 128 x 16 fp32 result is read back with tcgen05.ld and either written (one split) or
 //     combined across splits with the 64-bit fixed-point atomic of the M = 1 kernel.
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status, frees its TMEM
@@ -25,7 +29,7 @@
 #include <cudaTypedefs.h>
 
 #include <mutex>
-#include <unordered_map>
+#include <type_traits>
 
 #include "fb_common.cuh"
 
@@ -35,7 +39,8 @@ using namespace fb;
 
 constexpr int kTileRows = 128;
 constexpr int kN = 16;            // activation rows presented to the MMA (M padded)
-constexpr int kThreads = 256;
+constexpr int kProducers = 256;       // eight warps that dequantise
+constexpr int kThreads = kProducers + 32;  // and one warp whose elected lane issues the copies and the MMAs
 constexpr int kATile = kTileRows * 128 * 2;  // 32 KB: 128 rows x 128 k, 16-bit
 constexpr int kBTile = kN * 128 * 2;         // 4 KB
 constexpr int kPlaneTile = 3 * kTileRows * 16;  // 6 KB: three planes of 128 rows
@@ -81,17 +86,29 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
   unsigned char* const a_tiles = smem;                           // 2 x 32 KB
   unsigned char* const b_tiles = smem + 2 * kATile;              // 2 x 4 KB
   unsigned char* const planes_s = b_tiles + 2 * kBTile;          // 2 x 6 KB
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(planes_s + 2 * kPlaneTile);  // plane_full[2], mma_done[2], all_done
-  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(planes_s + 2 * kPlaneTile);  // plane_full[2], mma_done[2], all_done, tile_full[2]
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  // Nibble table: entry e (4 plane bits) -> four 16-bit floats, 1.0 where the bit is set.  Sixteen
+  // copies side by side (entry stride 128 B, copy stride 8 B): lane l reads copy l % 16, so the 16
+  // lanes of a half-warp phase of an 8-byte load hit 16 different 8-byte bank groups whatever the
+  // weights are.
+  // The table starts on a 2 KB boundary (found at run time inside 4 KB of slack), so that entry
+  // offset (bits 7..10), copy offset (bits 3..6) and base combine with one logic instruction.
+  unsigned char* const nibbles = planes_s + 2 * kPlaneTile + 64 + ((2048u - ((smem_u32(planes_s) + 2 * kPlaneTile + 64) & 2047u)) & 2047u);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, split = blockIdx.y;
   const int g_begin = split * p.groups_per_split, g_end = min(p.G, g_begin + p.groups_per_split);
   const int ng = g_end - g_begin;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (tid < 5) {
-    mbar_init(smem_u32(&bars[tid]), 1);
+  if (tid < 7) {
+    mbar_init(smem_u32(&bars[tid]), tid < 5 ? 1 : kProducers);  // a finished tile: every producer thread arrives
     mbar_init_fence();
+  }
+  if (tid < kProducers) {
+    const uint32_t one = BF16 ? 0x3f80u : 0x3c00u, entry = (uint32_t)tid >> 4;
+    const uint2 halves = make_uint2(((entry & 1u) ? one : 0u) | (((entry & 2u) ? one : 0u) << 16), ((entry & 4u) ? one : 0u) | (((entry & 8u) ? one : 0u) << 16));
+    *reinterpret_cast<uint2*>(nibbles + entry * 128 + (tid & 15) * 8) = halves;  // 256 threads: 16 entries x 16 copies
   }
   if (warp == 0) {  // TMEM columns for the 128 x 16 fp32 accumulator
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
@@ -111,7 +128,8 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
         "l"(&p.plane_map), "r"(0), "r"(tile * (kTileRows / 32)), "r"(3 * (g_begin + gi)), "r"(bar)
         : "memory");
   };
-  if (tid == 0) {  // weights never change: staged before the wait on the previous kernel
+  const bool issuer = tid == kProducers;  // lane 0 of the ninth warp
+  if (issuer) {  // weights never change: staged before the wait on the previous kernel
     if (ng > 0) issue_planes(0);
     if (ng > 1) issue_planes(1);
   }
@@ -121,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
   const uint32_t format = p.act_dtype == FB_BF16 ? 1u : 0u;
   const uint32_t idesc = (1u << 4) | (format << 7) | (format << 10) | ((uint32_t)(kN >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
 
-  const int row_in_tile = tid & 127, khalf = tid >> 7;  // dequantisation: one row, 8 of its 16 chunks
+  const int row_in_tile = tid & 127, khalf = (tid >> 7) & 1;  // dequantisation: one row, 8 of its 16 chunks
   const int row = tile * kTileRows + row_in_tile;
   const int xn = tid >> 4, xc = tid & 15;  // activation tile: row of the batch, chunk of 8 inputs
   bool dead = false;
@@ -154,9 +172,32 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
       }
     }
   };
-  if (ng > 0) fetch_group(g_begin);
+  // ---- the issuing lane: for every group, wait for its tile, run the eight MMAs, signal the
+  // buffer free through the MMAs' completion, and stage the planes of two groups ahead (every
+  // producer has read this buffer's planes once the tile is complete).  No CTA-wide barrier in
+  // the loop: producers and issuer meet on mbarriers only. ----
+  if (issuer) {
+    for (int gi = 0; gi < ng; ++gi) {
+      const int buf = gi & 1;
+      if (!mbar_wait_bounded(smem_u32(&bars[5 + buf]), (uint32_t)((gi >> 1) & 1))) {
+        dead = true;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_base = smem_u32(a_tiles + (size_t)buf * kATile), b_base = smem_u32(b_tiles + (size_t)buf * kBTile);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)  // K = 16 per instruction: two chunks
+        mma_f16(tmem_base, smem_desc(a_base + j * 2 * 2048, 2048, 128), smem_desc(b_base + j * 2 * 256, 256, 128), idesc,
+                (gi > 0 || j > 0) ? 1u : 0u);
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[2 + buf])) : "memory");
+      if (gi + 2 < ng) issue_planes(gi + 2);
+    }
+    if (!dead) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[4])) : "memory");
+  }
 
-  for (int gi = 0; gi < ng; ++gi) {
+  if (tid < kProducers && ng > 0) fetch_group(g_begin);
+
+  for (int gi = 0; gi < ng && tid < kProducers; ++gi) {
     const int buf = gi & 1;
     const float scale = row < p.O ? bits_to_float((unsigned short)scale_bits_next, p.scale_dtype) : 0.f;
     const float zero = (float)zero_bits_next;
@@ -166,7 +207,7 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
     bool ok = true;
     if (gi >= 2) ok = mbar_wait_bounded(smem_u32(&bars[2 + buf]), (uint32_t)(((gi >> 1) - 1) & 1));
     ok = ok && mbar_wait_bounded(smem_u32(&bars[buf]), (uint32_t)((gi >> 1) & 1));
-    if (__syncthreads_or(!ok)) {
+    if (!ok) {
       dead = true;
       break;
     }
@@ -177,69 +218,63 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
       const unsigned char* pl = planes_s + (size_t)buf * kPlaneTile + row_in_tile * 16 + khalf * 8;
       const uint2 w0 = *reinterpret_cast<const uint2*>(pl), w1 = *reinterpret_cast<const uint2*>(pl + kTileRows * 16),
                   w2 = *reinterpret_cast<const uint2*>(pl + 2 * kTileRows * 16);
-      // weight = T((code - zero) * T(scale)) with packed 16-bit arithmetic: the pair of codes is
-      // built as the 16-bit floats (magic + code), magic = 128 (bf16) or 1024 (fp16), where small
-      // integers are exact; one packed subtract removes magic + zero exactly, one packed multiply
-      // applies the scale with a single rounding, as the reference's dense fallback rounds.
+      // weight = T((code - zero) * T(scale)) in packed 16-bit arithmetic.  Each plane byte is two
+      // nibbles; a nibble's four bits come back from the table as four 16-bit floats (0 or 1), so
+      // code - 4 = t0 + 2 t1 - 4 t2' (the high plane is stored inverted) is two packed multiply-adds
+      // on exact small integers, one packed add moves the zero point (4 - zero), and one packed
+      // multiply applies the scale with a single rounding, as the reference's dense fallback rounds.
       constexpr bool bf16 = BF16;
-      const uint32_t magic = bf16 ? 0x43004300u : 0x64006400u;
-      uint32_t offset2, scale2;
+      using Pair = typename std::conditional<BF16, __nv_bfloat162, __half2>::type;
+      auto as_pair = [](uint32_t bits) { return *reinterpret_cast<const Pair*>(&bits); };
+      auto as_bits = [](Pair v) { return *reinterpret_cast<const uint32_t*>(&v); };
+      const Pair two = as_pair(bf16 ? 0x40004000u : 0x40004000u), minus_four = as_pair(bf16 ? 0xc080c080u : 0xc400c400u);
+      Pair shift2, scale2;
       if (bf16) {
-        const __nv_bfloat162 o2 = __float2bfloat162_rn(128.f + zero), s2 = __float2bfloat162_rn(scale);
-        offset2 = *reinterpret_cast<const uint32_t*>(&o2);
-        scale2 = *reinterpret_cast<const uint32_t*>(&s2);
+        const __nv_bfloat162 o2 = __float2bfloat162_rn(4.f - zero), s2 = __float2bfloat162_rn(scale);
+        shift2 = *reinterpret_cast<const Pair*>(&o2);
+        scale2 = *reinterpret_cast<const Pair*>(&s2);
       } else {
-        const __half2 o2 = __float2half2_rn(1024.f + zero), s2 = __float2half2_rn(scale);
-        offset2 = *reinterpret_cast<const uint32_t*>(&o2);
-        scale2 = *reinterpret_cast<const uint32_t*>(&s2);
+        const __half2 o2 = __float2half2_rn(4.f - zero), s2 = __float2half2_rn(scale);
+        shift2 = *reinterpret_cast<const Pair*>(&o2);
+        scale2 = *reinterpret_cast<const Pair*>(&s2);
       }
+      const uint32_t table = smem_u32(nibbles) + (uint32_t)((lane & 15) * 8);
+      auto nibble = [&](uint32_t word, int bit) {  // the table row of bits [bit, bit + 4) of `word`
+        const uint32_t offset = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
+        uint2 v;
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"((offset & 0x780u) | table));
+        return v;
+      };
       unsigned char* const a_row = a_tiles + (size_t)buf * kATile + (row_in_tile >> 3) * 128 + (row_in_tile & 7) * 16;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        const uint32_t b0 = ((c < 4 ? w0.x : w0.y) >> (8 * (c & 3))) & 0xffu;
-        const uint32_t b1 = ((c < 4 ? w1.x : w1.y) >> (8 * (c & 3))) & 0xffu;
-        const uint32_t b2 = ((c < 4 ? w2.x : w2.y) >> (8 * (c & 3))) & 0xffu;  // stored inverted: code bit 2 = 1 - b2
-        // low half: the byte; high half: the byte shifted right by one; even bit positions only
-        const uint32_t e0 = (b0 * 0x8001u) & 0x00550055u, e1 = (b1 * 0x8001u) & 0x00550055u,
-                       e2 = ((b2 ^ 0xffu) * 0x8001u) & 0x00550055u;
-        const uint32_t low2 = e0 + 2u * e1, high = e2 << 2;
+        const uint32_t p0 = c < 4 ? w0.x : w0.y, p1 = c < 4 ? w1.x : w1.y, p2 = c < 4 ? w2.x : w2.y;
         uint32_t packed[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          // codes of inputs 2i (low half) and 2i+1 (high half) as 16-bit floats magic + code
-          const uint32_t pair = ((((low2 >> (2 * i)) & 0x00030003u) | ((high >> (2 * i)) & 0x00040004u))) | magic;
-          if (bf16) {
-            const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pair), *reinterpret_cast<const __nv_bfloat162*>(&offset2)),
-                                             *reinterpret_cast<const __nv_bfloat162*>(&scale2));
-            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
-          } else {
-            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&offset2)),
-                                      *reinterpret_cast<const __half2*>(&scale2));
-            packed[i] = *reinterpret_cast<const uint32_t*>(&v);
+        for (int h = 0; h < 2; ++h) {  // low nibble: inputs 0..3 of the chunk, high nibble: inputs 4..7
+          const int bit = 8 * (c & 3) + 4 * h;
+          const uint2 t0 = nibble(p0, bit), t1 = nibble(p1, bit), t2 = nibble(p2, bit);
+          const uint32_t t0w[2] = {t0.x, t0.y}, t1w[2] = {t1.x, t1.y}, t2w[2] = {t2.x, t2.y};
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            Pair v = __hfma2(as_pair(t1w[i]), two, as_pair(t0w[i]));
+            v = __hfma2(as_pair(t2w[i]), minus_four, v);
+            packed[2 * h + i] = as_bits(__hmul2(__hadd2(v, shift2), scale2));
           }
         }
         *reinterpret_cast<uint4*>(a_row + (size_t)(khalf * 8 + c) * 2048) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
     }
-    // generic-proxy stores must be visible to the tensor core's (async proxy) reads
+    // generic-proxy stores must be visible to the tensor core's (async proxy) reads; then this
+    // thread's part of the tile is done
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_base = smem_u32(a_tiles + (size_t)buf * kATile), b_base = smem_u32(b_tiles + (size_t)buf * kBTile);
-#pragma unroll
-      for (int j = 0; j < 8; ++j)  // K = 16 per instruction: two chunks
-        mma_f16(tmem_base, smem_desc(a_base + j * 2 * 2048, 2048, 128), smem_desc(b_base + j * 2 * 256, 256, 128), idesc,
-                (gi > 0 || j > 0) ? 1u : 0u);
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[2 + buf])) : "memory");
-      if (gi + 2 < ng) issue_planes(gi + 2);  // every thread has read this buffer's planes
-    }
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[5 + buf])) : "memory");
   }
 
   // ---- all MMAs done: read the accumulator back ----
-  if (!dead) {
-    if (tid == 0) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[4])) : "memory");
-    const bool ok = ng == 0 || mbar_wait_bounded(smem_u32(&bars[4]), 0u);
+  // (a thread whose bounded wait expired arrives here with `dead` set; the others' waits expire in turn)
+  {
+    const bool ok = !dead && (ng == 0 || mbar_wait_bounded(smem_u32(&bars[4]), 0u));
     if (__syncthreads_or(!ok)) dead = true;
   }
   if (dead) {
@@ -350,7 +385,7 @@ extern "C" int fb_w3_gemm_small(const void* x, int act_dtype, int m, const uint8
   p.groups_per_split = (G + splits - 1) / splits;
   p.splits = (G + p.groups_per_split - 1) / p.groups_per_split;
 
-  const size_t smem = 2 * (size_t)kATile + 2 * kBTile + 2 * kPlaneTile + 64;
+  const size_t smem = 2 * (size_t)kATile + 2 * kBTile + 2 * kPlaneTile + 64 + 4096;
   static std::mutex lock;
   static bool ready[64] = {};
   int device = 0;
