@@ -1,13 +1,16 @@
 // Two-base binary-basis GEMV, M = 1:  W ~ sum_b diag(row_b) * B_b * diag(col_b), B_b in {-1,+1},
 // packed one bit per weight per base, in groups of 128 inputs.
 //
-// Same skeleton as the W3 GEMV (HBM-bound byte work, see fb_w3_gemv.cu): a K block is ONE group;
-// a CTA holds 32 signed activation tables for it (2 bases x 16 chunks of 8 inputs, entries are
+// Same skeleton as the W3 GEMV (HBM-bound byte work, see fb_w3_gemv.cu): a K block is TWO groups
+// (one for matrices of fewer than 128 row units);
+// a CTA holds 32 signed activation tables per group (2 bases x 16 chunks of 8 inputs, entries are
 // sums of +/- x*col in ascending order) laid out entry-major so that the bank of a lookup is the
-// table number; lane = output row; lanes walk the 32 (base, chunk) pairs in a lane-rotated order
-// so that lookups and staged-word reads are bank-conflict free; a warp's rows are one contiguous
-// run of 32-byte code rows, staged by a single bulk copy; the split over groups is combined in the
-// kernel by one 64-bit fixed-point atomic add per contribution (order-independent, repeat-exact).
+// table number; lane = output row; lanes walk the 32 (base, chunk) pairs of a group in a
+// lane-rotated order so that lookups and staged-word reads are bank-conflict free; a warp's rows
+// are, per group, one contiguous run of 32-byte code rows, staged by a bulk copy; the split over
+// the K blocks is combined in the kernel by one 64-bit fixed-point atomic add per contribution
+// (order-independent, repeat-exact).  Two groups per unit halve the fixed cost per byte of a unit
+// (staging, scale loads, the returning atomic) and the atomics per output row.
 //
 // Two scale conventions:
 //  * group mode (the reference's hybrid g128-s8 payload, deployment.py:23-27, kernel
@@ -26,12 +29,12 @@ namespace {
 using namespace fb;
 
 constexpr int kUnitRows = 32;
-constexpr int kUnitBytes = kUnitRows * 32;  // 1 KB of codes per unit
+constexpr int kGroupBytes = kUnitRows * 32;  // 1 KB of codes per unit and group
 constexpr int kWarps = 8;
 constexpr int kCtasPerSm = 2;
-constexpr int kMaxSlots = 4;
-constexpr int kLutBytes = 32768;            // 256 entries x 32 tables x 4 B
-constexpr int kSparseLutBytes = 2048;       // 2 tables x 256 entries
+constexpr int kMaxSlots = 4;                // staged units per warp: at most 4 KB in flight per warp
+constexpr int kGroupLutBytes = 32768;       // 256 entries x 32 tables x 4 B
+constexpr int kGroupSparseBytes = 2048;     // 2 tables x 256 entries
 
 struct BBParams {
   const void* x;
@@ -49,7 +52,7 @@ struct BBParams {
   void* out;
   unsigned long long* combine;  // [O] split-K accumulators, zero between launches
   unsigned* status;
-  int O, K, G, nRU;
+  int O, K, G, nKB, nRU;
   int act_dtype, interleaved, global_mode, n_sal;
   int slots, ctas_per_kb;
 };
@@ -62,8 +65,11 @@ __device__ __forceinline__ uint32_t compact_even(uint32_t word) {
   return (word | (word >> 4)) & 0xffu;
 }
 
-template <bool INTERLEAVED, bool GLOBAL>
+template <bool INTERLEAVED, bool GLOBAL, int GPB>
 __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const BBParams p) {
+  constexpr int kBlockGroups = GPB;
+  constexpr int kUnitBytes = GPB * kGroupBytes;  // staged per unit
+  constexpr int kLutBytes = GPB * kGroupLutBytes, kSparseLutBytes = GPB * kGroupSparseBytes;
   extern __shared__ __align__(1024) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int S = p.slots;
@@ -74,7 +80,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   const uint32_t stage_u32 = smem_u32(stage_base);
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int nV = p.G * p.ctas_per_kb;
+  const int nV = p.nKB * p.ctas_per_kb;
   if ((int)blockIdx.x >= nV) return;
 
   if (lane == 0)
@@ -82,23 +88,30 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   mbar_init_fence();
   __syncwarp();
 
-  auto share = [&](int v, int& g, int& first, int& count) {
-    g = v / p.ctas_per_kb;
-    const int slice = v - g * p.ctas_per_kb;
+  auto share = [&](int v, int& kb, int& first, int& count) {
+    kb = v / p.ctas_per_kb;
+    const int slice = v - kb * p.ctas_per_kb;
     const int ua = (int)((long long)slice * p.nRU / p.ctas_per_kb);
     const int ub = (int)((long long)(slice + 1) * p.nRU / p.ctas_per_kb);
     const int n = ub - ua, q = n / kWarps, r = n - q * kWarps;
     first = ua + warp * q + min(warp, r);
     count = q + (warp < r ? 1 : 0);
   };
-  // rows past O in the last unit are never copied (the copy is clipped) and never stored
-  auto stage_units = [&](int g, int first, int n, int slot, int bar_index) {
+  // n units from `first` into slots slot.., one bulk copy per unit and group; rows past O in the
+  // last unit are never copied (the copy is clipped) and never stored
+  auto stage_units = [&](int kb, int first, int n, int slot, int bar_index) {
     if (lane == 0) {
-      const int rows = min(n * kUnitRows, p.O - first * kUnitRows);
+      const int ngroups = min(kBlockGroups, p.G - kBlockGroups * kb);
       const uint32_t bar = smem_u32(&bars[bar_index]);
-      mbar_expect_tx(bar, (uint32_t)(rows * 32));
-      bulk_g2s(stage_u32 + (uint32_t)(slot * kUnitBytes), p.codes + ((size_t)g * p.O + (size_t)first * kUnitRows) * 32,
-               (uint32_t)(rows * 32), bar);
+      int total = 0;
+      for (int u = 0; u < n; ++u) total += min(kUnitRows, p.O - (first + u) * kUnitRows) * 32 * ngroups;
+      mbar_expect_tx(bar, (uint32_t)total);
+      for (int u = 0; u < n; ++u) {
+        const int rows = min(kUnitRows, p.O - (first + u) * kUnitRows);
+        for (int gi = 0; gi < ngroups; ++gi)
+          bulk_g2s(stage_u32 + (uint32_t)((slot + u) * kUnitBytes + gi * kGroupBytes),
+                   p.codes + ((size_t)(kBlockGroups * kb + gi) * p.O + (size_t)(first + u) * kUnitRows) * 32, (uint32_t)(rows * 32), bar);
+      }
     }
   };
 
@@ -118,13 +131,13 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   };
   uint32_t chunk_parity = 0, slot_parity = 0;
   bool dead = false, first_pass = true;
-  int g, my_first, my_count;
-  share((int)blockIdx.x, g, my_first, my_count);
-  if (my_count > 0) stage_units(g, my_first, min(S, my_count), 0, kMaxSlots);
+  int kb, my_first, my_count;
+  share((int)blockIdx.x, kb, my_first, my_count);
+  if (my_count > 0) stage_units(kb, my_first, min(S, my_count), 0, kMaxSlots);
 
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // Split over the groups: every contribution is ONE 64-bit atomic add carrying the scaled
+  // Split over the K blocks: every contribution is ONE 64-bit atomic add carrying the scaled
   // partial sum in fixed point (steps of 2^-26, bits 16..63), an arrival count (bits 0..7) and a
   // count of partials that are not finite or too large for the format (bits 8..15).  Integer
   // adds commute, so the result is independent of arrival order; whoever reads back the last
@@ -134,7 +147,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   int pend_row = -1;
   auto settle = [&]() {
     if (pend_row < 0) return;
-    if (((unsigned)pend_old & 255u) == (unsigned)(p.G - 1)) {
+    if (((unsigned)pend_old & 255u) == (unsigned)(p.nKB - 1)) {
       const unsigned long long total = pend_old + pend_add;
       float value = __ll2float_rn((long long)total >> 16) * 1.4901161193847656e-08f;  // 2^-26
       if ((total >> 8) & 255ull) value = __int_as_float(0x7fc00000);
@@ -147,17 +160,20 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   for (int v = (int)blockIdx.x; v < nV; v += (int)gridDim.x) {
     if (!first_pass) {
       __syncthreads();  // everyone has finished reading the previous tables
-      share(v, g, my_first, my_count);
-      if (!dead && my_count > 0) stage_units(g, my_first, min(S, my_count), 0, kMaxSlots);
+      share(v, kb, my_first, my_count);
+      if (!dead && my_count > 0) stage_units(kb, my_first, min(S, my_count), 0, kMaxSlots);
     }
     first_pass = false;
+    const int ngroups = min(kBlockGroups, p.G - kBlockGroups * kb);
 
-    float sal_x = 0.f;
-    // ---- 32 signed tables: lane = table (base = lane/16, chunk = lane%16), warp = 32 entries ----
-    {
+    float sal_x[kBlockGroups] = {};
+    // ---- 32 signed tables per group: lane = table (base = lane/16, chunk = lane%16), warp = 32 entries ----
+#pragma unroll
+    for (int gi = 0; gi < kBlockGroups; ++gi) {
+      const int g = kBlockGroups * kb + gi;
       const int base = lane >> 4, chunk = lane & 15;
       float v8[8];
-      {
+      if (gi < ngroups) {
         // eight activations (and, with matrix-wide scales, eight fp16 column scales) in one 16-byte load each
         const int k0 = g * 128 + chunk * 8;
         const uint4 xr = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + k0);
@@ -174,13 +190,16 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
                                   : p.cols[(size_t)(k0 + j) * 2 + base];
           v8[j] = __fmul_rn(xv, cv);
         }
+      } else {  // an odd number of groups: the second half of the last K block is empty
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v8[j] = 0.f;
       }
       // the salient input this group's contribution carries (matrix-wide scales): fetched once per group
-      if (GLOBAL && g < p.n_sal) sal_x = load_act(p.x, p.act_dtype, p.sal_idx[g]);
+      if (GLOBAL && gi < ngroups && g < p.n_sal) sal_x[gi] = load_act(p.x, p.act_dtype, p.sal_idx[g]);
       // entry(p) = sum_b (bit b of p ? +v_b : -v_b) = low-nibble part + high-nibble part.  Warp w
       // owns the entries whose low nibble is 2w or 2w+1; the sixteen high-nibble parts come from
       // a tree (one add each), so an entry costs one add and one store.
-      unsigned char* const column = lut + lane * 4;
+      unsigned char* const column = lut + gi * kGroupLutBytes + lane * 4;
       float hi[16];
       hi[0] = ((-v8[4] - v8[5]) - v8[6]) - v8[7];
 #pragma unroll
@@ -197,19 +216,19 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
 #pragma unroll
         for (int h = 0; h < 16; ++h) *reinterpret_cast<float*>(column + (size_t)(h * 16 + q) * 128) = lo + hi[h];
       }
-      if (!GLOBAL) {
+      if (!GLOBAL && gi < ngroups) {
         // two refinement tables over the group's 8 selected columns; warp w fills entries 32w..32w+31
         const int pp = warp * 32 + lane;
 #pragma unroll
         for (int base2 = 0; base2 < 2; ++base2) {
-          float s = 0.f;
+          float sum = 0.f;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int idx = p.indices[g * 8 + j];
             const float sv = __fmul_rn(load_act(p.x, p.act_dtype, g * 128 + idx), p.scols[(size_t)(g * 8 + j) * 2 + base2]);
-            s += ((pp >> j) & 1) ? sv : -sv;
+            sum += ((pp >> j) & 1) ? sv : -sv;
           }
-          sparse_lut[base2 * 256 + pp] = s;
+          sparse_lut[gi * 512 + base2 * 256 + pp] = sum;
         }
       }
     }
@@ -221,19 +240,26 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
       const int ru = my_first + i;
       const int row = ru * kUnitRows + lane;
       const bool live = row < p.O;
-      float2 rs = make_float2(0.f, 0.f), srs = make_float2(0.f, 0.f);
-      unsigned sp = 0;
+      float2 rs[kBlockGroups], srs[kBlockGroups];
+      unsigned sp[kBlockGroups] = {};
       uint32_t g0bits = 0, g1bits = 0;
-      uint32_t sal_bits = 0;
-      if (GLOBAL && live && g < p.n_sal) asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sal_bits) : "l"(p.sal + (size_t)row * p.n_sal + g));
+      uint32_t sal_bits[kBlockGroups] = {};
+#pragma unroll
+      for (int gi = 0; gi < kBlockGroups; ++gi) {
+        const int g = kBlockGroups * kb + gi;
+        rs[gi] = make_float2(0.f, 0.f);
+        srs[gi] = make_float2(0.f, 0.f);
+        if (GLOBAL && live && gi < ngroups && g < p.n_sal)
+          asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(sal_bits[gi]) : "l"(p.sal + (size_t)row * p.n_sal + g));
+        if (!GLOBAL && live && gi < ngroups) {
+          rs[gi] = *reinterpret_cast<const float2*>(p.rows + ((size_t)g * p.O + row) * 2);
+          srs[gi] = *reinterpret_cast<const float2*>(p.srows + ((size_t)g * p.O + row) * 2);
+          sp[gi] = *reinterpret_cast<const unsigned short*>(p.sparse + ((size_t)g * p.O + row) * 2);
+        }
+      }
       if (GLOBAL && live) {
         asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(g0bits) : "l"(p.grow + row));
         asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(g1bits) : "l"(p.grow + (size_t)p.O + row));
-      }
-      if (!GLOBAL && live) {
-        rs = *reinterpret_cast<const float2*>(p.rows + ((size_t)g * p.O + row) * 2);
-        srs = *reinterpret_cast<const float2*>(p.srows + ((size_t)g * p.O + row) * 2);
-        sp = *reinterpret_cast<const unsigned short*>(p.sparse + ((size_t)g * p.O + row) * 2);
       }
 
       bool ok = false;
@@ -250,79 +276,94 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
       }
       if (i >= chunk_units) slot_parity ^= 1u << slot;
 
-      float d0 = 0.f, d1 = 0.f;
+      float d0[kBlockGroups] = {}, d1[kBlockGroups] = {};
       if (!dead) {
-        const unsigned char* const buf = stage_base + slot * kUnitBytes + lane * 32;
-        const uint32_t buf_u32 = stage_u32 + (uint32_t)(slot * kUnitBytes + lane * 32);
-        if (!INTERLEAVED) {
-          // row = [base 0: 16 bytes][base 1: 16 bytes]; steps with jh = 0 serve base rh
-          float acc[2] = {0.f, 0.f};
 #pragma unroll
-          for (int jh = 0; jh < 2; ++jh) {
-            const int h = jh ^ rh;
+        for (int gi = 0; gi < kBlockGroups; ++gi) {
+          if (gi >= ngroups) break;  // nothing was staged for an empty second group
+          const unsigned char* const buf = stage_base + slot * kUnitBytes + gi * kGroupBytes + lane * 32;
+          const uint32_t buf_u32 = stage_u32 + (uint32_t)(slot * kUnitBytes + gi * kGroupBytes + lane * 32);
+          const uint32_t group_lut = lut_u32 + (uint32_t)(gi * kGroupLutBytes);
+          if (!INTERLEAVED) {
+            // row = [base 0: 16 bytes][base 1: 16 bytes]; steps with jh = 0 serve base rh
+            float acc[2] = {0.f, 0.f};
 #pragma unroll
-            for (int jw = 0; jw < 4; ++jw) {
-              const int ws = (jw + rw) & 3;
-              uint32_t w;
-              asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(buf_u32 + (uint32_t)(h * 16 + ws * 4)));
+            for (int jh = 0; jh < 2; ++jh) {
+              const int h = jh ^ rh;
 #pragma unroll
-              for (int b = 0; b < 4; ++b) acc[jh] += lookup(w, b, lut_u32 + (uint32_t)(64 * h + 16 * ws + 4 * ((b + rb) & 3)));
-            }
-          }
-          d0 = rh ? acc[1] : acc[0];
-          d1 = rh ? acc[0] : acc[1];
-        } else {
-          // row = 16 little-endian 16-bit words, word c holds chunk c of both bases, bits
-          // interleaved.  A 32-bit read gives chunks 2w and 2w+1; sub-step b picks
-          // (chunk half, base) = ((b+rb)&1, (b+rb)>>1 & 1).
-          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+              for (int jw = 0; jw < 4; ++jw) {
+                const int ws = (jw + rw) & 3;
+                uint32_t w;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(buf_u32 + (uint32_t)(h * 16 + ws * 4)));
 #pragma unroll
-          for (int jh = 0; jh < 2; ++jh) {
-#pragma unroll
-            for (int jw = 0; jw < 4; ++jw) {
-              const int w8 = 4 * (jh ^ rh) + ((jw + rw) & 3);
-              const uint32_t w = *reinterpret_cast<const uint32_t*>(buf + w8 * 4);
-#pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                const int combo = (b + rb) & 3, half = combo & 1, base = combo >> 1;
-                const uint32_t entry = compact_even((w >> (16 * half)) >> base);
-                acc[b] += *reinterpret_cast<const float*>(lut + entry * 128 + 4 * (16 * base + 2 * w8 + half));
+                for (int b = 0; b < 4; ++b) acc[jh] += lookup(w, b, group_lut + (uint32_t)(64 * h + 16 * ws + 4 * ((b + rb) & 3)));
               }
             }
-          }
+            d0[gi] = rh ? acc[1] : acc[0];
+            d1[gi] = rh ? acc[0] : acc[1];
+          } else {
+            // row = 16 little-endian 16-bit words, word c holds chunk c of both bases, bits
+            // interleaved.  A 32-bit read gives chunks 2w and 2w+1; sub-step b picks
+            // (chunk half, base) = ((b+rb)&1, (b+rb)>>1 & 1).
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            if ((((b + rb) & 3) >> 1) == 0) d0 += acc[b]; else d1 += acc[b];
+            for (int jh = 0; jh < 2; ++jh) {
+#pragma unroll
+              for (int jw = 0; jw < 4; ++jw) {
+                const int w8 = 4 * (jh ^ rh) + ((jw + rw) & 3);
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(buf + w8 * 4);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const int combo = (b + rb) & 3, half = combo & 1, base = combo >> 1;
+                  const uint32_t entry = compact_even((w >> (16 * half)) >> base);
+                  acc[b] += *reinterpret_cast<const float*>(lut + gi * kGroupLutBytes + entry * 128 + 4 * (16 * base + 2 * w8 + half));
+                }
+              }
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              if ((((b + rb) & 3) >> 1) == 0) d0[gi] += acc[b]; else d1[gi] += acc[b];
+            }
           }
         }
       }
 
       __syncwarp();
-      if (!dead && i + S < my_count) stage_units(g, my_first + i + S, 1, slot, slot);
+      if (!dead && i + S < my_count) stage_units(kb, my_first + i + S, 1, slot, slot);
 
       settle();  // the previous unit's answer has long arrived
       if (!dead && live) {
-        float value;
+        float value = 0.f;
         if (GLOBAL) {
           asm volatile("" : "+r"(g0bits), "+r"(g1bits));  // first use: after the lookups
-          value = __fmaf_rn(__half2float(__ushort_as_half((unsigned short)g0bits)), d0, 0.f);
-          value = __fmaf_rn(__half2float(__ushort_as_half((unsigned short)g1bits)), d1, value);
-          // the dense residual columns are dealt round-robin over the groups' contributions
-          if (g < p.n_sal) {
-            asm volatile("" : "+r"(sal_bits));
-            value = __fmaf_rn(__uint_as_float(sal_bits << 16), sal_x, value);
+          const float r0 = __half2float(__ushort_as_half((unsigned short)g0bits)), r1 = __half2float(__ushort_as_half((unsigned short)g1bits));
+#pragma unroll
+          for (int gi = 0; gi < kBlockGroups; ++gi) {
+            if (gi >= ngroups) break;
+            const int g = kBlockGroups * kb + gi;
+            value = __fmaf_rn(r0, d0[gi], value);
+            value = __fmaf_rn(r1, d1[gi], value);
+            // the dense residual columns are dealt round-robin over the groups' contributions
+            if (g < p.n_sal) {
+              asm volatile("" : "+r"(sal_bits[gi]));
+              value = __fmaf_rn(__uint_as_float(sal_bits[gi] << 16), sal_x[gi], value);
+            }
+            for (int sidx = g + p.G; sidx < p.n_sal; sidx += p.G)  // more salient columns than groups: rare
+              value = __fmaf_rn(__bfloat162float(p.sal[(size_t)row * p.n_sal + sidx]), load_act(p.x, p.act_dtype, p.sal_idx[sidx]), value);
           }
-          for (int sidx = g + p.G; sidx < p.n_sal; sidx += p.G)  // more salient columns than groups: rare
-            value = __fmaf_rn(__bfloat162float(p.sal[(size_t)row * p.n_sal + sidx]), load_act(p.x, p.act_dtype, p.sal_idx[sidx]), value);
         } else {
-          const uint32_t p0 = INTERLEAVED ? compact_even(sp) : (sp & 0xffu);
-          const uint32_t p1 = INTERLEAVED ? compact_even(sp >> 1) : (sp >> 8);
-          value = __fmaf_rn(rs.x, d0, 0.f);
-          value = __fmaf_rn(rs.y, d1, value);
-          value = __fmaf_rn(srs.x, sparse_lut[p0], value);
-          value = __fmaf_rn(srs.y, sparse_lut[256 + p1], value);
+#pragma unroll
+          for (int gi = 0; gi < kBlockGroups; ++gi) {
+            if (gi >= ngroups) break;
+            const uint32_t p0 = INTERLEAVED ? compact_even(sp[gi]) : (sp[gi] & 0xffu);
+            const uint32_t p1 = INTERLEAVED ? compact_even(sp[gi] >> 1) : (sp[gi] >> 8);
+            value = __fmaf_rn(rs[gi].x, d0[gi], value);
+            value = __fmaf_rn(rs[gi].y, d1[gi], value);
+            value = __fmaf_rn(srs[gi].x, sparse_lut[gi * 512 + p0], value);
+            value = __fmaf_rn(srs[gi].y, sparse_lut[gi * 512 + 256 + p1], value);
+          }
         }
-        if (p.G == 1) {
+        if (p.nKB == 1) {
           store_act(p.out, p.act_dtype, row, value);
         } else {
           const bool fits = fabsf(value) < 8192.f;  // 255 of them stay inside 48 bits
@@ -340,7 +381,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
 
 constexpr size_t kCombineOffset = 16384;  // after the status block: one 64-bit word per output row
 
-template <bool INTERLEAVED, bool GLOBAL>
+template <bool INTERLEAVED, bool GLOBAL, int GPB>
 int launch(const BBParams& p, int grid, size_t smem, int max_smem, bool pdl, cudaStream_t stream) {
   static std::mutex lock;
   static bool ready[64] = {};
@@ -349,7 +390,7 @@ int launch(const BBParams& p, int grid, size_t smem, int max_smem, bool pdl, cud
   {
     std::lock_guard<std::mutex> guard(lock);
     if (!ready[device]) {
-      cudaError_t err = cudaFuncSetAttribute(bb_gemv_kernel<INTERLEAVED, GLOBAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+      cudaError_t err = cudaFuncSetAttribute(bb_gemv_kernel<INTERLEAVED, GLOBAL, GPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
       if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(bb_gemv_kernel)");
       ready[device] = true;
     }
@@ -364,7 +405,7 @@ int launch(const BBParams& p, int grid, size_t smem, int max_smem, bool pdl, cud
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = pdl && pdl_allowed() ? 1 : 0;
-  cudaError_t err = cudaLaunchKernelEx(&config, bb_gemv_kernel<INTERLEAVED, GLOBAL>, p);
+  cudaError_t err = cudaLaunchKernelEx(&config, bb_gemv_kernel<INTERLEAVED, GLOBAL, GPB>, p);
   if (err != cudaSuccess) return cuda_fail(err, "bb_gemv_kernel launch");
   return FB_OK;
 }
@@ -379,20 +420,30 @@ int run(BBParams& p, void* scratch, size_t scratch_bytes, unsigned flags, fb_str
   p.status = reinterpret_cast<unsigned*>(base);
   p.combine = reinterpret_cast<unsigned long long*>(base + kCombineOffset);
   p.nRU = (p.O + kUnitRows - 1) / kUnitRows;
-  int c = kCtasPerSm * info->sm_count / p.G;
+  // Two groups per K block halve the per-byte cost of a unit; with few row units the second table
+  // build on the critical path costs more than that saves.
+  const int gpb = p.nRU >= 128 && p.G >= 2 ? 2 : 1;
+  p.nKB = (p.G + gpb - 1) / gpb;
+  int c = kCtasPerSm * info->sm_count / p.nKB;
   if (c < 1) c = 1;
   if (c > p.nRU) c = p.nRU;
   p.ctas_per_kb = c;
-  const int nV = p.G * c;
+  const int nV = p.nKB * c;
   const int grid = nV < kCtasPerSm * info->sm_count ? nV : kCtasPerSm * info->sm_count;
   const int per_warp = ((p.nRU + c - 1) / c + kWarps - 1) / kWarps;
-  p.slots = per_warp < kMaxSlots ? (per_warp < 1 ? 1 : per_warp) : kMaxSlots;
-  const size_t smem = kLutBytes + kSparseLutBytes + (size_t)kWarps * p.slots * kUnitBytes + (size_t)kWarps * (kMaxSlots + 1) * 8;
+  const int max_slots = kMaxSlots / gpb;
+  p.slots = per_warp < max_slots ? (per_warp < 1 ? 1 : per_warp) : max_slots;
+  const size_t smem = (size_t)gpb * (kGroupLutBytes + kGroupSparseBytes) + (size_t)kWarps * p.slots * gpb * kGroupBytes + (size_t)kWarps * (kMaxSlots + 1) * 8;
   const bool pdl = (flags & FB_W3_NO_PDL) == 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (p.global_mode) return launch<false, true>(p, grid, smem, info->max_smem_optin, pdl, s);
-  if (p.interleaved) return launch<true, false>(p, grid, smem, info->max_smem_optin, pdl, s);
-  return launch<false, false>(p, grid, smem, info->max_smem_optin, pdl, s);
+  if (gpb == 2) {
+    if (p.global_mode) return launch<false, true, 2>(p, grid, smem, info->max_smem_optin, pdl, s);
+    if (p.interleaved) return launch<true, false, 2>(p, grid, smem, info->max_smem_optin, pdl, s);
+    return launch<false, false, 2>(p, grid, smem, info->max_smem_optin, pdl, s);
+  }
+  if (p.global_mode) return launch<false, true, 1>(p, grid, smem, info->max_smem_optin, pdl, s);
+  if (p.interleaved) return launch<true, false, 1>(p, grid, smem, info->max_smem_optin, pdl, s);
+  return launch<false, false, 1>(p, grid, smem, info->max_smem_optin, pdl, s);
 }
 
 int check_common(const char* who, const void* x, int act_dtype, const uint8_t* codes, void* out, int O, int K) {
