@@ -56,8 +56,11 @@ using namespace fb;
 constexpr int kUnitRows = 32;
 constexpr int kPlaneTile = kUnitRows * 16;      // 512 B: one plane of one group for a unit
 constexpr int kUnitBytes = 2 * 3 * kPlaneTile;  // 3072 B of planes staged per unit
-constexpr int kWarps = 8;
-constexpr int kCtasPerSm = 2;
+// CTA shape by activation rows: with the tables of one or two rows (32 / 64 KB) two CTAs of eight
+// warps share an SM, so that one CTA's build and tail overlap the other's lookups; the 128 KB of
+// tables for three or four rows leave room for one CTA, which then runs sixteen warps.
+constexpr int warps_for(int m) { return m <= 2 ? 8 : 16; }
+constexpr int ctas_per_sm_for(int m) { return m <= 2 ? 2 : 1; }
 constexpr int kMaxM = 4;
 constexpr int kMaxSplits = 16;  // partial sums per output (one arrival count of 6 bits, 52-bit fixed-point sum)
 constexpr int kMaxMatrices = 4;
@@ -109,16 +112,19 @@ struct W3Params {
 // Shared-memory geometry.  Entry p of table t for activation row m lives at byte
 //   p * kStride + m * 128 + t * 4,   kStride = 128 * (M rounded up to a power of two),
 // so with M = 1 the 32 tables of a K block take 32 KB and the bank of a lookup is the table
-// number.  The ring holds three staged units per warp, two when the tables take 128 KB.
+// number.  The ring holds three staged units per warp with M = 1, two otherwise (M = 2 then still
+// fits two CTAs per SM).
 template <int M>
 struct Geom {
+  static constexpr int kWarps = warps_for(M);
+  static constexpr int kCtasPerSm = ctas_per_sm_for(M);
   static constexpr int kStrideLog = 7 + (M == 1 ? 0 : (M == 2 ? 1 : 2));
   static constexpr int kStride = 1 << kStrideLog;
   static constexpr int kLutBytes = 256 << kStrideLog;
-  static constexpr int kStages = M <= 2 ? 3 : 2;
-  // a staged unit: its planes, then (M <= 2; with 128 KB of tables there is no room) its scales at
-  // +3072 (2 groups x 64 B) and its zero points at +3200 (2 groups x 32 B)
-  static constexpr bool kStageAux = M <= 2;
+  static constexpr int kStages = M == 1 ? 3 : 2;
+  // a staged unit: its planes, then (M = 1 only: with larger tables two CTAs per SM leave no room)
+  // its scales at +3072 (2 groups x 64 B) and its zero points at +3200 (2 groups x 32 B)
+  static constexpr bool kStageAux = M == 1;
   static constexpr int kSlotBytes = kUnitBytes + (kStageAux ? 256 : 0);
   static constexpr int kRingOffset = kLutBytes;
   static constexpr int kBarOffset = kRingOffset + kWarps * kStages * kSlotBytes;
@@ -203,10 +209,10 @@ __device__ __forceinline__ void emit_combined(const W3Params& p, int m, int ru, 
 }
 
 template <int M, bool CORRECT>
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const __grid_constant__ W3Params p) {
+__global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_gemv_kernel(const __grid_constant__ W3Params p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   using G_ = Geom<M>;
-  constexpr int kStages = G_::kStages;
+  constexpr int kStages = G_::kStages, kWarps = G_::kWarps;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* const lut = smem;
   // Every warp owns a private ring of kStages staged units, [stage][group half * 3 + plane][32 rows
@@ -320,7 +326,7 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   // that follow the wait.
   if (pf_left > 0) issue_next();
 
-  // Without room in the ring (M > 2) the scales and zero points of a task come straight from global
+  // Without room in the ring (M > 1) the scales and zero points of a task come straight from global
   // memory (one coalesced run per group), requested ONE TASK AHEAD of their use so that HBM latency
   // never sits between a unit's lookups and its result.  Half jh of a lane's walk covers group
   // 2*kb + (jh ^ rh).
@@ -405,8 +411,8 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) w3_gemv_kernel(const 
   }
   for (int t = 1; t < kStages && pf_left > 0; ++t) issue_next();  // the rest of the ring, behind the activation loads
 
-  // ---- build the 32 tables of K block kb_: lane = table; warp w owns the entries whose low
-  // nibble is 2w or 2w + 1, so that the walk over the high nibble unrolls with constant offsets.  sx[m][jh]: the sum of the activations of the group this lane walks in half jh. ----
+  // ---- build the 32 tables of K block kb_: lane = table; warp w owns the entries of
+  // 16 / kWarps low nibbles (2w and 2w + 1 with eight warps), so that the walk over the high nibble unrolls with constant offsets.  sx[m][jh]: the sum of the activations of the group this lane walks in half jh. ----
   auto build = [&](int kb_, float (&sx)[M][2]) {
     const int g = 2 * kb_ + (lane >> 4);
     const int kbase = g * 128 + (lane & 15) * 8;
@@ -704,14 +710,14 @@ size_t smem_bytes(int m) {
   }
 }
 
-// One CTA per SM.  At most kMaxSplits partial sums per output: beyond 16 K blocks one CTA walks
+// ctas_per_sm_for(m) CTAs per SM.  At most kMaxSplits partial sums per output: beyond 16 K blocks one CTA walks
 // several K blocks of its rows in turn.  The SMs are dealt over the super-blocks; the CTAs of a
 // super-block split its row units.
 Plan make_plan(int m, int nKB, int nRU, const DeviceInfo& info) {
   Plan plan;
   plan.S = (nKB + kMaxSplits - 1) / kMaxSplits;
   plan.nSB = (nKB + plan.S - 1) / plan.S;
-  int c = kCtasPerSm * info.sm_count / plan.nSB;
+  int c = ctas_per_sm_for(m) * info.sm_count / plan.nSB;
   if (c < 1) c = 1;
   if (c > nRU) c = nRU;
   plan.slices = c;
@@ -738,7 +744,7 @@ int launch(const W3Params& p, const Plan& plan, bool pdl, cudaStream_t stream) {
   }
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(plan.slices, plan.nSB);
-  config.blockDim = dim3(kWarps * 32);
+  config.blockDim = dim3(Geom<M>::kWarps * 32);
   config.dynamicSmemBytes = plan.smem;
   config.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -835,7 +841,7 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
       return fail(FB_EALIAS, "fb_w3_gemv: out overlaps an input");
     if (scratch && overlaps(scratch, scratch_bytes, in.out, out_bytes)) return fail(FB_EALIAS, "fb_w3_gemv: scratch overlaps out");
     if (!plane_tensor_map(in.planes, O, G, 1, 6, &p.plane_maps[j])) return FB_ECUDA;
-    if (m <= 2) {  // the kernels for M <= 2 stage scales and zero points with the planes
+    if (m == 1) {  // the M = 1 kernel stages scales and zero points with the planes
       if (!group_row_tensor_map(in.scales, 2, O, G, &p.scale_maps[j])) return FB_ECUDA;
       if (in.zeros && !group_row_tensor_map(in.zeros, 1, O, G, &p.zero_maps[j])) return FB_ECUDA;
       if (!in.zeros) p.zero_maps[j] = p.scale_maps[j];
