@@ -259,6 +259,14 @@ int fb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void
  * token; every CTA norms and rotates the q head it serves (and the new k) itself, uses the new
  * token's k / v directly and one CTA per k/v head writes them into cache row `position`.
  * Attends over positions 0..position.  Same results, bit for bit, as the two calls.
+ * Ordering: the cache rows of positions < `position` are read BEFORE the kernel waits for the
+ * launch ahead of it in the stream, so they must be complete when that launch begins.  That holds
+ * when they were written by ordinary (not programmatically dependent) work, or by an earlier
+ * fb_attn_decode_fused with at least one fb_attn_decode_fused or fb_lm_head_argmax launch, or any
+ * ordinary launch, between it and this call: those kernels release their dependents only after
+ * their own wait.  A decode loop (one such call per layer and step, the LM head between steps)
+ * satisfies this by construction; two calls on the same cache directly behind each other, or with
+ * only fb_w3_gemv launches between them, do not.
  */
 int fb_attn_decode_fused(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
                          const void* cosv, const void* sinv, void* k_cache, void* v_cache, void* out, int q_heads,

@@ -122,8 +122,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
                                                                       unsigned* __restrict__ tickets, int q_heads, int kv_heads,
                                                                       int length, int max_positions, float scale, int dtype,
                                                                       const NewToken nt) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int D = 128;
   const int head = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -152,7 +150,17 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
       }
     }
   };
-  fetch(p0 + warp * kAttnBatch);
+  // FUSED: the cache rows of EARLIER positions are requested before the wait on the preceding
+  // launch, so that their HBM round trip overlaps that launch's tail.  This is ordered because
+  // this kernel (like the LM-head kernel) releases its own dependents only after its wait: when a
+  // launch that follows one of them starts, everything before that one has completed, so the rows
+  // written by the attention launches of earlier steps are in place as soon as one such launch
+  // (or any launch without programmatic dependency) lies between the writer and this kernel.
+  // The unfused form reads the newest row, written by the launch just before it, and must wait first.
+  if (FUSED) fetch(p0 + warp * kAttnBatch);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!FUSED) fetch(p0 + warp * kAttnBatch);
   float qv[4];
   if (FUSED) {
     if (warp == 0) norm_rope_head(nt.q + (size_t)head * D, nt.q_weight, nt.cosv, nt.sinv, nt.eps, dtype, lane, sm_new[0]);
@@ -192,19 +200,28 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
       for (int j = 0; j < kAttnBatch; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], d);
     }
+    // Online softmax a batch at a time: the batch's maximum first, then every exponential and
+    // product independently (no chain through the running maximum from position to position).
+    float batch_max = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kAttnBatch; ++j)
+      if (base + j < p1) batch_max = fmaxf(batch_max, s[j]);
+    const float m_new = fmaxf(m, batch_max);
+    const float correction = __expf(m - m_new);
+    float psum = 0.f, pv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < kAttnBatch; ++j) {
-      if (base + j < p1) {
-        const float m_new = fmaxf(m, s[j]);
-        const float correction = __expf(m - m_new), pj = __expf(s[j] - m_new);
-        float vf[4];
-        unpack4(vr[j], dtype, vf);
+      const float pj = base + j < p1 ? __expf(s[j] - m_new) : 0.f;
+      float vf[4];
+      unpack4(vr[j], dtype, vf);
+      psum += pj;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[i] = acc[i] * correction + pj * vf[i];
-        l = l * correction + pj;
-        m = m_new;
-      }
+      for (int i = 0; i < 4; ++i) pv[i] += pj * vf[i];
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = acc[i] * correction + pv[i];
+    l = l * correction + psum;
+    m = m_new;
   }
   __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps], sm_acc[kAttnWarps][D];
   if (lane == 0) {

@@ -68,7 +68,6 @@ __global__ void __launch_bounds__(kHeadThreads, kHeadCtasPerSm) lm_head_kernel(c
   __shared__ int is_last;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int dtype = BF16 ? FB_BF16 : FB_F16;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int warps_total = gridDim.x * (kHeadThreads / 32);
   int row = blockIdx.x * (kHeadThreads / 32) + warp;
@@ -83,6 +82,10 @@ __global__ void __launch_bounds__(kHeadThreads, kHeadCtasPerSm) lm_head_kernel(c
     if (row < p.V && k0 < p.K) ahead[u] = __ldcs(reinterpret_cast<const uint4*>(p.weight + (size_t)row * p.K + k0));
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Dependents are released only after the wait: a launch that follows this one then starts with
+  // everything before this one complete (the decode attention relies on that for its early reads
+  // of the cache); nothing is lost, this kernel fills every SM until it ends.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- stage x (optionally RMS-normed, with fb_rmsnorm's summation order) ----
   float inv = 1.f;

@@ -256,13 +256,15 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ one decode step
     @torch.inference_mode()
-    def step(self, token: torch.Tensor, position: int, next_forced: torch.Tensor | None = None, embed_next: bool = False) -> None:
+    def step(self, token: torch.Tensor, position: int, next_forced: torch.Tensor | None = None, embed_next: bool = False,
+             choice_out: torch.Tensor | None = None) -> None:
         """Decode one token (``token``: device int64 ``[1]``) at ``position``; leaves the greedy choice in
         ``self.next_token`` (and the logits in ``self.logits`` while ``keep_logits``).  No allocation, no host sync.
 
         ``embed_next``: the LM-head launch also writes the embedding row of the next token (``next_forced``,
         a device int64 ``[1]``, or the greedy choice) into the hidden-state buffer, and the next ``step`` then
-        skips its gather launch."""
+        skips its gather launch.  ``choice_out`` (device int64 ``[1]``) receives the greedy choice instead of
+        ``self.next_token``."""
         s, nat = self.shape, _native
         w3 = self.arm == "w3"
         f16 = torch.float16
@@ -338,7 +340,7 @@ class DecodeEngine:
             launches += (5 if fuse else 8) + (0 if self.fuse_attention else 1) + (2 if self.tp_size > 1 else 0)
         # final RMSNorm + LM head + argmax (+ the next token's embedding row, written over the hidden
         # state once every CTA has staged it) in one launch
-        nat.lm_head_argmax(self.h, self.final_norm, s.eps, self.lm_head, self.next_token, logits=self.logits if self.keep_logits else None,
+        nat.lm_head_argmax(self.h, self.final_norm, s.eps, self.lm_head, self.next_token if choice_out is None else choice_out, logits=self.logits if self.keep_logits else None,
                            forced_next=next_forced if embed_next else None, embedding=self.embedding if embed_next else None,
                            next_hidden=self.h if embed_next else None, scratch=self.head_scratch)
         self._h_is_embedded = embed_next
@@ -403,8 +405,9 @@ class DecodeEngine:
             for i in range(steps):
                 last = i + 1 == steps
                 following = None if forced_dev is None or last else forced_dev[i + 1:i + 2]
-                self.step(self.token_in if forced_dev is None else forced_dev[0:1], start + i, next_forced=following, embed_next=not last)
-                predictions[i:i + 1].copy_(self.next_token)
+                # the LM-head launch writes its choice straight into the prediction list: no copy node in the graph
+                self.step(self.token_in if forced_dev is None else forced_dev[0:1], start + i, next_forced=following, embed_next=not last,
+                          choice_out=predictions[i:i + 1])
             self._h_is_embedded = False
 
         with torch.cuda.stream(stream):
