@@ -259,8 +259,9 @@ int fb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void
  * token; every CTA norms and rotates the q head it serves (and the new k) itself, uses the new
  * token's k / v directly and one CTA per k/v head writes them into cache row `position`.
  * Attends over positions 0..position.  Same results, bit for bit, as the two calls.
- * Ordering: the cache rows of positions < `position` are read BEFORE the kernel waits for the
- * launch ahead of it in the stream, so they must be complete when that launch begins.  That holds
+ * Ordering: the norm weights, the rotary row and the cache rows of positions < `position` are read
+ * BEFORE the kernel waits for the launch ahead of it in the stream, so they must be complete when
+ * that launch begins (weights and rotary tables are constants of a decode).  For the cache rows that holds
  * when they were written by ordinary (not programmatically dependent) work, or by an earlier
  * fb_attn_decode_fused with at least one fb_attn_decode_fused or fb_lm_head_argmax launch, or any
  * ordinary launch, between it and this call: those kernels release their dependents only after

@@ -88,26 +88,46 @@ struct NewToken {
 };
 
 // Per-head RMSNorm + rotary embedding of one 128-wide head by one warp, result (in the 16-bit
-// dtype's bits) into shared memory; the arithmetic of qknorm_rope_cache_kernel.
-__device__ __forceinline__ void norm_rope_head(const unsigned short* src, const unsigned short* weight, const unsigned short* cosv,
-                                               const unsigned short* sinv, float eps, int dtype, int lane, unsigned short* dst) {
-  constexpr int dim = 128, half = 64;
-  float ss = 0.f;
-  for (int i = lane; i < dim; i += 32) {
-    const float x = bits_to_float(src[i], dtype);
-    ss += x * x;
+// dtype's bits) into shared memory; the arithmetic of qknorm_rope_cache_kernel.  A lane owns the
+// dims lane, lane + 32 and their partners + 64.  The constants (norm weight, rotary row) never
+// change during a decode and are loaded separately, ahead of the wait on the preceding launch.
+struct HeadConstants {
+  float w[4], c[4], s[4];  // dims lane, lane + 32, lane + 64, lane + 96
+};
+
+__device__ __forceinline__ HeadConstants load_head_constants(const unsigned short* weight, const unsigned short* cosv,
+                                                             const unsigned short* sinv, int dtype, int lane) {
+  HeadConstants k;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    k.w[j] = bits_to_float(weight[lane + 32 * j], dtype);
+    k.c[j] = bits_to_float(cosv[lane + 32 * j], dtype);
+    k.s[j] = bits_to_float(sinv[lane + 32 * j], dtype);
   }
+  return k;
+}
+
+__device__ __forceinline__ void norm_rope_head(const unsigned short* src, const HeadConstants& k, float eps, int dtype, int lane,
+                                               unsigned short* dst) {
+  constexpr int dim = 128;
+  float x[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) x[j] = bits_to_float(src[lane + 32 * j], dtype);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
 #pragma unroll
   for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
   const float inv = rsqrtf(ss / (float)dim + eps);
-  for (int i = lane; i < half; i += 32) {
-    const float lo = bits_to_float(weight[i], dtype) * round_to(bits_to_float(src[i], dtype) * inv, dtype);
-    const float hi = bits_to_float(weight[i + half], dtype) * round_to(bits_to_float(src[i + half], dtype) * inv, dtype);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float lo = k.w[j] * round_to(x[j] * inv, dtype);
+    const float hi = k.w[j + 2] * round_to(x[j + 2] * inv, dtype);
     const float nlo = round_to(lo, dtype), nhi = round_to(hi, dtype);
-    const float y0 = round_to(nlo * bits_to_float(cosv[i], dtype), dtype) + (-nhi) * bits_to_float(sinv[i], dtype);
-    const float y1 = round_to(nhi * bits_to_float(cosv[i + half], dtype), dtype) + nlo * bits_to_float(sinv[i + half], dtype);
-    dst[i] = to_bits(y0, dtype);
-    dst[i + half] = to_bits(y1, dtype);
+    const float y0 = round_to(nlo * k.c[j], dtype) + (-nhi) * k.s[j];
+    const float y1 = round_to(nhi * k.c[j + 2], dtype) + nlo * k.s[j + 2];
+    dst[lane + 32 * j] = to_bits(y0, dtype);
+    dst[lane + 32 * j + 64] = to_bits(y1, dtype);
   }
 }
 
@@ -157,14 +177,18 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
   // written by the attention launches of earlier steps are in place as soon as one such launch
   // (or any launch without programmatic dependency) lies between the writer and this kernel.
   // The unfused form reads the newest row, written by the launch just before it, and must wait first.
-  if (FUSED) fetch(p0 + warp * kAttnBatch);
+  HeadConstants hc = {};
+  if (FUSED) {
+    if (warp < 2) hc = load_head_constants(warp == 0 ? nt.q_weight : nt.k_weight, nt.cosv, nt.sinv, dtype, lane);  // constants of the decode
+    fetch(p0 + warp * kAttnBatch);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (!FUSED) fetch(p0 + warp * kAttnBatch);
   float qv[4];
   if (FUSED) {
-    if (warp == 0) norm_rope_head(nt.q + (size_t)head * D, nt.q_weight, nt.cosv, nt.sinv, nt.eps, dtype, lane, sm_new[0]);
-    if (warp == 1) norm_rope_head(nt.k + (size_t)kvh * D, nt.k_weight, nt.cosv, nt.sinv, nt.eps, dtype, lane, sm_new[1]);
+    if (warp == 0) norm_rope_head(nt.q + (size_t)head * D, hc, nt.eps, dtype, lane, sm_new[0]);
+    if (warp == 1) norm_rope_head(nt.k + (size_t)kvh * D, hc, nt.eps, dtype, lane, sm_new[1]);
     if (warp == 2) *reinterpret_cast<uint2*>(&sm_new[2][lane * 4]) = *reinterpret_cast<const uint2*>(nt.v + (size_t)kvh * D + lane * 4);
     __syncthreads();
     if (head % group == 0 && split == splits - 1 && warp < 2) {  // the cache row of the new token

@@ -367,35 +367,57 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
   // Everything below reads activations and writes scratch / outputs of this stream.
   pdl_wait_prior_grid();
 
-  // Raw 16-bit activations of one lane's table (8 values) and of the fused transform's operand;
-  // the next K block's are fetched while the current one is being computed.
+  // Raw 16-bit activations of one lane's table (8 values); the next K block's are fetched while
+  // the current one is being computed.
   const bool fast_x = M == 1 && !p.perm;
-  auto fetch_x = [&](int kb_, uint4& raw, uint4& op) {
+  auto fetch_x = [&](int kb_, uint4& raw) {
     const int g = 2 * kb_ + (lane >> 4);
     raw = make_uint4(0u, 0u, 0u, 0u);
-    op = raw;
-    if (g < p.G) {
-      const int kbase = g * 128 + (lane & 15) * 8;
-      raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + kbase);
-      if (p.prologue != 0) op = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.prologue_arg) + kbase);
+    if (g < p.G) raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + g * 128 + (lane & 15) * 8);
+  };
+  // With a fused input transform every thread owns ONE of the K block's 256 activations: it loads
+  // the raw value and the operand, transforms them once and shares the result through shared
+  // memory, instead of every warp transforming all 256 for itself.
+  const bool shared_x = fast_x && p.prologue != 0;
+  __shared__ __align__(16) float xs[M == 1 ? 256 : 4];
+  uint32_t el_raw = 0u, el_op = 0u;
+  auto fetch_el = [&](int kb_) {
+    const int e = kb_ * 256 + (int)threadIdx.x;
+    el_raw = el_op = 0u;
+    if (threadIdx.x < 256 && e < p.K) {
+      el_raw = reinterpret_cast<const unsigned short*>(p.x)[e];
+      el_op = reinterpret_cast<const unsigned short*>(p.prologue_arg)[e];
     }
   };
   // requested before the RMS reduction below, so that the two round trips overlap
-  uint4 raw_next = make_uint4(0u, 0u, 0u, 0u), op_next = raw_next;
-  if (fast_x) fetch_x(kb_begin, raw_next, op_next);
+  uint4 raw_next = make_uint4(0u, 0u, 0u, 0u);
+  if (shared_x)
+    fetch_el(kb_begin);
+  else if (fast_x)
+    fetch_x(kb_begin, raw_next);
 
   // Optional fused input transform.  For RMSNorm every CTA reduces the whole activation row
   // itself (K 16-bit values: a few KB out of L2), which costs far less than a separate launch.
   float inv_rms = 1.f;
   if (p.prologue == 1) {
     float ss = 0.f;
-    for (int i = threadIdx.x * 8; i < p.K; i += kWarps * 32 * 8) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + i);
-      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+    constexpr int kStep = kWarps * 32 * 8, kAhead = 4;  // four 16-byte loads of a thread in flight: one round trip for K <= 8192
+    for (int i0 = threadIdx.x * 8; i0 < p.K; i0 += kAhead * kStep) {
+      uint4 raws[kAhead];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float v = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
-        ss += v * v;
+      for (int u = 0; u < kAhead; ++u) {
+        const int i = i0 + u * kStep;
+        raws[u] = make_uint4(0u, 0u, 0u, 0u);  // zeros past the end add nothing to the sum
+        if (i < p.K) raws[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.x) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const uint32_t words[4] = {raws[u].x, raws[u].y, raws[u].z, raws[u].w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+          ss += v * v;
+        }
       }
     }
 #pragma unroll
@@ -420,21 +442,25 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float v8[8];
-      if (fast_x) {
-        const uint32_t words[4] = {raw_next.x, raw_next.y, raw_next.z, raw_next.w};
-        const uint32_t owords[4] = {op_next.x, op_next.y, op_next.z, op_next.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
-          if (p.prologue != 0) {
-            // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
-            // SwiGLU rounds silu(gate) before the product
-            const float other = bits_to_float((unsigned short)((owords[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
-            v8[j] = p.prologue == 1 ? round_to(other * round_to(v8[j] * inv_rms, p.act_dtype), p.act_dtype)
-                                    : round_to(round_to(v8[j] / (1.f + __expf(-v8[j])), p.act_dtype) * other, p.act_dtype);
-          }
+      if (shared_x) {
+        if (threadIdx.x < 256) {
+          // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
+          // SwiGLU rounds silu(gate) before the product
+          const float v = bits_to_float((unsigned short)el_raw, p.act_dtype), other = bits_to_float((unsigned short)el_op, p.act_dtype);
+          xs[M == 1 ? threadIdx.x : 0] = p.prologue == 1 ? round_to(other * round_to(v * inv_rms, p.act_dtype), p.act_dtype)
+                                                           : round_to(round_to(v / (1.f + __expf(-v)), p.act_dtype) * other, p.act_dtype);
         }
-        if (kb_ + 1 < kb_begin + nS) fetch_x(kb_ + 1, raw_next, op_next);
+        if (kb_ + 1 < kb_begin + nS) fetch_el(kb_ + 1);
+        __syncthreads();
+        const float4 lo = *reinterpret_cast<const float4*>(&xs[M == 1 ? (lane >> 4) * 128 + (lane & 15) * 8 : 0]);
+        const float4 hi4 = *reinterpret_cast<const float4*>(&xs[M == 1 ? (lane >> 4) * 128 + (lane & 15) * 8 + 4 : 0]);
+        v8[0] = lo.x, v8[1] = lo.y, v8[2] = lo.z, v8[3] = lo.w;
+        v8[4] = hi4.x, v8[5] = hi4.y, v8[6] = hi4.z, v8[7] = hi4.w;
+      } else if (fast_x) {
+        const uint32_t words[4] = {raw_next.x, raw_next.y, raw_next.z, raw_next.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v8[j] = bits_to_float((unsigned short)((words[j >> 1] >> (16 * (j & 1))) & 0xffffu), p.act_dtype);
+        if (kb_ + 1 < kb_begin + nS) fetch_x(kb_ + 1, raw_next);
       } else if (g < p.G) {
         if (p.perm) {
 #pragma unroll
