@@ -127,6 +127,18 @@ int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transform, const vo
                            void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream);
 
 /*
+ * The attention output as the fused input of the Linear that consumes it (o_proj): `partials` is
+ * what fb_attn_decode_partial left, per head and split (output[128], max, sum) as fp32 at float
+ * offset (16 * head + split) * 132; in_features = heads * 128.  The splits are merged while the
+ * tables are built, with the arithmetic of fb_attn_decode's own last step (the results equal
+ * fb_attn_decode_fused followed by fb_w3_gemv_multi bit for bit), which takes the cross-CTA merge
+ * of the attention launch and its barrier off the critical path.  1..8 splits.
+ */
+int fb_w3_gemv_attn_merge(const void* partials, int splits, int act_dtype, const fb_w3_matrix_t* matrices,
+                          int n_matrices, int scale_dtype, int in_features, void* scratch, size_t scratch_bytes,
+                          unsigned flags, fb_stream_t stream);
+
+/*
  * Tensor-parallel form of a row-split Linear (o_proj, down_proj): one matrix, M = 1, optional
  * fused input transform (0 = none) as in fb_w3_gemv_fused_input.  Instead of writing `out`
  * (ignored; may be any non-null pointer), the final fp32 value of output row o is stored,
@@ -273,6 +285,18 @@ int fb_attn_decode_fused(const void* q, const void* k, const void* v, const void
                          const void* cosv, const void* sinv, void* k_cache, void* v_cache, void* out, int q_heads,
                          int kv_heads, int head_dim, int position, int max_positions, float eps, float scale, int dtype,
                          void* scratch, size_t scratch_bytes, fb_stream_t stream);
+
+/*
+ * fb_attn_decode_fused without its last step: every CTA leaves the (output, max, sum) of its share
+ * of the positions in `partials` (fb_attn_decode_scratch_bytes(q_heads) bytes, 16-byte aligned; no
+ * need to zero it) for fb_w3_gemv_attn_merge; fb_attn_decode_splits(position + 1) is the number of
+ * splits per head it uses.  Same ordering rules as fb_attn_decode_fused.
+ */
+int fb_attn_decode_splits(int length);
+int fb_attn_decode_partial(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
+                           const void* cosv, const void* sinv, void* k_cache, void* v_cache, int q_heads, int kv_heads,
+                           int head_dim, int position, int max_positions, float eps, float scale, int dtype,
+                           void* partials, size_t partial_bytes, fb_stream_t stream);
 
 int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream);
 

@@ -101,6 +101,14 @@ def library() -> ctypes.CDLL:
         lib.fb_attn_decode_fused.restype = ctypes.c_int
         lib.fb_attn_decode_fused.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_float, ctypes.c_int,
                                                                                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        lib.fb_attn_decode_splits.restype = ctypes.c_int
+        lib.fb_attn_decode_splits.argtypes = [ctypes.c_int]
+        lib.fb_attn_decode_partial.restype = ctypes.c_int
+        lib.fb_attn_decode_partial.argtypes = [ctypes.c_void_p] * 9 + [ctypes.c_int] * 5 + [ctypes.c_float, ctypes.c_float, ctypes.c_int,
+                                                                                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        lib.fb_w3_gemv_attn_merge.restype = ctypes.c_int
+        lib.fb_w3_gemv_attn_merge.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(W3Matrix), ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint, ctypes.c_void_p]
         lib.fb_attn_decode_scratch_bytes.restype = ctypes.c_size_t
         lib.fb_attn_decode_scratch_bytes.argtypes = [ctypes.c_int]
         lib.fb_silu_mul.restype = ctypes.c_int
@@ -352,6 +360,31 @@ def attn_decode_fused(q, k, v, q_weight, k_weight, cos, sin, k_cache, v_cache, o
                                              ptr(v_cache), ptr(out), q.numel() // dim, k_cache.shape[-3], dim, int(position),
                                              k_cache.shape[-2], float(eps), float(scale), dtype_tag(q.dtype), ptr(scratch),
                                              scratch.numel(), stream_handle(q.device)))
+
+
+def attn_decode_partial(q, k, v, q_weight, k_weight, cos, sin, k_cache, v_cache, position: int, eps: float, scale: float,
+                        partials) -> int:
+    """``attn_decode_fused`` without its last step: every CTA leaves its share (output, max, sum) in ``partials``
+    (uint8, ``attn_scratch_bytes`` long) for ``w3_gemv_attn_merge``.  Returns the number of splits per head."""
+    dim = k_cache.shape[-1]
+    with torch.cuda.device(q.device):
+        check(library().fb_attn_decode_partial(ptr(q), ptr(k), ptr(v), ptr(q_weight), ptr(k_weight), ptr(cos), ptr(sin), ptr(k_cache),
+                                               ptr(v_cache), q.numel() // dim, k_cache.shape[-3], dim, int(position), k_cache.shape[-2],
+                                               float(eps), float(scale), dtype_tag(q.dtype), ptr(partials), partials.numel(),
+                                               stream_handle(q.device)))
+    return int(library().fb_attn_decode_splits(int(position) + 1))
+
+
+def w3_gemv_attn_merge(partials, splits: int, act_dtype, in_features: int, matrices, n_matrices, total_out, scale_dtype, *,
+                       scratch=None, decoded_bf16=False) -> None:
+    """``w3_gemv_multi`` for one activation row that is the attention output still in ``splits`` pieces per head
+    (``attn_decode_partial``); the pieces are merged while the tables are built."""
+    if scratch is None:
+        scratch = scratch_for(partials.device, w3_scratch_bytes(1, total_out, in_features))
+    with torch.cuda.device(partials.device):
+        check(library().fb_w3_gemv_attn_merge(ptr(partials), int(splits), dtype_tag(act_dtype), matrices, n_matrices, dtype_tag(scale_dtype),
+                                              int(in_features), ptr(scratch), scratch.numel() * scratch.element_size(),
+                                              FB_W3_DECODED_BF16 if decoded_bf16 else 0, stream_handle(partials.device)))
 
 
 def silu_mul(gate, up, out) -> None:

@@ -134,7 +134,10 @@ __device__ __forceinline__ void norm_rope_head(const unsigned short* src, const 
 // FUSED: q arrives raw; the kernel norms and rotates q and the new k itself (every CTA of a head
 // repeats that small piece of work), takes the new token's k / v from shared memory instead of
 // the cache, and one CTA per k/v head writes them into the cache for the steps to come.
-template <bool FUSED, bool CLUSTER>
+// PARTIAL: every CTA leaves its (output, max, sum) in its scratch slot and the launch ends there;
+// the consumer of the attention output (fb_w3_gemv_attn_merge) merges the splits while it builds
+// its tables, with the arithmetic of the merge below.  No cluster, no barrier, no ticket.
+template <bool FUSED, bool CLUSTER, bool PARTIAL = false>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsigned short* __restrict__ q,
                                                                       unsigned short* __restrict__ k_cache,
                                                                       unsigned short* __restrict__ v_cache,
@@ -271,9 +274,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) {
       const float f = sm_m[w] == -INFINITY ? 0.f : __expf(sm_m[w] - gm);
-      total += sm_l[w] * f;
+      total = fmaf(sm_l[w], f, total);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) o[i] += sm_acc[w][lane * 4 + i] * f;
+      for (int i = 0; i < 4; ++i) o[i] = fmaf(sm_acc[w][lane * 4 + i], f, o[i]);
+    }
+    if (PARTIAL) {
+      *reinterpret_cast<float4*>(slot + lane * 4) = make_float4(o[0], o[1], o[2], o[3]);
+      if (lane == 0) *reinterpret_cast<float2*>(slot + 128) = make_float2(gm, total);
+      return;
     }
     if (!CLUSTER && splits == 1) {  // nothing to merge: no scratch round trip
       const float inv1 = 1.f / total;
@@ -337,12 +345,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const unsi
   float total = 0.f, o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int sp = 0; sp < kAttnMaxSplits; ++sp) {
+    // explicit fused multiply-adds: fb_w3_gemv_attn_merge repeats this merge and must round alike
     const float f = __shfl_sync(0xffffffffu, my_f, sp);
-    total += __shfl_sync(0xffffffffu, my_l, sp) * f;
-    o[0] += part[sp].x * f;
-    o[1] += part[sp].y * f;
-    o[2] += part[sp].z * f;
-    o[3] += part[sp].w * f;
+    total = fmaf(__shfl_sync(0xffffffffu, my_l, sp), f, total);
+    o[0] = fmaf(part[sp].x, f, o[0]);
+    o[1] = fmaf(part[sp].y, f, o[1]);
+    o[2] = fmaf(part[sp].z, f, o[2]);
+    o[3] = fmaf(part[sp].w, f, o[3]);
   }
   const float inv = 1.f / total;
   uint2 packed;
@@ -518,6 +527,29 @@ extern "C" int fb_attn_decode_fused(const void* q, const void* k, const void* v,
   return launch_attention(attn_decode_kernel<true, false>, attn_decode_kernel<true, true>, dim3(q_heads, splits), static_cast<cudaStream_t>(stream), "attn_decode_fused launch",
                     static_cast<const unsigned short*>(nullptr), u16(k_cache), u16(v_cache), u16(out), partial, tickets, q_heads, kv_heads, length,
                     max_positions, scale, dtype, nt);
+}
+
+extern "C" int fb_attn_decode_splits(int length) { return length < 1 ? 0 : attention_splits(length); }
+
+extern "C" int fb_attn_decode_partial(const void* q, const void* k, const void* v, const void* q_weight, const void* k_weight,
+                                      const void* cosv, const void* sinv, void* k_cache, void* v_cache, int q_heads, int kv_heads,
+                                      int head_dim, int position, int max_positions, float eps, float scale, int dtype,
+                                      void* partials, size_t partial_bytes, fb_stream_t stream) {
+  if (!q || !k || !v || !q_weight || !k_weight || !cosv || !sinv || !k_cache || !v_cache) return fail(FB_EINVAL, "fb_attn_decode_partial: null pointer");
+  if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_attn_decode_partial: dtype must be FB_F16 or FB_BF16");
+  if (head_dim != 128) return fail(FB_ELIMIT, "fb_attn_decode_partial: head_dim must be 128");
+  if (q_heads < 1 || kv_heads < 1 || q_heads % kv_heads) return fail(FB_ELIMIT, "fb_attn_decode_partial: q_heads must be a multiple of kv_heads");
+  if (position < 0 || position >= max_positions) return fail(FB_ELIMIT, "fb_attn_decode_partial: position %d outside the cache of %d", position, max_positions);
+  if (!aligned(q, 8) || !aligned(k, 8) || !aligned(v, 8) || !aligned(k_cache, 8) || !aligned(v_cache, 8))
+    return fail(FB_EINVAL, "fb_attn_decode_partial: tensors must be 8-byte aligned");
+  const size_t need = fb_attn_decode_scratch_bytes(q_heads);
+  if (!partials || partial_bytes < need || !aligned(partials, 16)) return fail(FB_ESCRATCH, "fb_attn_decode_partial: 16-byte aligned buffer of %zu bytes needed", need);
+  const int length = position + 1;
+  const NewToken nt = {u16(q), u16(k), u16(v), u16(q_weight), u16(k_weight), u16(cosv), u16(sinv), eps};
+  return launch_pdl(attn_decode_kernel<true, false, true>, dim3(q_heads, attention_splits(length)), dim3(kAttnWarps * 32), 0,
+                    static_cast<cudaStream_t>(stream), "attn_decode_partial launch", static_cast<const unsigned short*>(nullptr), u16(k_cache),
+                    u16(v_cache), static_cast<unsigned short*>(nullptr), static_cast<float*>(partials), static_cast<unsigned*>(nullptr), q_heads,
+                    kv_heads, length, max_positions, scale, dtype, nt);
 }
 
 extern "C" int fb_silu_mul(const void* gate, const void* up, void* out, int n, int dtype, fb_stream_t stream) {

@@ -90,8 +90,9 @@ struct W3Params {
   W3Matrix mats[kMaxMatrices];
   int n_mats;
   const int16_t* perm;
-  const void* prologue_arg;  // RMSNorm weight [K] (kind 1) or the `up` vector [K] (kind 2)
-  int prologue;              // 0 none, 1 RMSNorm of x, 2 x = silu(x) * up  (M = 1, identity order)
+  const void* prologue_arg;  // RMSNorm weight [K] (kind 1), the `up` vector [K] (kind 2), attention partials (kind 3)
+  int prologue;              // 0 none, 1 RMSNorm of x, 2 x = silu(x) * up, 3 x = merged attention splits  (M = 1, identity order)
+  int attn_splits;           // kind 3: splits per head (1..8)
   float eps;
   // Tensor-parallel push (M = 1, one matrix): instead of writing `out`, the final fp32 value of a
   // row goes, together with a valid mark in the same 8-byte store, to slot `row` of a buffer on
@@ -384,7 +385,7 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
   auto fetch_el = [&](int kb_) {
     const int e = kb_ * 256 + (int)threadIdx.x;
     el_raw = el_op = 0u;
-    if (threadIdx.x < 256 && e < p.K) {
+    if (p.prologue != 3 && threadIdx.x < 256 && e < p.K) {
       el_raw = reinterpret_cast<const unsigned short*>(p.x)[e];
       el_op = reinterpret_cast<const unsigned short*>(p.prologue_arg)[e];
     }
@@ -442,7 +443,45 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
 #pragma unroll
     for (int m = 0; m < M; ++m) {
       float v8[8];
-      if (shared_x) {
+      if (shared_x && p.prologue == 3) {
+        // x = the attention output, still in pieces: every split of a head left (output[128], max, sum) in
+        // its slot; merge them as the attention kernel's own last step does (ascending split order, the
+        // same fused multiply-adds) and round to the activation dtype.
+        if (threadIdx.x < 256) {
+          const int e = kb_ * 256 + (int)threadIdx.x;
+          float value = 0.f;
+          if (e < p.K) {
+            const float* slots = static_cast<const float*>(p.prologue_arg) + (size_t)(e >> 7) * (16 * 132);
+            float ms[8], ls[8], as[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+              ms[sp] = -INFINITY, ls[sp] = 0.f, as[sp] = 0.f;
+              if (sp < p.attn_splits) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(slots + sp * 132 + 128));
+                ms[sp] = ml.x, ls[sp] = ml.y;
+                as[sp] = __ldcg(slots + sp * 132 + (e & 127));
+              }
+            }
+            float gm = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) gm = fmaxf(gm, ms[sp]);
+            float total = 0.f, o = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+              const float f = ms[sp] == -INFINITY ? 0.f : __expf(ms[sp] - gm);
+              total = fmaf(ls[sp], f, total);
+              o = fmaf(as[sp], f, o);
+            }
+            value = round_to(o * (1.f / total), p.act_dtype);
+          }
+          xs[M == 1 ? threadIdx.x : 0] = value;
+        }
+        __syncthreads();
+        const float4 lo = *reinterpret_cast<const float4*>(&xs[M == 1 ? (lane >> 4) * 128 + (lane & 15) * 8 : 0]);
+        const float4 hi4 = *reinterpret_cast<const float4*>(&xs[M == 1 ? (lane >> 4) * 128 + (lane & 15) * 8 + 4 : 0]);
+        v8[0] = lo.x, v8[1] = lo.y, v8[2] = lo.z, v8[3] = lo.w;
+        v8[4] = hi4.x, v8[5] = hi4.y, v8[6] = hi4.z, v8[7] = hi4.w;
+      } else if (shared_x) {
         if (threadIdx.x < 256) {
           // same roundings as the separate kernels: RMSNorm casts before the weight multiply,
           // SwiGLU rounds silu(gate) before the product
@@ -817,7 +856,8 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
       if (!push->data[r] || !aligned(push->data[r], 8))
         return fail(FB_EINVAL, "fb_w3_gemv_push: exchange pointer of rank %d missing or not 8-byte aligned", r);
   }
-  if (prologue < 0 || prologue > 2) return fail(FB_EINVAL, "fb_w3_gemv: unknown input transform %d", prologue);
+  if (prologue < 0 || prologue > 3) return fail(FB_EINVAL, "fb_w3_gemv: unknown input transform %d", prologue);
+  if (prologue == 3 && (K % 128 || eps < 1.f || eps > 8.f)) return fail(FB_ELIMIT, "fb_w3_gemv_attn_merge: 1..8 splits per head");
   if (prologue != 0 && (m != 1 || perm || !prologue_arg || !aligned(prologue_arg, 16)))
     return fail(FB_EINVAL, "fb_w3_gemv: a fused input transform needs M = 1, identity column order and a 16-byte aligned operand");
   const bool group_partials = (flags & FB_W3_GROUP_PARTIALS) != 0;
@@ -838,6 +878,7 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   p.x = x;
   p.perm = perm;
   p.prologue = prologue;
+  p.attn_splits = prologue == 3 ? (int)eps : 0;
   p.prologue_arg = prologue_arg;
   p.eps = eps;
   p.push_world = push ? push->world : 0;
@@ -941,6 +982,15 @@ extern "C" int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transfor
     return fail(FB_EINVAL, "fb_w3_gemv_fused_input: transform must be FB_W3_INPUT_RMSNORM or FB_W3_INPUT_SILU_MUL");
   return run_multi(x, act_dtype, 1, matrices, n_matrices, scale_dtype, nullptr, in_features, scratch, scratch_bytes, flags, stream,
                    transform, operand, eps);
+}
+
+extern "C" int fb_w3_gemv_attn_merge(const void* partials, int splits, int act_dtype, const fb_w3_matrix_t* matrices, int n_matrices,
+                                     int scale_dtype, int in_features, void* scratch, size_t scratch_bytes, unsigned flags,
+                                     fb_stream_t stream) {
+  if (splits < 1 || splits > 8) return fail(FB_ELIMIT, "fb_w3_gemv_attn_merge: %d splits per head, 1..8 supported", splits);
+  // the partials stand in for x (head h, split s at float offset (16 h + s) * 132) and are the transform's operand
+  return run_multi(partials, act_dtype, 1, matrices, n_matrices, scale_dtype, nullptr, in_features, scratch, scratch_bytes, flags, stream,
+                   3, partials, (float)splits);
 }
 
 extern "C" int fb_w3_gemv_push(const void* x, int act_dtype, int transform, const void* operand, float eps,

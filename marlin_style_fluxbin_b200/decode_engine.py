@@ -286,7 +286,12 @@ class DecodeEngine:
                 nat.w3_gemv_multi(self.xn, layer.qkv_list, 3, self.qkv.numel(), f16, None, scratch=self.scratch, decoded_bf16=dec)
             else:
                 torch.mm(self.xn, layer.dense["qkv"].t(), out=self.qkv)  # q, k, v are views of this buffer
-            if self.fuse_attention:
+            # packed arm, unsharded: the attention launch stops at per-split pieces and the o GEMV merges them in its table build
+            merge_in_o = w3 and self.fuse_attention and not self.tp_push and self.tp_size == 1
+            if merge_in_o:
+                splits = nat.attn_decode_partial(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.k_cache[index],
+                                                 self.v_cache[index], position, s.eps, scale, self.attn_scratch)
+            elif self.fuse_attention:
                 nat.attn_decode_fused(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.k_cache[index],
                                       self.v_cache[index], self.attn, position, s.eps, scale, self.attn_scratch)
             else:
@@ -298,6 +303,9 @@ class DecodeEngine:
                 nat.w3_gemv_push(self.attn, 0, None, 0.0, layer.o_push, self.attn.shape[-1], f16, site["push"], scratch=self.scratch,
                                  decoded_bf16=dec)
                 nat.tp_reduce(site["parts"], self.tp_size, self.h, self.h_next, site["status"])
+            elif merge_in_o:
+                nat.w3_gemv_attn_merge(self.attn_scratch, splits, self.dtype, self.attn.shape[-1], layer.o_list, 1, s.hidden, f16,
+                                       scratch=self.scratch, decoded_bf16=dec)
             elif w3:
                 nat.w3_gemv_multi(self.attn, layer.o_list, 1, s.hidden, f16, None, scratch=self.scratch, decoded_bf16=dec)
             elif self.tp_rank == 0:

@@ -151,3 +151,50 @@ def test_fused_attention_equals_the_two_launch_form(position, dtype):
     scores = torch.einsum("hd,hpd->hp", heads, keys.repeat_interleave(group, dim=0)) * scale
     want = torch.einsum("hp,hpd->hd", scores.softmax(-1), values.repeat_interleave(group, dim=0)).reshape(1, -1)
     assert (out_b.float() - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("position", (0, 63, 200, 530, 1500))
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+def test_attention_pieces_merged_by_the_consuming_gemv(position, dtype):
+    """The attention launch that stops at per-split pieces, merged inside the o-projection GEMV's table
+    build, gives the output of fb_attn_decode_fused followed by the plain GEMV bit for bit (cache rows too)."""
+    from marlin_style_fluxbin_b200 import _native
+    from marlin_style_fluxbin_b200.decode_engine import synthetic_w3
+
+    q_heads, kv_heads, dim, max_positions, hidden = 8, 2, 128, 1536, 384
+    gen = torch.Generator().manual_seed(position + 11)
+    rnd = lambda *shape: torch.randn(*shape, generator=gen).to(dtype).cuda()  # noqa: E731
+    q, k, v = rnd(1, q_heads * dim), rnd(1, kv_heads * dim), rnd(1, kv_heads * dim)
+    q_weight, k_weight = (1 + 0.1 * rnd(dim)), (1 + 0.1 * rnd(dim))
+    angle = torch.rand(dim // 2, generator=gen) * 6.28
+    cos, sin = torch.cat([angle.cos()] * 2).to(dtype).cuda(), torch.cat([angle.sin()] * 2).to(dtype).cuda()
+    caches = [rnd(kv_heads, max_positions, dim) for _ in range(2)]
+    scale = dim ** -0.5
+    layout = synthetic_w3(hidden, q_heads * dim, torch.device("cuda"), torch.Generator(device="cuda").manual_seed(5))
+    residual = rnd(1, hidden)
+
+    def project(run_attention):
+        k_cache, v_cache = caches[0].clone(), caches[1].clone()
+        scratch = torch.zeros(_native.attn_scratch_bytes(q_heads), dtype=torch.uint8, device="cuda")
+        out = torch.full((1, hidden), float("nan"), device="cuda", dtype=dtype)
+        matrices = _native.w3_matrix_list([(layout["planes"], layout["scales"], layout.get("zeros"), out, residual)])
+        run_attention(k_cache, v_cache, scratch, matrices)
+        torch.cuda.synchronize()
+        _native.check_status(torch.device("cuda"))
+        return out, k_cache, v_cache
+
+    def whole(k_cache, v_cache, scratch, matrices):
+        attn = torch.empty_like(q)
+        _native.attn_decode_fused(q, k, v, q_weight, k_weight, cos, sin, k_cache, v_cache, attn, position, 1e-6, scale, scratch)
+        _native.w3_gemv_multi(attn, matrices, 1, hidden, layout["scales"].dtype, None)
+
+    def pieces(k_cache, v_cache, scratch, matrices):
+        splits = _native.attn_decode_partial(q, k, v, q_weight, k_weight, cos, sin, k_cache, v_cache, position, 1e-6, scale, scratch)
+        assert 1 <= splits <= 8 and (splits > 1) == (position + 1 > 80)
+        _native.w3_gemv_attn_merge(scratch, splits, dtype, q_heads * dim, matrices, 1, hidden, layout["scales"].dtype)
+
+    want, k_a, v_a = project(whole)
+    got, k_b, v_b = project(pieces)
+    assert torch.isfinite(want.float()).all()
+    assert torch.equal(got, want)
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
