@@ -7,11 +7,13 @@
 //   * a CTA owns 128 output rows and a contiguous range of K groups (split-K over CTAs);
 //   * the three bit planes of (group, 128 rows) arrive by one tiled TMA copy (6 KB);
 //   * 256 threads turn them into a 128 x 128 tile of 16-bit weights T((code - zero) * T(scale)):
-//     every 4 plane bits index a 16-entry table of four 16-bit floats (0 / 1), kept in sixteen
-//     bank-disjoint copies, and packed 16-bit multiply-adds combine the planes, the zero point
-//     and the scale; tiles are written straight in the K-major "core matrix" order that the MMA's
-//     shared-memory descriptor walks (8 rows x 16 bytes per core matrix, no swizzle): one 16-byte
-//     store per 8 weights;
+//     a plane byte (8 inputs) indexes a 256-entry table that spreads its bits over the eight
+//     nibbles of a word; the three planes' words add up to eight 3-bit codes, which one logic
+//     instruction per pair drops into the mantissas of two 16-bit floats (1024 + code, or
+//     128 + code for bf16); a packed subtract removes the bias and the zero point exactly and a
+//     packed multiply applies the scale with its single rounding.  Tiles are written straight in
+//     the K-major "core matrix" order that the MMA's shared-memory descriptor walks (8 rows x 16
+//     bytes per core matrix, no swizzle): one 16-byte store per 8 weights;
 //   * the activations of the group (M rows padded to N = 16) are stored the same way;
 //   * warp-specialised: eight warps dequantise, the elected lane of a ninth issues the plane
 //     copies and 8 x tcgen05.mma (128 x 16 x 16 each) per group, accumulating in 16 TMEM columns
@@ -44,6 +46,7 @@ constexpr int kThreads = kProducers + 32;  // and one warp whose elected lane is
 constexpr int kATile = kTileRows * 128 * 2;  // 32 KB: 128 rows x 128 k, 16-bit
 constexpr int kBTile = kN * 128 * 2;         // 4 KB
 constexpr int kPlaneTile = 3 * kTileRows * 16;  // 6 KB: three planes of 128 rows
+constexpr int kPlaneStages = 4;  // groups whose planes are in flight or staged: HBM latency is longer than one tile's dequantisation
 constexpr int kMaxSplits = 16;
 constexpr int kTmemCols = 32;
 constexpr size_t kCombineOffset = 16384;
@@ -86,29 +89,34 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
   unsigned char* const a_tiles = smem;                           // 2 x 32 KB
   unsigned char* const b_tiles = smem + 2 * kATile;              // 2 x 4 KB
   unsigned char* const planes_s = b_tiles + 2 * kBTile;          // 2 x 6 KB
-  uint64_t* const bars = reinterpret_cast<uint64_t*>(planes_s + 2 * kPlaneTile);  // plane_full[2], mma_done[2], all_done, tile_full[2]
-  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
-  // Nibble table: entry e (4 plane bits) -> four 16-bit floats, 1.0 where the bit is set.  Sixteen
-  // copies side by side (entry stride 128 B, copy stride 8 B): lane l reads copy l % 16, so the 16
-  // lanes of a half-warp phase of an 8-byte load hit 16 different 8-byte bank groups whatever the
-  // weights are.
-  // The table starts on a 2 KB boundary (found at run time inside 4 KB of slack), so that entry
-  // offset (bits 7..10), copy offset (bits 3..6) and base combine with one logic instruction.
-  unsigned char* const nibbles = planes_s + 2 * kPlaneTile + 64 + ((2048u - ((smem_u32(planes_s) + 2 * kPlaneTile + 64) & 2047u)) & 2047u);
+  // barriers: mma_done[2] at 0, all_done at 2, tile_full[2] at 3, plane_full[kPlaneStages] at 5
+  uint64_t* const bars = reinterpret_cast<uint64_t*>(planes_s + kPlaneStages * kPlaneTile);
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 + kPlaneStages);
+  // Spread table: entry b (a plane byte, bit i = input i of the chunk) -> a word whose nibble for
+  // input i holds that bit; input 2j sits in nibble j of the low half, input 2j + 1 in nibble j of
+  // the high half, so that shifting by 4j and masking with 0x000f000f leaves inputs 2j and 2j + 1 in
+  // the two 16-bit lanes of a word.  Sixteen copies side by side (entry stride 64 B, copy stride
+  // 4 B): lane l reads copy l % 16, so two lanes at most share a bank group.
+  unsigned char* const spread = planes_s + kPlaneStages * kPlaneTile + 128;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, split = blockIdx.y;
   const int g_begin = split * p.groups_per_split, g_end = min(p.G, g_begin + p.groups_per_split);
   const int ng = g_end - g_begin;
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (tid < 7) {
-    mbar_init(smem_u32(&bars[tid]), tid < 5 ? 1 : kProducers);  // a finished tile: every producer thread arrives
+  if (tid < 5 + kPlaneStages) {
+    mbar_init(smem_u32(&bars[tid]), tid == 3 || tid == 4 ? kProducers : 1);  // a finished tile: every producer thread arrives
     mbar_init_fence();
   }
   if (tid < kProducers) {
-    const uint32_t one = BF16 ? 0x3f80u : 0x3c00u, entry = (uint32_t)tid >> 4;
-    const uint2 halves = make_uint2(((entry & 1u) ? one : 0u) | (((entry & 2u) ? one : 0u) << 16), ((entry & 4u) ? one : 0u) | (((entry & 8u) ? one : 0u) << 16));
-    *reinterpret_cast<uint2*>(nibbles + entry * 128 + (tid & 15) * 8) = halves;  // 256 threads: 16 entries x 16 copies
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {  // 256 entries x 16 copies, written in address order
+      const uint32_t index = (uint32_t)tid + 256u * j, byte = index >> 4;
+      uint32_t word = 0u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) word |= ((byte >> i) & 1u) << ((i & 1) * 16 + (i >> 1) * 4);
+      reinterpret_cast<uint32_t*>(spread)[index] = word;
+    }
   }
   if (warp == 0) {  // TMEM columns for the 128 x 16 fp32 accumulator
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
@@ -120,18 +128,17 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
 
   auto issue_planes = [&](int gi) {  // one elected thread: the three planes of group gi, 128 rows
-    const uint32_t bar = smem_u32(&bars[gi & 1]);
+    const uint32_t bar = smem_u32(&bars[5 + gi % kPlaneStages]);
     mbar_expect_tx(bar, (uint32_t)kPlaneTile);
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-            smem_u32(planes_s + (size_t)(gi & 1) * kPlaneTile)),
+            smem_u32(planes_s + (size_t)(gi % kPlaneStages) * kPlaneTile)),
         "l"(&p.plane_map), "r"(0), "r"(tile * (kTileRows / 32)), "r"(3 * (g_begin + gi)), "r"(bar)
         : "memory");
   };
   const bool issuer = tid == kProducers;  // lane 0 of the ninth warp
   if (issuer) {  // weights never change: staged before the wait on the previous kernel
-    if (ng > 0) issue_planes(0);
-    if (ng > 1) issue_planes(1);
+    for (int gi = 0; gi < kPlaneStages && gi < ng; ++gi) issue_planes(gi);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -173,13 +180,13 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
     }
   };
   // ---- the issuing lane: for every group, wait for its tile, run the eight MMAs, signal the
-  // buffer free through the MMAs' completion, and stage the planes of two groups ahead (every
+  // buffer free through the MMAs' completion, and stage the planes kPlaneStages groups ahead (every
   // producer has read this buffer's planes once the tile is complete).  No CTA-wide barrier in
   // the loop: producers and issuer meet on mbarriers only. ----
   if (issuer) {
     for (int gi = 0; gi < ng; ++gi) {
       const int buf = gi & 1;
-      if (!mbar_wait_bounded(smem_u32(&bars[5 + buf]), (uint32_t)((gi >> 1) & 1))) {
+      if (!mbar_wait_bounded(smem_u32(&bars[3 + buf]), (uint32_t)((gi >> 1) & 1))) {
         dead = true;
         break;
       }
@@ -189,10 +196,10 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
       for (int j = 0; j < 8; ++j)  // K = 16 per instruction: two chunks
         mma_f16(tmem_base, smem_desc(a_base + j * 2 * 2048, 2048, 128), smem_desc(b_base + j * 2 * 256, 256, 128), idesc,
                 (gi > 0 || j > 0) ? 1u : 0u);
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[2 + buf])) : "memory");
-      if (gi + 2 < ng) issue_planes(gi + 2);
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[buf])) : "memory");
+      if (gi + kPlaneStages < ng) issue_planes(gi + kPlaneStages);  // every producer has read this stage: its tile is complete
     }
-    if (!dead) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[4])) : "memory");
+    if (!dead) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[2])) : "memory");
   }
 
   if (tid < kProducers && ng > 0) fetch_group(g_begin);
@@ -205,8 +212,8 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
     if (gi + 1 < ng) fetch_group(g_begin + gi + 1);
     // the tiles of this buffer were last read by the MMAs issued two groups ago
     bool ok = true;
-    if (gi >= 2) ok = mbar_wait_bounded(smem_u32(&bars[2 + buf]), (uint32_t)(((gi >> 1) - 1) & 1));
-    ok = ok && mbar_wait_bounded(smem_u32(&bars[buf]), (uint32_t)((gi >> 1) & 1));
+    if (gi >= 2) ok = mbar_wait_bounded(smem_u32(&bars[buf]), (uint32_t)(((gi >> 1) - 1) & 1));
+    ok = ok && mbar_wait_bounded(smem_u32(&bars[5 + gi % kPlaneStages]), (uint32_t)((gi / kPlaneStages) & 1));
     if (!ok) {
       dead = true;
       break;
@@ -215,52 +222,49 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
     *reinterpret_cast<uint4*>(b_tiles + (size_t)buf * kBTile + xc * 256 + (xn >> 3) * 128 + (xn & 7) * 16) = xraw;
     // ---- weight tile: core matrix (chunk, 8 rows) at chunk * 2048 + (row / 8) * 128 ----
     {
-      const unsigned char* pl = planes_s + (size_t)buf * kPlaneTile + row_in_tile * 16 + khalf * 8;
+      const unsigned char* pl = planes_s + (size_t)(gi % kPlaneStages) * kPlaneTile + row_in_tile * 16 + khalf * 8;
       const uint2 w0 = *reinterpret_cast<const uint2*>(pl), w1 = *reinterpret_cast<const uint2*>(pl + kTileRows * 16),
                   w2 = *reinterpret_cast<const uint2*>(pl + 2 * kTileRows * 16);
-      // weight = T((code - zero) * T(scale)) in packed 16-bit arithmetic.  Each plane byte is two
-      // nibbles; a nibble's four bits come back from the table as four 16-bit floats (0 or 1), so
-      // code - 4 = t0 + 2 t1 - 4 t2' (the high plane is stored inverted) is two packed multiply-adds
-      // on exact small integers, one packed add moves the zero point (4 - zero), and one packed
-      // multiply applies the scale with a single rounding, as the reference's dense fallback rounds.
-      constexpr bool bf16 = BF16;
+      // weight = T((code - zero) * T(scale)) in packed 16-bit arithmetic.  The three planes' spread
+      // words add up to code' = b0 + 2 b1 + 4 b2' per nibble (the high plane is stored inverted, so
+      // code = code' ^ 4).  For the pair of inputs (2j, 2j + 1): shift by 4j, keep the two nibbles,
+      // flip their bit 2 and set the exponent bits of 1024 (fp16) or 128 (bf16) in ONE three-input
+      // logic instruction: the two lanes now hold bias + code exactly.  A packed subtract of
+      // bias + zero leaves code - zero, a packed multiply applies the scale with a single rounding,
+      // as the reference's dense fallback rounds.
       using Pair = typename std::conditional<BF16, __nv_bfloat162, __half2>::type;
       auto as_pair = [](uint32_t bits) { return *reinterpret_cast<const Pair*>(&bits); };
       auto as_bits = [](Pair v) { return *reinterpret_cast<const uint32_t*>(&v); };
-      const Pair two = as_pair(bf16 ? 0x40004000u : 0x40004000u), minus_four = as_pair(bf16 ? 0xc080c080u : 0xc400c400u);
-      Pair shift2, scale2;
-      if (bf16) {
-        const __nv_bfloat162 o2 = __float2bfloat162_rn(4.f - zero), s2 = __float2bfloat162_rn(scale);
-        shift2 = *reinterpret_cast<const Pair*>(&o2);
+      Pair bias_zero2, scale2;  // bias + zero (an integer below 2048 / 256: exact), scale
+      if (BF16) {
+        const __nv_bfloat162 o2 = __float2bfloat162_rn(128.f + zero), s2 = __float2bfloat162_rn(scale);
+        bias_zero2 = *reinterpret_cast<const Pair*>(&o2);
         scale2 = *reinterpret_cast<const Pair*>(&s2);
       } else {
-        const __half2 o2 = __float2half2_rn(4.f - zero), s2 = __float2half2_rn(scale);
-        shift2 = *reinterpret_cast<const Pair*>(&o2);
+        const __half2 o2 = __float2half2_rn(1024.f + zero), s2 = __float2half2_rn(scale);
+        bias_zero2 = *reinterpret_cast<const Pair*>(&o2);
         scale2 = *reinterpret_cast<const Pair*>(&s2);
       }
-      const uint32_t table = smem_u32(nibbles) + (uint32_t)((lane & 15) * 8);
-      auto nibble = [&](uint32_t word, int bit) {  // the table row of bits [bit, bit + 4) of `word`
-        const uint32_t offset = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
-        uint2 v;
-        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"((offset & 0x780u) | table));
+      constexpr uint32_t kMagic = (BF16 ? 0x43004300u : 0x64006400u) | 0x00040004u;  // exponent bits, and the flip of bit 2
+      const uint32_t table = smem_u32(spread) + (uint32_t)((lane & 15) * 4);
+      auto spread_of = [&](uint32_t word, int byte) {  // the table word of byte `byte` of `word`
+        uint32_t v;
+        const uint32_t index = (word >> (8 * byte)) & 0xffu;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(table + index * 64u));
         return v;
       };
       unsigned char* const a_row = a_tiles + (size_t)buf * kATile + (row_in_tile >> 3) * 128 + (row_in_tile & 7) * 16;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const uint32_t p0 = c < 4 ? w0.x : w0.y, p1 = c < 4 ? w1.x : w1.y, p2 = c < 4 ? w2.x : w2.y;
+        // nibbles never carry: b0 + 2 b1 + 4 b2' <= 7
+        const uint32_t codes = spread_of(p0, c & 3) + 2u * spread_of(p1, c & 3) + 4u * spread_of(p2, c & 3);
         uint32_t packed[4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {  // low nibble: inputs 0..3 of the chunk, high nibble: inputs 4..7
-          const int bit = 8 * (c & 3) + 4 * h;
-          const uint2 t0 = nibble(p0, bit), t1 = nibble(p1, bit), t2 = nibble(p2, bit);
-          const uint32_t t0w[2] = {t0.x, t0.y}, t1w[2] = {t1.x, t1.y}, t2w[2] = {t2.x, t2.y};
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            Pair v = __hfma2(as_pair(t1w[i]), two, as_pair(t0w[i]));
-            v = __hfma2(as_pair(t2w[i]), minus_four, v);
-            packed[2 * h + i] = as_bits(__hmul2(__hadd2(v, shift2), scale2));
-          }
+        for (int j = 0; j < 4; ++j) {
+          uint32_t biased;  // (shifted & 0x000f000f) ^ 0x00040004 | exponent bits == mask ? shifted ^ magic : magic
+          asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(biased) : "r"(codes >> (4 * j)), "r"(0x000f000fu), "r"(kMagic));
+          packed[j] = as_bits(__hmul2(__hsub2(as_pair(biased), bias_zero2), scale2));
         }
         *reinterpret_cast<uint4*>(a_row + (size_t)(khalf * 8 + c) * 2048) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
@@ -268,13 +272,13 @@ __global__ void __launch_bounds__(kThreads, 2) w3_mma_kernel(const __grid_consta
     // generic-proxy stores must be visible to the tensor core's (async proxy) reads; then this
     // thread's part of the tile is done
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[5 + buf])) : "memory");
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[3 + buf])) : "memory");
   }
 
   // ---- all MMAs done: read the accumulator back ----
   // (a thread whose bounded wait expired arrives here with `dead` set; the others' waits expire in turn)
   {
-    const bool ok = !dead && (ng == 0 || mbar_wait_bounded(smem_u32(&bars[4]), 0u));
+    const bool ok = !dead && (ng == 0 || mbar_wait_bounded(smem_u32(&bars[2]), 0u));
     if (__syncthreads_or(!ok)) dead = true;
   }
   if (dead) {
@@ -385,7 +389,7 @@ extern "C" int fb_w3_gemm_small(const void* x, int act_dtype, int m, const uint8
   p.groups_per_split = (G + splits - 1) / splits;
   p.splits = (G + p.groups_per_split - 1) / p.groups_per_split;
 
-  const size_t smem = 2 * (size_t)kATile + 2 * kBTile + 2 * kPlaneTile + 64 + 4096;
+  const size_t smem = 2 * (size_t)kATile + 2 * kBTile + kPlaneStages * kPlaneTile + 128 + 16384;  // tiles, barriers, spread table
   static std::mutex lock;
   static bool ready[64] = {};
   int device = 0;
