@@ -423,16 +423,16 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
     }
 #pragma unroll
     for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
-    float* scratch_f = reinterpret_cast<float*>(lut);  // the table area is still free here
-    if (lane == 0) scratch_f[warp] = ss;
+    __shared__ float warp_sums[kWarps];
+    if (lane == 0) warp_sums[warp] = ss;
     __syncthreads();
     ss = 0.f;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) ss += scratch_f[w];
+    for (int w = 0; w < kWarps; ++w) ss += warp_sums[w];
     inv_rms = rsqrtf(ss / (float)p.K + p.eps);
-    __syncthreads();
   }
-  for (int t = 1; t < kStages && pf_left > 0; ++t) issue_next();  // the rest of the ring, behind the activation loads
+
+  if (kStages > 1 && pf_left > 0) issue_next();  // the second ring stage, behind the activation loads
 
   // ---- build the 32 tables of K block kb_: lane = table; warp w owns the entries of
   // 16 / kWarps low nibbles (2w and 2w + 1 with eight warps), so that the walk over the high nibble unrolls with constant offsets.  sx[m][jh]: the sum of the activations of the group this lane walks in half jh. ----
@@ -749,6 +749,7 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
     }
   };
   build(kb_begin, sx_cur);
+  for (int t = 2; t < kStages && pf_left > 0; ++t) issue_next();  // the rest of the ring
   __syncthreads();
   for (int s = 0; s < nS; ++s) {
     if (!dead) run_block(s);
