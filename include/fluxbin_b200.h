@@ -332,6 +332,9 @@ int fb_embed_row(const void* embedding, const int64_t* token, void* out, int voc
  * allocates nothing.  The first call on a device looks up the array's device address; make that
  * first call before any stream capture.  All calls on a device share the one array: the control
  * block is cleared on the stream at every call, and two calls that can overlap on the GPU race.
+ * The device-side status word (an expired bounded wait) lives in that control block too and is
+ * wiped by the next call's clear, so it cannot be observed through this entry point: callers that
+ * need it use fb_w3_gemv with their own scratch.
  * It has no counterpart in the reference, whose callers always pass a workspace.
  */
 #define FB_W3_STATIC_SCRATCH_BYTES (4u << 20)
