@@ -241,6 +241,18 @@ def test_native_rejections_carry_messages():
         _native.w3_gemv(xg, lg["planes"], lg["scales"], None, None, out, scratch=torch.zeros(256, dtype=torch.uint8, device="cuda"))
     with pytest.raises(_native.NativeError, match="multiple of 32"):
         _native.w3_gemv(xg, lg["planes"][:, :, :40].contiguous(), lg["scales"][:, :40].contiguous(), None, None, out[:, :40])
+    # the attention-pieces entry points: split count outside 1..8, a pieces buffer that is too small
+    matrices = _native.w3_matrix_list([(lg["planes"], lg["scales"], None, out, None)])
+    pieces = torch.zeros(_native.attn_scratch_bytes(2), dtype=torch.uint8, device="cuda")
+    for splits in (0, 9):
+        with pytest.raises(_native.NativeError, match="splits"):
+            _native.w3_gemv_attn_merge(pieces, splits, torch.bfloat16, 256, matrices, 1, 64, lg["scales"].dtype)
+    head = torch.zeros(1, 256, device="cuda", dtype=torch.bfloat16)
+    row, cache = torch.zeros(128, device="cuda", dtype=torch.bfloat16), torch.zeros(1, 16, 128, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(_native.NativeError, match="buffer"):
+        _native.attn_decode_partial(head, head[:, :128], head[:, :128], row, row, row, row, cache, cache.clone(), 3, 1e-6, 1.0, pieces[:64])
+    assert _native.library().fb_attn_decode_splits(80) == 1 and _native.library().fb_attn_decode_splits(81) == 2
+    assert _native.library().fb_attn_decode_splits(100000) == 8 and _native.library().fb_attn_decode_splits(0) == 0
 
 
 def test_prepared_linear_binding_and_graph():
