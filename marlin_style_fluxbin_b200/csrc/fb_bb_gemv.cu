@@ -71,7 +71,8 @@ __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm) bb_gemv_kernel(const 
   constexpr int kUnitBytes = GPB * kGroupBytes;  // staged per unit
   constexpr int kLutBytes = GPB * kGroupLutBytes, kSparseLutBytes = GPB * kGroupSparseBytes;
   extern __shared__ __align__(1024) unsigned char smem[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // the warp index through a shuffle, so that the compiler knows it is the same in all lanes (uniform registers)
+  const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int S = p.slots;
   unsigned char* const lut = smem;
   float* const sparse_lut = reinterpret_cast<float*>(smem + kLutBytes);

@@ -214,7 +214,9 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
   extern __shared__ __align__(1024) unsigned char smem[];
   using G_ = Geom<M>;
   constexpr int kStages = G_::kStages, kWarps = G_::kWarps;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // the warp index through a shuffle: the compiler then knows that it, and everything derived from it (ring
+  // addresses, unit counters, copy coordinates), is the same in all lanes and keeps it in uniform registers
+  const int lane = threadIdx.x & 31, warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   unsigned char* const lut = smem;
   // Every warp owns a private ring of kStages staged units, [stage][group half * 3 + plane][32 rows
   // x 16 B], and one mbarrier per stage: warps never wait for one another between table builds.
