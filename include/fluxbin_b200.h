@@ -122,6 +122,8 @@ int fb_w3_gemv_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* 
  */
 #define FB_W3_INPUT_RMSNORM 1
 #define FB_W3_INPUT_SILU_MUL 2
+#define FB_W3_INPUT_ATTN_PIECES 3 /* fb_w3_gemv_push only: x = the pieces fb_attn_decode_partial left, eps = splits per head
+                                     (what fb_w3_gemv_attn_merge does for the unsharded Linear) */
 int fb_w3_gemv_fused_input(const void* x, int act_dtype, int transform, const void* operand, float eps,
                            const fb_w3_matrix_t* matrices, int n_matrices, int scale_dtype, int in_features,
                            void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream);
@@ -321,6 +323,24 @@ int fb_lm_head_argmax(const void* x, const void* norm_weight, float eps, const v
 
 /* out[0..K) = embedding[*token, 0..K): the embedding lookup of one token id held on the device. */
 int fb_embed_row(const void* embedding, const int64_t* token, void* out, int vocab, int in_features, fb_stream_t stream);
+
+/*
+ * The LM head split by vocabulary rows over tensor-parallel ranks.  fb_lm_head_shard runs
+ * fb_lm_head_argmax's kernel over rows row_base .. row_base + vocab_rows - 1 (`weight` points at
+ * the shard's first row, `logits`, if given, at the shard's first logit) and, instead of
+ * publishing a choice, stores the shard's best key (rounded logit and global row) into slot `rank`
+ * of every rank's key array (`keys`: one array of `world` 8-byte words per rank, zero before first
+ * use; peer pointers, plain stores, no multicast).  fb_tp_argmax, launched after it on every rank,
+ * polls this rank's `world` slots (bounded: wait_ns as in fb_tp_reduce; status 6 on expiry), takes
+ * the largest key (ties: the lowest row), zeroes the slots, writes the chosen row to `best` and,
+ * when given, copies the embedding row of `forced_next` (or of the choice) into `next_hidden`.
+ * Every rank thus holds the same choice without a collective call.  No counterpart in the reference.
+ */
+int fb_lm_head_shard(const void* x, const void* norm_weight, float eps, const void* weight, int vocab_rows, int row_base,
+                     int in_features, int dtype, void* logits, const fb_w3_push_t* keys, int rank, void* scratch,
+                     size_t scratch_bytes, fb_stream_t stream);
+int fb_tp_argmax(void* keys, int world, int64_t* best, const int64_t* forced_next, const void* embedding, void* next_hidden,
+                 int vocab, int in_features, unsigned* status, uint64_t wait_ns, fb_stream_t stream);
 
 /*
  * fb_w3_gemv without a scratch argument, for callers that cannot allocate device memory where

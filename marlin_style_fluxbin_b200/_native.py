@@ -113,6 +113,13 @@ def library() -> ctypes.CDLL:
         lib.fb_attn_decode_scratch_bytes.argtypes = [ctypes.c_int]
         lib.fb_silu_mul.restype = ctypes.c_int
         lib.fb_silu_mul.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.fb_lm_head_shard.restype = ctypes.c_int
+        lib.fb_lm_head_shard.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(W3Push), ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                                         ctypes.c_void_p]
+        lib.fb_tp_argmax.restype = ctypes.c_int
+        lib.fb_tp_argmax.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                     ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]
         lib.fb_lm_head_scratch_bytes.restype = ctypes.c_size_t
         lib.fb_lm_head_scratch_bytes.argtypes = []
         lib.fb_lm_head_argmax.restype = ctypes.c_int
@@ -392,7 +399,7 @@ def silu_mul(gate, up, out) -> None:
         check(library().fb_silu_mul(ptr(gate), ptr(up), ptr(out), gate.numel(), dtype_tag(gate.dtype), stream_handle(gate.device)))
 
 
-W3_INPUT_RMSNORM, W3_INPUT_SILU_MUL = 1, 2
+W3_INPUT_RMSNORM, W3_INPUT_SILU_MUL, W3_INPUT_ATTN_PIECES = 1, 2, 3
 
 
 def w3_gemv_fused_input(x, transform: int, operand, eps: float, matrices, n_matrices, total_out, scale_dtype, *,
@@ -431,10 +438,12 @@ def w3_push_descriptor(data_ptrs) -> W3Push:
 
 
 def w3_gemv_push(x, transform: int, operand, eps: float, matrix, k: int, scale_dtype, push: W3Push, *, scratch, pdl=True,
-                 decoded_bf16=False) -> None:
-    """Row-split Linear of a tensor-parallel rank: results go to every rank's exchange buffer (see the header)."""
+                 decoded_bf16=False, act_dtype=None) -> None:
+    """Row-split Linear of a tensor-parallel rank: results go to every rank's exchange buffer (see the header).
+    With ``W3_INPUT_ATTN_PIECES`` ``x`` is the pieces buffer of ``attn_decode_partial``, ``eps`` the splits per head and
+    ``act_dtype`` the activation dtype."""
     with torch.cuda.device(x.device):
-        check(library().fb_w3_gemv_push(ptr(x), dtype_tag(x.dtype), transform, ptr(operand), float(eps), matrix, dtype_tag(scale_dtype), k,
+        check(library().fb_w3_gemv_push(ptr(x), dtype_tag(x.dtype if act_dtype is None else act_dtype), transform, ptr(operand), float(eps), matrix, dtype_tag(scale_dtype), k,
                                         ctypes.byref(push), ptr(scratch), scratch.numel() * scratch.element_size(),
                                         (0 if pdl else FB_W3_NO_PDL) | (FB_W3_DECODED_BF16 if decoded_bf16 else 0),
                                         stream_handle(x.device)))
@@ -464,6 +473,25 @@ def lm_head_argmax(x, norm_weight, eps: float, weight, best, *, logits=None, for
         check(library().fb_lm_head_argmax(ptr(x), ptr(norm_weight), float(eps), ptr(weight), vocab, k, dtype_tag(x.dtype), ptr(logits),
                                           ptr(best), ptr(forced_next), ptr(embedding), ptr(next_hidden), ptr(scratch),
                                           scratch.numel() * scratch.element_size(), stream_handle(x.device)))
+
+
+def lm_head_shard(x, norm_weight, eps: float, weight_shard, row_base: int, keys: W3Push, rank: int, *, logits_shard=None, scratch) -> None:
+    """The LM head over one rank's rows of the vocabulary (``weight_shard [V/p, K]``, a contiguous row range starting at
+    ``row_base``): the shard's best key goes to slot ``rank`` of every rank's key array; follow with ``tp_argmax``."""
+    rows, k = weight_shard.shape
+    with torch.cuda.device(x.device):
+        check(library().fb_lm_head_shard(ptr(x), ptr(norm_weight), float(eps), ptr(weight_shard), rows, int(row_base), k, dtype_tag(x.dtype),
+                                         ptr(logits_shard), ctypes.byref(keys), int(rank), ptr(scratch), scratch.numel() * scratch.element_size(),
+                                         stream_handle(x.device)))
+
+
+def tp_argmax(keys_ptr: int, world: int, best, status_ptr: int, *, forced_next=None, embedding=None, next_hidden=None, wait_ns: int = 0) -> None:
+    """Receiving half of ``lm_head_shard``: the largest of the ``world`` delivered keys becomes ``best`` (int64 ``[1]``); optionally
+    the embedding row of ``forced_next`` (or of the choice) is copied into ``next_hidden``.  Bounded poll, status 6 on expiry."""
+    vocab, k = embedding.shape if embedding is not None else (0, 0)
+    with torch.cuda.device(best.device):
+        check(library().fb_tp_argmax(ctypes.c_void_p(keys_ptr), world, ptr(best), ptr(forced_next), ptr(embedding), ptr(next_hidden), vocab, k,
+                                     ctypes.c_void_p(status_ptr), int(wait_ns), stream_handle(best.device)))
 
 
 def embed_row(embedding, token, out) -> None:

@@ -37,6 +37,12 @@ struct HeadParams {
   unsigned short* next_hidden;    // [K] or null
   float eps;
   int V, K, dtype;
+  // Vocabulary shard of a tensor-parallel rank: `weight` holds rows row_base .. row_base + V - 1 of the
+  // whole matrix, keys carry the global row, and instead of publishing its choice the last CTA stores
+  // the shard's best key into slot `push_rank` of every rank's key array (plain 8-byte peer stores).
+  int row_base;
+  unsigned long long* push_keys[8];
+  int push_world, push_rank;
 };
 
 __device__ __forceinline__ unsigned ordered_bits(float v) {
@@ -149,7 +155,7 @@ __global__ void __launch_bounds__(kHeadThreads, kHeadCtasPerSm) lm_head_kernel(c
     for (int d = 16; d >= 1; d >>= 1) total += __shfl_xor_sync(0xffffffffu, total, d);
     const float logit = round_to(total, dtype);
     if (lane == 0 && p.logits) p.logits[row] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(total)) : __half_as_ushort(__float2half_rn(total));
-    const unsigned long long key = ((unsigned long long)ordered_bits(logit) << 32) | (unsigned long long)(0xffffffffu - (unsigned)row);
+    const unsigned long long key = ((unsigned long long)ordered_bits(logit) << 32) | (unsigned long long)(0xffffffffu - (unsigned)(p.row_base + row));
     best_key = key > best_key ? key : best_key;
   }
 
@@ -169,6 +175,14 @@ __global__ void __launch_bounds__(kHeadThreads, kHeadCtasPerSm) lm_head_kernel(c
   if (!is_last) return;
   __threadfence();
   const unsigned long long final_key = *reinterpret_cast<volatile unsigned long long*>(&p.state[0]);
+  if (p.push_world > 0) {  // a key is never zero (its low word is 2^32 - 1 - row), so a non-zero slot is a delivered one
+    if (t < p.push_world) asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p.push_keys[t] + p.push_rank), "l"(final_key) : "memory");
+    if (t == 0) {
+      p.state[0] = 0ull;
+      p.state[1] = 0ull;
+    }
+    return;
+  }
   const long long chosen = (long long)(0xffffffffu - (unsigned)(final_key & 0xffffffffull));
   if (p.embedding && p.next_hidden) {
     const long long token = p.forced_next ? *p.forced_next : chosen;
@@ -195,9 +209,10 @@ __global__ void embed_row_kernel(const unsigned short* __restrict__ embedding, c
 
 extern "C" size_t fb_lm_head_scratch_bytes(void) { return 256; }
 
-extern "C" int fb_lm_head_argmax(const void* x, const void* norm_weight, float eps, const void* weight, int vocab, int in_features,
-                                 int dtype, void* logits, int64_t* best, const int64_t* forced_next, const void* embedding,
-                                 void* next_hidden, void* scratch, size_t scratch_bytes, fb_stream_t stream) {
+namespace {
+int run_head(const void* x, const void* norm_weight, float eps, const void* weight, int vocab, int in_features, int dtype, void* logits,
+             int64_t* best, const int64_t* forced_next, const void* embedding, void* next_hidden, void* scratch, size_t scratch_bytes,
+             fb_stream_t stream, int row_base, const fb_w3_push_t* keys, int rank) {
   if (!x || !weight || !best) return fail(FB_EINVAL, "fb_lm_head_argmax: x, weight and best must be non-null");
   if (dtype != FB_F16 && dtype != FB_BF16) return fail(FB_EINVAL, "fb_lm_head_argmax: dtype must be FB_F16 or FB_BF16");
   if (vocab < 1 || vocab > (1 << 30) || in_features < 8 || in_features % 8 || in_features > 49152)
@@ -227,6 +242,10 @@ extern "C" int fb_lm_head_argmax(const void* x, const void* norm_weight, float e
   p.V = vocab;
   p.K = in_features;
   p.dtype = dtype;
+  p.row_base = row_base;
+  p.push_world = keys ? keys->world : 0;
+  p.push_rank = rank;
+  for (int r = 0; r < 8; ++r) p.push_keys[r] = keys && r < keys->world ? static_cast<unsigned long long*>(keys->data[r]) : nullptr;
   const size_t smem = (size_t)in_features * sizeof(float);
   static std::mutex lock;
   static bool ready[64] = {};
@@ -249,6 +268,81 @@ extern "C" int fb_lm_head_argmax(const void* x, const void* norm_weight, float e
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == FB_BF16) return launch_pdl(lm_head_kernel<true>, dim3(ctas), dim3(kHeadThreads), smem, s, "lm_head_kernel launch", p);
   return launch_pdl(lm_head_kernel<false>, dim3(ctas), dim3(kHeadThreads), smem, s, "lm_head_kernel launch", p);
+}
+}  // namespace
+
+extern "C" int fb_lm_head_argmax(const void* x, const void* norm_weight, float eps, const void* weight, int vocab, int in_features,
+                                 int dtype, void* logits, int64_t* best, const int64_t* forced_next, const void* embedding,
+                                 void* next_hidden, void* scratch, size_t scratch_bytes, fb_stream_t stream) {
+  return run_head(x, norm_weight, eps, weight, vocab, in_features, dtype, logits, best, forced_next, embedding, next_hidden, scratch,
+                  scratch_bytes, stream, 0, nullptr, 0);
+}
+
+namespace {
+// Receiving half of the vocabulary-split LM head: one CTA polls the `world` keys that the ranks'
+// shards delivered (bounded), takes the largest (ties: the lowest row, as torch.argmax), zeroes the
+// slots, publishes the choice and copies the embedding row of the next token into the hidden state.
+__global__ void __launch_bounds__(256) tp_argmax_kernel(unsigned long long* keys, int world, long long* best, const long long* forced_next,
+                                                        const unsigned short* embedding, unsigned short* next_hidden, int V, int K,
+                                                        unsigned* status, unsigned long long wait_ns) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // after the wait: see the attention kernel's ordering rule
+  __shared__ unsigned long long chosen_key;
+  const int t = threadIdx.x;
+  if (t < 32) {
+    unsigned long long key = 0ull;
+    if (t < world) {
+      const unsigned long long start = global_timer_ns();
+      for (;;) {
+        asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(key) : "l"(keys + t) : "memory");
+        if (key != 0ull || global_timer_ns() - start > wait_ns) break;
+      }
+      if (key == 0ull) atomicExch(status, 6u);
+      asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(keys + t), "l"(0ull) : "memory");
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, d);
+      key = other > key ? other : key;
+    }
+    if (t == 0) chosen_key = key;
+  }
+  __syncthreads();
+  const long long chosen = (long long)(0xffffffffu - (unsigned)(chosen_key & 0xffffffffull));
+  if (embedding && next_hidden) {
+    const long long token = forced_next ? *forced_next : chosen;
+    if (token >= 0 && token < V)
+      for (int i = t; i < K; i += 256) next_hidden[i] = embedding[(size_t)token * K + i];
+  }
+  if (t == 0) *best = chosen;
+}
+}  // namespace
+
+extern "C" int fb_lm_head_shard(const void* x, const void* norm_weight, float eps, const void* weight, int vocab_rows, int row_base,
+                                int in_features, int dtype, void* logits, const fb_w3_push_t* keys, int rank, void* scratch,
+                                size_t scratch_bytes, fb_stream_t stream) {
+  if (!keys || keys->world < 1 || keys->world > 8 || rank < 0 || rank >= keys->world)
+    return fail(FB_EINVAL, "fb_lm_head_shard: key arrays of 1..8 ranks and a rank among them");
+  for (int r = 0; r < keys->world; ++r)
+    if (!keys->data[r] || !aligned(keys->data[r], 8)) return fail(FB_EINVAL, "fb_lm_head_shard: key array of rank %d missing or not 8-byte aligned", r);
+  if (row_base < 0 || vocab_rows < 1 || (long long)row_base + vocab_rows > (1ll << 30)) return fail(FB_ELIMIT, "fb_lm_head_shard: rows outside 0..2^30");
+  int64_t unused = 0;
+  return run_head(x, norm_weight, eps, weight, vocab_rows, in_features, dtype, logits, &unused, nullptr, nullptr, nullptr, scratch, scratch_bytes,
+                  stream, row_base, keys, rank);
+}
+
+extern "C" int fb_tp_argmax(void* keys, int world, int64_t* best, const int64_t* forced_next, const void* embedding, void* next_hidden,
+                            int vocab, int in_features, unsigned* status, uint64_t wait_ns, fb_stream_t stream) {
+  if (!keys || !best || !status) return fail(FB_EINVAL, "fb_tp_argmax: null pointer");
+  if (world < 1 || world > 8) return fail(FB_ELIMIT, "fb_tp_argmax: world outside 1..8");
+  if (!aligned(keys, 8) || !aligned(best, 8) || !aligned(forced_next, 8)) return fail(FB_EINVAL, "fb_tp_argmax: keys, best and forced_next must be 8-byte aligned");
+  if ((embedding == nullptr) != (next_hidden == nullptr)) return fail(FB_EINVAL, "fb_tp_argmax: embedding and next_hidden go together");
+  if (embedding && (vocab < 1 || in_features < 1)) return fail(FB_ELIMIT, "fb_tp_argmax: empty embedding table");
+  if (wait_ns > 60000000000ull) return fail(FB_ELIMIT, "fb_tp_argmax: wait limit above 60 s");
+  return launch_pdl(tp_argmax_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), "tp_argmax launch",
+                    static_cast<unsigned long long*>(keys), world, reinterpret_cast<long long*>(best), reinterpret_cast<const long long*>(forced_next),
+                    static_cast<const unsigned short*>(embedding), static_cast<unsigned short*>(next_hidden), vocab, in_features, status,
+                    (unsigned long long)(wait_ns ? wait_ns : 10000000000ull));
 }
 
 extern "C" int fb_embed_row(const void* embedding, const int64_t* token, void* out, int vocab, int in_features, fb_stream_t stream) {

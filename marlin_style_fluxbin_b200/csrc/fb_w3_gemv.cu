@@ -1000,8 +1000,9 @@ extern "C" int fb_w3_gemv_push(const void* x, int act_dtype, int transform, cons
                                const fb_w3_matrix_t* matrix, int scale_dtype, int in_features, const fb_w3_push_t* push,
                                void* scratch, size_t scratch_bytes, unsigned flags, fb_stream_t stream) {
   if (!push || !matrix) return fail(FB_EINVAL, "fb_w3_gemv_push: matrix and push descriptor must be non-null");
-  if (transform != 0 && transform != FB_W3_INPUT_RMSNORM && transform != FB_W3_INPUT_SILU_MUL)
+  if (transform != 0 && transform != FB_W3_INPUT_RMSNORM && transform != FB_W3_INPUT_SILU_MUL && transform != FB_W3_INPUT_ATTN_PIECES)
     return fail(FB_EINVAL, "fb_w3_gemv_push: unknown input transform %d", transform);
+  if (transform == FB_W3_INPUT_ATTN_PIECES) operand = x;  // the pieces are both the activations and the transform's operand
   return run_multi(x, act_dtype, 1, matrix, 1, scale_dtype, nullptr, in_features, scratch, scratch_bytes, flags, stream, transform,
                    operand, eps, push);
 }

@@ -191,7 +191,7 @@ class DecodeEngine:
         import torch.distributed._symmetric_memory as symm
 
         hidden, world = self.shape.hidden, self.tp_size
-        header = 64  # 8-byte slots: a status word first, then [site][rank][hidden] (value, mark) pairs
+        header = 64  # 8-byte slots: a status word first, [8..16) the LM-head keys of the ranks, then [site][rank][hidden] (value, mark) pairs
         self._xchg = symm.empty(2 * (header + 2 * world * hidden), dtype=torch.float32, device=self.device)
         self._xchg.zero_()
         group = self.group if self.group is not None else torch.distributed.group.WORLD
@@ -205,6 +205,13 @@ class DecodeEngine:
             data = 8 * (header + site * world * hidden)
             push = _native.w3_push_descriptor([base + data + 8 * self.tp_rank * hidden for base in bases])
             self._sites.append({"push": push, "parts": mine + data, "status": mine})
+        # vocabulary-split LM head: every rank scans V / world rows and delivers its best key to every rank
+        self.split_head = self.shape.vocab % world == 0
+        if self.split_head:
+            rows = self.shape.vocab // world
+            self._head_rows = (self.tp_rank * rows, rows)
+            self._head_keys = _native.w3_push_descriptor([base + 8 * 8 for base in bases])
+            self._head_keys_mine = mine + 8 * 8
         for layer in self.layers:  # no residual in the GEMV: the reduce kernel adds it on every rank
             entry = lambda lay, out: (lay["planes"], lay["scales"], lay["zeros"], out, None)  # noqa: E731
             layer.o_push = _native.w3_matrix_list([entry(layer.o, self.h_next)])
@@ -287,7 +294,7 @@ class DecodeEngine:
             else:
                 torch.mm(self.xn, layer.dense["qkv"].t(), out=self.qkv)  # q, k, v are views of this buffer
             # packed arm, unsharded: the attention launch stops at per-split pieces and the o GEMV merges them in its table build
-            merge_in_o = w3 and self.fuse_attention and not self.tp_push and self.tp_size == 1
+            merge_in_o = w3 and self.fuse_attention and (self.tp_push or self.tp_size == 1)
             if merge_in_o:
                 splits = nat.attn_decode_partial(self.q, self.k, self.v, layer.q_norm, layer.k_norm, cos, sin, self.k_cache[index],
                                                  self.v_cache[index], position, s.eps, scale, self.attn_scratch)
@@ -300,8 +307,12 @@ class DecodeEngine:
                 nat.attn_decode(self.q_rot, self.k_cache[index], self.v_cache[index], self.attn, position + 1, scale, self.attn_scratch)
             if self.tp_push:
                 site = self._sites[0]
-                nat.w3_gemv_push(self.attn, 0, None, 0.0, layer.o_push, self.attn.shape[-1], f16, site["push"], scratch=self.scratch,
-                                 decoded_bf16=dec)
+                if merge_in_o:
+                    nat.w3_gemv_push(self.attn_scratch, nat.W3_INPUT_ATTN_PIECES, None, float(splits), layer.o_push, self.attn.shape[-1], f16,
+                                     site["push"], scratch=self.scratch, decoded_bf16=dec, act_dtype=self.dtype)
+                else:
+                    nat.w3_gemv_push(self.attn, 0, None, 0.0, layer.o_push, self.attn.shape[-1], f16, site["push"], scratch=self.scratch,
+                                     decoded_bf16=dec)
                 nat.tp_reduce(site["parts"], self.tp_size, self.h, self.h_next, site["status"])
             elif merge_in_o:
                 nat.w3_gemv_attn_merge(self.attn_scratch, splits, self.dtype, self.attn.shape[-1], layer.o_list, 1, s.hidden, f16,
@@ -348,6 +359,16 @@ class DecodeEngine:
             launches += (5 if fuse else 8) + (0 if self.fuse_attention else 1) + (2 if self.tp_size > 1 else 0)
         # final RMSNorm + LM head + argmax (+ the next token's embedding row, written over the hidden
         # state once every CTA has staged it) in one launch
+        if self.tp_push and self.split_head:
+            base, rows = self._head_rows
+            nat.lm_head_shard(self.h, self.final_norm, s.eps, self.lm_head[base:base + rows], base, self._head_keys, self.tp_rank,
+                              logits_shard=self.logits[:, base:base + rows] if self.keep_logits else None, scratch=self.head_scratch)
+            nat.tp_argmax(self._head_keys_mine, self.tp_size, self.next_token if choice_out is None else choice_out, self._sites[0]["status"],
+                          forced_next=next_forced if embed_next else None, embedding=self.embedding if embed_next else None,
+                          next_hidden=self.h if embed_next else None)
+            self._h_is_embedded = embed_next
+            self.launches_per_step = launches + 2
+            return
         nat.lm_head_argmax(self.h, self.final_norm, s.eps, self.lm_head, self.next_token if choice_out is None else choice_out, logits=self.logits if self.keep_logits else None,
                            forced_next=next_forced if embed_next else None, embedding=self.embedding if embed_next else None,
                            next_hidden=self.h if embed_next else None, scratch=self.head_scratch)
@@ -372,6 +393,16 @@ class DecodeEngine:
             self.head_scratch.zero_()
             raise RuntimeError(f"a device-side wait expired: {bad}; scratch re-zeroed, results of that run are invalid")
 
+    def full_logits(self) -> torch.Tensor:
+        """A copy of the last step's logits ``[1, vocab]``; with the vocabulary-split LM head every rank holds a
+        shard, which an (eager, untimed) all-gather completes."""
+        if not (self.tp_push and getattr(self, "split_head", False)):
+            return self.logits.clone()
+        base, rows = self._head_rows
+        shards = [torch.empty(1, rows, device=self.device, dtype=self.dtype) for _ in range(self.tp_size)]
+        torch.distributed.all_gather(shards, self.logits[:, base:base + rows].contiguous(), group=self.group)
+        return torch.cat(shards, dim=-1)
+
     # ------------------------------------------------------------------ whole continuation
     @torch.inference_mode()
     def decode(self, first_token: torch.Tensor, start: int, steps: int, forced: torch.Tensor | None = None):
@@ -385,7 +416,7 @@ class DecodeEngine:
             fed.append(token.clone())
             self.step(token, start + i)
             predicted.append(self.next_token.clone())
-            logits.append(self.logits.clone())
+            logits.append(self.full_logits())
             token = self.next_token
         torch.cuda.synchronize(self.device)
         self.check_status()

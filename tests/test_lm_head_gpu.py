@@ -89,3 +89,55 @@ def test_embed_row_and_rejections():
     with pytest.raises(_native.NativeError, match="multiple of 8"):
         _native.lm_head_argmax(out[:, :100], None, 0.0, table[:, :100].contiguous(), best,
                                scratch=torch.zeros(256, dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("world", (2, 8))
+def test_vocabulary_shards_agree_through_the_key_exchange(world):
+    """The LM head split by rows over `world` ranks, all of them emulated on one device (the shard launches
+    complete before the receiving launches start, so no kernel waits on a later one): every rank's receiving
+    kernel names the row that the unsplit kernel names, the shards' logits tile the unsplit logits bit for bit,
+    the key slots come back to zero, and the planted tie across two shards goes to the lower row."""
+    from marlin_style_fluxbin_b200 import _native
+
+    vocab, k, dtype = 4096, 512, torch.bfloat16
+    gen = torch.Generator().manual_seed(world)
+    weight = torch.randint(-2, 3, (vocab, k), generator=gen).float()
+    x = torch.randint(-2, 3, (1, k), generator=gen).float()
+    top = float((x @ weight.t()).max()) + 8
+    pattern = torch.zeros(k)
+    pattern[0] = 1.0
+    x[0, 0] = 1.0
+    for row in (vocab // world + 3, 5):  # the same maximal logit in shard 1 and in shard 0: the lower row wins
+        weight[row] = 0
+        weight[row, 0] = top
+    weight, x = weight.to(dtype).cuda(), x.to(dtype).cuda()
+    embedding = torch.randn(vocab, k, generator=gen).to(dtype).cuda()
+    whole_best, whole_logits, _ = run_head(x, weight)
+    assert whole_best == 5
+
+    rows = vocab // world
+    keys = torch.zeros(world, world, dtype=torch.int64, device="cuda")  # [receiving rank][sending rank]
+    descriptor = _native.w3_push_descriptor([keys[r].data_ptr() for r in range(world)])
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    logits = torch.full((1, vocab), float("nan"), device="cuda", dtype=dtype)
+    scratch = torch.zeros(_native.lm_head_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    for rank in range(world):
+        _native.lm_head_shard(x, None, 1e-6, weight[rank * rows:(rank + 1) * rows], rank * rows, descriptor, rank,
+                              logits_shard=logits[:, rank * rows:(rank + 1) * rows], scratch=scratch)
+    forced = torch.tensor([77], dtype=torch.long, device="cuda")
+    for rank in range(world):
+        best = torch.full((1,), -1, dtype=torch.long, device="cuda")
+        hidden = torch.zeros(1, k, device="cuda", dtype=dtype)
+        _native.tp_argmax(keys[rank].data_ptr(), world, best, status.data_ptr(), forced_next=forced if rank % 2 else None, embedding=embedding,
+                          next_hidden=hidden)
+        torch.cuda.synchronize()
+        assert int(best[0]) == whole_best
+        assert torch.equal(hidden[0], embedding[77 if rank % 2 else whole_best])
+    assert torch.equal(logits, whole_logits)
+    assert int(keys.abs().sum()) == 0 and int(status[0]) == 0 and int(scratch.view(torch.int64).abs().sum()) == 0
+    # a key that never arrives: the bounded poll gives up, reports status 6 and the launch ends
+    keys[0, 0] = 12345
+    best = torch.full((1,), -1, dtype=torch.long, device="cuda")
+    _native.tp_argmax(keys[0].data_ptr(), world, best, status.data_ptr(), wait_ns=5_000_000)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 6 and int(keys[0].abs().sum()) == 0
