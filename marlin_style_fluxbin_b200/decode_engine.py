@@ -377,7 +377,7 @@ class DecodeEngine:
 
     def check_status(self) -> None:
         """After a synchronise: raise if a bounded device-side wait gave up (W3 GEMV staging: 1, tensor-core
-        kernel: 3, tensor-parallel reduce: 4).  The scratch and exchange words are re-zeroed so that the
+        kernel: 3, tensor-parallel reduce: 4, tensor-parallel argmax: 6).  The scratch and exchange words are re-zeroed so that the
         engine is usable again; the outputs of the failed run are invalid."""
         codes = {}
         if self.arm == "w3":
