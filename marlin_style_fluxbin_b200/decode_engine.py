@@ -82,6 +82,22 @@ def shard_groups(layout, rank, size):
             "zeros": layout["zeros"][lo:hi].contiguous(), "perm": torch.arange((hi - lo) * 128, dtype=torch.int16, device=layout["perm"].device)}
 
 
+def head_key(logit: float, row: int) -> int:
+    """The 64-bit key under which the LM-head kernels compare candidates (host mirror of the device code):
+    the fp32 bits of the (16-bit rounded) logit mapped to an unsigned order in the high word, ``2^32 - 1 - row``
+    in the low word, so that the largest key is the largest logit and, among equals, the lowest row, which is
+    ``torch.argmax``'s rule.  Keys of vocabulary shards compare across ranks because ``row`` is the global row."""
+    import struct
+
+    bits = struct.unpack("<I", struct.pack("<f", float(logit)))[0]
+    ordered = (~bits & 0xFFFFFFFF) if bits & 0x80000000 else (bits | 0x80000000)
+    return (ordered << 32) | (0xFFFFFFFF - int(row))
+
+
+def head_key_row(key: int) -> int:
+    return 0xFFFFFFFF - (int(key) & 0xFFFFFFFF)
+
+
 class _Layer:
     __slots__ = ("q", "k", "v", "o", "gate", "up", "down", "ln1", "ln2", "q_norm", "k_norm", "dense", "qkv_list", "gu_list", "o_list", "down_list",
                  "o_push", "down_push")

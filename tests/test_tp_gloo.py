@@ -1,6 +1,7 @@
 """Tensor-parallel sharding of the packed layouts, checked with two CPU ranks over gloo:
 column-parallel shards (output rows) concatenate, row-parallel shards (input groups) sum through an
-allreduce, and both reproduce the unsharded dequantise-then-matmul result."""
+allreduce, and both reproduce the unsharded dequantise-then-matmul result; the keys of the
+vocabulary-split LM head pick torch.argmax's row."""
 import os
 import socket
 
@@ -8,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from marlin_style_fluxbin_b200.decode_engine import shard_groups, shard_rows, synthetic_w3
+from marlin_style_fluxbin_b200.decode_engine import head_key, head_key_row, shard_groups, shard_rows, synthetic_w3
 from marlin_style_fluxbin_b200.gptq_deployment import restore_planar_w3, validate_planar_w3
 
 
@@ -43,6 +44,18 @@ def _worker(rank, world, port, failures):
         dist.all_reduce(partial)
         want = x2.double() @ restore_planar_w3(row).double().T
         torch.testing.assert_close(partial, want, rtol=1e-12, atol=1e-12)
+        # vocabulary-split LM head: every rank keys the best row of its shard, all ranks take the largest key;
+        # the choice equals torch.argmax of the whole logits, ties (planted across the two shards) included
+        logits = torch.randn(640, generator=gen).bfloat16()
+        logits[7] = logits[400] = logits[401] = 9.0
+        logits[100] = -0.0
+        rows = 640 // world
+        mine = max(head_key(float(logits[r]), r) for r in range(rank * rows, (rank + 1) * rows))
+        keys = [None] * world
+        dist.all_gather_object(keys, mine)
+        assert head_key_row(max(keys)) == int(torch.argmax(logits.float())) == 7
+        order = sorted(range(640), key=lambda r: head_key(float(logits[r]), r), reverse=True)
+        assert order == sorted(range(640), key=lambda r: (-float(logits[r]), r))  # descending logit, ascending row
     except Exception as exc:  # pragma: no cover - reported to the parent
         failures.put(f"rank {rank}: {exc!r}")
     finally:
