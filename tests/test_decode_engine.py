@@ -154,14 +154,14 @@ def test_fused_attention_equals_the_two_launch_form(position, dtype):
 
 
 @pytest.mark.parametrize("position", (0, 63, 200, 530, 1500))
-@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
-def test_attention_pieces_merged_by_the_consuming_gemv(position, dtype):
+@pytest.mark.parametrize("dtype,heads", ((torch.bfloat16, (8, 2)), (torch.float16, (8, 2)), (torch.bfloat16, (5, 1))))
+def test_attention_pieces_merged_by_the_consuming_gemv(position, dtype, heads):
     """The attention launch that stops at per-split pieces, merged inside the o-projection GEMV's table
     build, gives the output of fb_attn_decode_fused followed by the plain GEMV bit for bit (cache rows too)."""
     from marlin_style_fluxbin_b200 import _native
     from marlin_style_fluxbin_b200.decode_engine import synthetic_w3
 
-    q_heads, kv_heads, dim, max_positions, hidden = 8, 2, 128, 1536, 384
+    (q_heads, kv_heads), dim, max_positions, hidden = heads, 128, 1536, 384  # five heads: an odd number of groups in the GEMV
     gen = torch.Generator().manual_seed(position + 11)
     rnd = lambda *shape: torch.randn(*shape, generator=gen).to(dtype).cuda()  # noqa: E731
     q, k, v = rnd(1, q_heads * dim), rnd(1, kv_heads * dim), rnd(1, kv_heads * dim)
