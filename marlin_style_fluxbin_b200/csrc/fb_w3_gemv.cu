@@ -15,22 +15,26 @@
 //  * The three bit planes of a unit (6 runs of 512 bytes: group half x plane) are staged into
 //    shared memory by ONE tiled bulk copy (cp.async.bulk.tensor + mbarrier).  Every warp owns a
 //    private ring of staged units and refills a slot as soon as it has read it, so warps never
-//    wait for one another between table builds; scales and zero points come straight from
-//    global memory, requested before the lookups and used after them.
+//    wait for one another between table builds.
 //  * Two CTAs of 8 warps per SM (together the whole register file; 110 KB of shared memory each
 //    with M = 1): each K super-block is served by floor(2 SMs / super-blocks) CTAs that split its
 //    rows.  Two smaller CTAs beat one of 16 warps: when the first of a pair leaves, CTAs of the
 //    next kernel in the stream move in and stage weights beside the one still running.
 //  * A warp whose rows are a single unit carries its sum across the K blocks its CTA walks
 //    (K > 4096) in registers; otherwise the running sums go through an L2-resident scratch.
-//  * Scales and zero points of a unit ride with its planes (two more small tiled copies into
-//    the same ring slot), so HBM latency never sits between a unit's lookups and its result.
+//  * M = 1: scales and zero points of a unit ride with its planes (two more small tiled copies
+//    into the same ring slot), so HBM latency never sits between a unit's lookups and its
+//    result.  M > 1 (no room in the ring): coalesced global loads requested one task ahead.
+//  * Fused producers of x (M = 1): RMSNorm, the SwiGLU gate, or the merge of the attention
+//    launch's per-split pieces.  Every thread transforms ONE of the K block's 256 activations and
+//    shares it through shared memory; the tables are built from the shared values.
 //  * Two lookups are accumulated by one packed fp32x2 add or multiply-add (an even-step and an
 //    odd-step partial sum share a 64-bit register pair; the plane weights 1, 2, -4 ride in the
 //    multiply-add), which halves the arithmetic of the main loop and leaves four accumulators.
 //  * Launched with programmatic dependent launch: barrier set-up and the first weight copies
 //    come before griddepcontrol.wait; everything that reads activations or touches scratch
-//    comes after it.
+//    comes after it, and the later ring stages are requested after the first table build (their
+//    issue would otherwise sit in front of it on the critical path).
 //  * Split-K is combined inside the kernel with ONE 64-bit atomic add per contribution: the
 //    partial sum in fixed point (2^-26 units) plus an arrival count in the low bits.  Integer
 //    addition is associative, so the result is independent of arrival order (deterministic,
