@@ -37,7 +37,7 @@ LAYERS = 36
 NOMINAL_HBM_GBS = 8000.0
 # DRAM bytes over algorithmic bytes of a 12288x4096 launch, from one profiler capture of that launch;
 # traffic grows with the bytes a launch streams, so other launches are scaled by the same ratio.
-DRAM_TRAFFIC_RATIO = 20.226 / 20.087
+DRAM_TRAFFIC_RATIO = 20.219 / 20.087
 METRIC = "W3 GEMV HBM GB/s (% of 8 TB/s) per Qwen3-8B shape; batch-1 decode tokens/s"
 
 
@@ -597,19 +597,21 @@ def cpu_reference(steps: int, warmup: int):
         dense = orc.w3_dequant(planes, scales, orc.F16, zeros, None, orc.F32)
         t_dequant += time.perf_counter() - t0
         layer.append((dense, rng.standard_normal((1, k), dtype=np.float32)))
+    passes = 64  # a step is 64 passes over the layer (about half a second): ten seconds or so of timed CPU work at the default 20 steps
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        for dense, x in layer:
-            orc.dense_gemv_f32(dense, x)
+        for _ in range(passes):
+            for dense, x in layer:
+                orc.dense_gemv_f32(dense, x)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
-    step_s = sum(times) / len(times)
+    step_s = sum(times) / len(times) / passes
     nbytes = sum(gemv_bytes(o, k) for _, o, k in SHAPES)
     return {"value": nbytes / step_s / 1e9, "cores": orc.num_threads(), "step_ms": step_s * 1e3,
             "dequant_s_per_layer": t_dequant,
-            "sample": (f"one layer (7 Linears, {nbytes} packed bytes) per step: fp32 matmul on weights dequantised once "
-                       f"outside the timer ({t_dequant:.2f} s per layer when redone every call)")}
+            "sample": (f"one layer (7 Linears, {nbytes} packed bytes), {passes} passes per step, {sum(times):.1f} s timed: fp32 matmul on "
+                       f"weights dequantised once outside the timer ({t_dequant:.2f} s per layer when redone every call)")}
 
 
 def small_case(args):
@@ -764,7 +766,7 @@ def main():
             entry["pct_of_measured"] = round(100 * entry["gbs"] / peak, 1)
             # the same time against the byte count with zero points held as fp16
             entry["gbs_zeros_as_fp16"] = round(entry["gbs"] * entry["bytes_zeros_as_fp16"] / entry["bytes"], 1)
-        cpu = cpu_reference(3, 1) if world == 1 and not args.headline_only else None
+        cpu = cpu_reference(20, 2) if world == 1 and not args.headline_only else None
         launches_per_step = result["launches"] // args.steps
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
