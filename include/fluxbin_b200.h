@@ -52,6 +52,17 @@ extern "C" {
                                    (reference: inline_main, csrc/w3_lut.cu:251-273); follow
                                    with fb_w3_finish */
 
+#define FB_W3_SAME_INPUT 8u /* the caller states that x (and perm) were complete before the launch DIRECTLY
+                              ahead of this one in the stream began, that that launch is an fb_w3_gemv*
+                              launch (these release their dependents only after their own wait) or an
+                              ordinary launch, and that `out` and `scratch` are not touched by it: k_proj
+                              behind q_proj, up_proj behind gate_proj on the same activations, each with
+                              its own scratch.  The kernel then starts reading at once instead of waiting
+                              for the launch ahead (about 1.3 us after that launch's last store) and
+                              waits for it only before it ends, so stream order holds for whatever
+                              follows.  At most three such launches in a row share no scratch if three
+                              scratches rotate. */
+
 typedef void* fb_stream_t; /* a cudaStream_t */
 
 /* Message describing the last rejected call made by this thread ("" if none). */

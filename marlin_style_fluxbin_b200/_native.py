@@ -18,6 +18,7 @@ FB_F16, FB_BF16 = 0, 1
 FB_W3_DECODED_BF16 = 1
 FB_W3_NO_PDL = 2
 FB_W3_GROUP_PARTIALS = 4
+FB_W3_SAME_INPUT = 8
 
 _lib = None
 
@@ -133,7 +134,13 @@ def library() -> ctypes.CDLL:
     return _lib
 
 
+# The last call into the library per (device, stream), when it was a plain W3 GEMV launch: its activation
+# buffer and how many launches in a row have read it.  Any other library call forgets it (see ``w3_gemv``).
+_same_input: dict = {}
+
+
 def check(code: int) -> None:
+    _same_input.clear()  # whatever was just launched is now the launch ahead of the next one
     if code != 0:
         raise NativeError(library().fb_last_error().decode() or f"native call failed with code {code}")
 
@@ -173,6 +180,8 @@ _retired: list[torch.Tensor] = []
 
 def _family_bytes(family: str) -> int:
     lib = library()
+    if family.startswith("w3#"):  # the second and third scratch of launches that may overlap (one activation row)
+        return int(lib.fb_w3_gemv_scratch_bytes(1, 65536, 32640))
     if family == "w3":
         return int(lib.fb_w3_gemv_scratch_bytes(4, 65536, 32640))
     if family == "w3mma":
@@ -194,6 +203,13 @@ def scratch_for(device: torch.device, nbytes: int, family: str = "w3") -> torch.
         buf = torch.zeros(max(nbytes, _family_bytes(family)), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
+
+
+def status_word(device: torch.device | None = None) -> int:
+    """Synchronise and return the largest device-side status word over the scratches handed out by
+    ``scratch_for`` (0: no bounded wait expired); nothing is raised or re-zeroed."""
+    torch.cuda.synchronize(device)
+    return max((int(buf[:4].view(torch.int32)[0]) for buf in _scratch.values()), default=0)
 
 
 def check_status(device: torch.device | None = None) -> None:
@@ -219,17 +235,31 @@ def w3_gemv(x, planes, scales, zeros, perm, out, *, decoded_bf16=False, group_pa
     m, k = x.shape
     o = planes.shape[2]
     need = w3_scratch_bytes(m, o, k)
-    if scratch is None:
-        scratch = scratch_for(x.device, need)
     if _os.environ.get("FB_NO_PDL"):
         pdl = False
+    # Consecutive Linears on the SAME activations (k_proj and v_proj behind q_proj, up_proj behind gate_proj): the
+    # launch ahead is a W3 GEMV that read this very buffer, so the buffer was complete before that launch began and
+    # this one need not wait for it (FB_W3_SAME_INPUT).  Such launches may overlap, so each takes its own scratch
+    # (three rotate; a fourth launch in a row waits again).  Any other call into the library in between, a scratch
+    # or a column order chosen by the caller, or several rows switch this off.
+    key = (x.device.index if x.device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(x.device).cuda_stream)
+    ahead = _same_input.get(key)
+    here = (x.data_ptr(), tuple(x.shape), x.dtype)
+    follow = (ahead is not None and ahead[0] == here and ahead[1] < 3 and scratch is None and pdl and m == 1 and perm is None
+              and not group_partials and not _os.environ.get("FB_NO_SAME_INPUT"))
+    slot = ahead[1] if follow else 0
+    own_scratch = scratch is None
+    if own_scratch:
+        scratch = scratch_for(x.device, need, "w3" if slot == 0 else f"w3#{slot}")
     flags = (FB_W3_DECODED_BF16 if decoded_bf16 else 0) | (0 if pdl else FB_W3_NO_PDL) | (
-        FB_W3_GROUP_PARTIALS if group_partials else 0)
+        FB_W3_GROUP_PARTIALS if group_partials else 0) | (FB_W3_SAME_INPUT if follow else 0)
     with torch.cuda.device(x.device):
         check(library().fb_w3_gemv(
             ptr(x), dtype_tag(x.dtype), m, ptr(planes), ptr(scales), dtype_tag(scales.dtype),
             ptr(zeros), ptr(perm), ptr(out), o, k, ptr(scratch), scratch.numel() * scratch.element_size(),
             flags, stream_handle(x.device)))
+    if own_scratch and pdl and m == 1 and perm is None and not group_partials:
+        _same_input[key] = (here, slot + 1)
 
 
 def w3_finish(partials, out) -> None:

@@ -112,6 +112,7 @@ struct W3Params {
   int S, nSB;          // K blocks per super-block (one CTA walks them in turn), super-blocks
   int units_per_slice, units_extra;  // nRU / slices and nRU % slices
   int group_partials;  // write scale-multiplied per-group sums instead of reducing
+  int same_input;      // FB_W3_SAME_INPUT: no wait at the start, one before the end
 };
 
 // Shared-memory geometry.  Entry p of table t for activation row m lives at byte
@@ -227,9 +228,13 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
   const uint32_t ring_u32 = smem_u32(smem + G_::kRingOffset) + (uint32_t)(warp * kStages * G_::kSlotBytes);
   const uint32_t bars_u32 = smem_u32(smem + G_::kBarOffset) + (uint32_t)(warp * kStages * 8);
 
-  // The next kernel in the stream may be scheduled as soon as this grid's CTAs leave; it orders
-  // itself after this grid with its own wait before touching activations or scratch.
-  pdl_launch_dependents();
+  // Release of the next kernel in the stream.  A launch that waits for the one ahead of it releases
+  // its dependents only AFTER that wait (further down): whatever follows it in the stream then
+  // starts with everything before this launch complete.  That is what allows a launch whose inputs
+  // were ready before the launch ahead began (FB_W3_SAME_INPUT: k_proj behind q_proj, up_proj
+  // behind gate_proj) to skip the wait at its start: it begins at once, releases at once, and waits
+  // for the launch ahead only before it ends, so that stream order holds for what comes after.
+  if (p.same_input) pdl_launch_dependents();
 
   if (threadIdx.x < kWarps * kStages) {
     mbar_init(smem_u32(smem + G_::kBarOffset) + threadIdx.x * 8, 1);  // the issuing lane's expect_tx
@@ -372,7 +377,10 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
     }
 
   // Everything below reads activations and writes scratch / outputs of this stream.
-  pdl_wait_prior_grid();
+  if (!p.same_input) {
+    pdl_wait_prior_grid();
+    pdl_launch_dependents();
+  }
 
   // Raw 16-bit activations of one lane's table (8 values); the next K block's are fetched while
   // the current one is being computed.
@@ -766,6 +774,7 @@ __global__ void __launch_bounds__(Geom<M>::kWarps * 32, Geom<M>::kCtasPerSm) w3_
     }
   }
   settle();
+  if (p.same_input) pdl_wait_prior_grid();  // stream order for everything that comes after this launch
 }
 
 struct Plan {
@@ -876,7 +885,9 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   if (K < 128 || K % 128 || K / 128 > 255) return fail(FB_ELIMIT, "fb_w3_gemv: K=%d must be a multiple of 128 with at most 255 groups", K);
   if (!aligned(x, 16) && !perm) return fail(FB_EINVAL, "fb_w3_gemv: x must be 16-byte aligned");
   if (!aligned(x, 2) || (perm && !aligned(perm, 2))) return fail(FB_EINVAL, "fb_w3_gemv: 16-bit tensors must be 2-byte aligned");
-  if (flags & ~(FB_W3_DECODED_BF16 | FB_W3_NO_PDL | FB_W3_GROUP_PARTIALS)) return fail(FB_EINVAL, "fb_w3_gemv: unknown flag bits 0x%x", flags);
+  if (flags & ~(FB_W3_DECODED_BF16 | FB_W3_NO_PDL | FB_W3_GROUP_PARTIALS | FB_W3_SAME_INPUT)) return fail(FB_EINVAL, "fb_w3_gemv: unknown flag bits 0x%x", flags);
+  if ((flags & FB_W3_SAME_INPUT) && (prologue != 0 || push || (flags & FB_W3_NO_PDL)))
+    return fail(FB_EINVAL, "fb_w3_gemv: FB_W3_SAME_INPUT goes with a plain programmatic launch (no fused input, no push)");
   if (group_partials && (m != 1 || n_matrices != 1)) return fail(FB_EINVAL, "fb_w3_gemv: group partials need M = 1 and a single matrix");
   const int G = K / 128;
   const size_t x_bytes = (size_t)m * K * 2;
@@ -957,6 +968,7 @@ int run_multi(const void* x, int act_dtype, int m, const fb_w3_matrix_t* matrice
   p.units_extra = p.nRU % plan.slices;
   p.nSB = plan.nSB;
   p.group_partials = group_partials ? 1 : 0;
+  p.same_input = (flags & FB_W3_SAME_INPUT) ? 1 : 0;
   if (plan.smem > (size_t)info->max_smem_optin) return fail(FB_ELIMIT, "fb_w3_gemv: plan needs %zu bytes of shared memory", plan.smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool correct = (flags & FB_W3_DECODED_BF16) != 0;

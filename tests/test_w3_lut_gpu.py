@@ -522,3 +522,55 @@ def test_polling_reduce_gives_up_after_its_limit():
     _native.tp_reduce(buffer.data_ptr(), world, None, out, status.data_ptr(), wait_ns=5_000_000)
     torch.cuda.synchronize()
     assert int(status[0]) == 0 and torch.equal(out.float().cpu(), torch.full((1, n), 3.0))
+
+
+def test_linears_on_the_same_activations_do_not_wait_for_one_another():
+    """q/k/v-style launches behind one another on ONE activation buffer: the second and third start without
+    waiting for the launch ahead (each with its own scratch), the fourth waits again; results equal the
+    launches made one by one with a caller's scratch (which never take that path), eagerly and in a graph
+    replayed many times back to back."""
+    from marlin_style_fluxbin_b200 import _native
+
+    shapes = ((4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096))
+    cases = [to_cuda(make_case(o, k, seed=30 + i, zeros=True)[0]) for i, (o, k) in enumerate(shapes)]
+    x = torch.randn(1, 4096, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    other = x.clone()
+    own = torch.zeros(_native.w3_scratch_bytes(1, 4096, 4096), dtype=torch.uint8, device="cuda")
+    want = []
+    for lg in cases:
+        out = torch.empty(1, lg["planes"].shape[2], device="cuda", dtype=torch.bfloat16)
+        _native.w3_gemv(x, lg["planes"], lg["scales"], lg["zeros"], None, out, scratch=own)
+        want.append(out)
+    outs = [torch.full_like(w, float("nan")) for w in want]
+    def stream_key():
+        return (torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
+
+    def launch_all():
+        seen = []
+        for lg, out in zip(cases, outs):
+            _native.w3_gemv(x, lg["planes"], lg["scales"], lg["zeros"], None, out)
+            seen.append(_native._same_input[stream_key()][1])
+        return seen
+
+    _native.w3_gemv(other, cases[0]["planes"], cases[0]["scales"], cases[0]["zeros"], None, torch.empty_like(want[0]))  # another buffer ahead
+    assert launch_all() == [1, 2, 3, 1]  # launches in a row on this buffer; the fourth starts a new row
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(outs, want))
+    _native.rmsnorm(x, torch.ones(4096, device="cuda", dtype=torch.bfloat16), torch.empty_like(x), 1e-6)
+    assert stream_key() not in _native._same_input  # any other launch of the library forgets the buffer
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        launch_all()  # sizes this stream's three scratches
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(8):
+                launch_all()
+        for out in outs:
+            out.fill_(float("nan"))
+        for _ in range(50):
+            graph.replay()
+        stream.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(outs, want))
+    _native.check_status(torch.device("cuda"))
